@@ -1,0 +1,60 @@
+// Host-side plumbing shared by every translation unit of libghost_b200: status codes, the
+// thread-local error message, the kernel-launch counter, the per-device error word that kernels
+// write when a bounded wait gives up, and TMA tensor-map construction.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/ghost_b200.h"
+
+namespace gb {
+
+// ---- error message (thread local) -------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+
+#define GB_CUDA_OK(expr)                                                                   \
+  do {                                                                                     \
+    cudaError_t _e = (expr);                                                               \
+    if (_e != cudaSuccess)                                                                 \
+      return ::gb::fail(GHOST_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                    \
+                        cudaGetErrorString(_e), __FILE__, __LINE__);                       \
+  } while (0)
+
+#define GB_REQUIRE(cond, ...)                                                              \
+  do {                                                                                     \
+    if (!(cond)) return ::gb::fail(GHOST_ERR_INVALID, __VA_ARGS__);                        \
+  } while (0)
+
+// ---- launch accounting -------------------------------------------------------------------
+void count_launch(int n = 1);
+int post_launch(const char* what);  // cudaGetLastError -> status
+
+// ---- per-device state ----------------------------------------------------------------------
+struct DeviceState {
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  int* err_word = nullptr;  // device address of the kernel error word
+};
+// Returns nullptr (and sets the error) if the current device is not sm_100.
+const DeviceState* device_state();
+
+// ---- TMA ---------------------------------------------------------------------------------------
+// 2-D row-major bf16 tensor [rows, cols] with row pitch `ld` elements; box = [box_rows, 64 cols]
+// (64 bf16 = 128 bytes) with the 128-byte swizzle.  Out-of-bounds elements read as zero.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                      uint32_t box_rows, uint32_t box_cols = 64);
+
+// 3-D view [samples, rows, cols] of a row-major bf16 matrix (sample pitch = rows * ld); box =
+// [1, box_rows, 64 cols].  Rows past the end of a sample read as zero, so a K-loop over one
+// sample's tokens never sees its neighbour's.
+int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t samples, uint64_t rows,
+                      uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols = 64);
+
+inline int ceil_div(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
+
+}  // namespace gb

@@ -1,0 +1,310 @@
+// Embedding-table terms of the ghost hot path (index / gather work, HBM- and latency-bound).
+//
+// embedding_dot:  M[v, b] = sum_{t, s : id_b[t] == id_v[s]} <G_b[t], G_v[s]>
+//   The reference scatters the validation rows into a [vocab, d] table and gathers it at the train
+//   ids (ghostEngines/supported_layers_grad_samplers_dotprod.py:203-210); here the validation
+//   tokens are chained per token id in a vocab-sized head table (4 bytes per id) and every train
+//   token walks the chain of its id, so no [vocab, d] scratch exists and the result is split per
+//   validation sample.
+//
+// embedding_wgrad: averaged train gradient of the table (:214-235).  Train tokens are bucketed by
+//   id (count, scan, fill), each bucket is put in ascending token order and summed in float32 in
+//   that order, rounded to the table dtype once, then divided by n_train -- the arithmetic and
+//   the order of the CPU index_add_, so the result is bit-identical to it.
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace gb {
+
+__device__ __forceinline__ float ewarp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <typename T> __device__ __forceinline__ float ld_f32(const T* p);
+template <> __device__ __forceinline__ float ld_f32<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ld_f32<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ float round_to(float x);
+template <> __device__ __forceinline__ float round_to<float>(float x) { return x; }
+template <> __device__ __forceinline__ float round_to<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// ---------------------------------------------------------------- dot product
+__global__ void emb_chain_val_kernel(const long long* __restrict__ ids_val, long long n_tok, int vocab,
+                                     int* __restrict__ head, int* __restrict__ next) {
+  for (long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n_tok;
+       j += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long id = ids_val[j];
+    if (id >= 0 && id < vocab) next[j] = atomicExch(&head[id], static_cast<int>(j));
+    else next[j] = -1;
+  }
+}
+
+// grid (token blocks of one sample, n_train); 8 warps, each walks kTokPerWarp tokens
+template <typename T>
+__global__ void __launch_bounds__(256)
+emb_dot_kernel(const long long* __restrict__ ids, const T* __restrict__ G, int n_train, int n_val,
+               long long Tn, int d, int vocab, const int* __restrict__ head,
+               const int* __restrict__ next, float scale, float* __restrict__ M, int tok_per_block) {
+  extern __shared__ float s_acc[];   // [n_val]
+  const int b = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int v = threadIdx.x; v < n_val; v += blockDim.x) s_acc[v] = 0.f;
+  __syncthreads();
+  const long long t_begin = static_cast<long long>(blockIdx.x) * tok_per_block;
+  long long t_end = t_begin + tok_per_block;
+  if (t_end > Tn) t_end = Tn;
+  const T* Gval = G + static_cast<long long>(n_train) * Tn * d;
+  const bool vec = (d % 8 == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0);
+  for (long long t = t_begin + warp; t < t_end; t += 8) {
+    const long long id = ids[static_cast<long long>(b) * Tn + t];
+    if (id < 0 || id >= vocab) continue;
+    int j = head[id];
+    const T* row = G + (static_cast<long long>(b) * Tn + t) * d;
+    while (j >= 0) {
+      const T* vrow = Gval + static_cast<long long>(j) * d;
+      float s = 0.f;
+      if (vec && sizeof(T) == 2) {
+        for (int f = lane * 8; f < d; f += 256) {
+          const uint4 x = *reinterpret_cast<const uint4*>(row + f);
+          const uint4 y = *reinterpret_cast<const uint4*>(vrow + f);
+          const uint32_t xx[4] = {x.x, x.y, x.z, x.w}, yy[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s = fmaf(__uint_as_float(xx[e] << 16), __uint_as_float(yy[e] << 16), s);
+            s = fmaf(__uint_as_float(xx[e] & 0xffff0000u), __uint_as_float(yy[e] & 0xffff0000u), s);
+          }
+        }
+      } else {
+        for (int f = lane; f < d; f += 32) s = fmaf(ld_f32<T>(row + f), ld_f32<T>(vrow + f), s);
+      }
+      s = ewarp_sum(s);
+      if (lane == 0) atomicAdd(&s_acc[j / Tn], s);
+      j = next[j];
+    }
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < n_val; v += blockDim.x) {
+    const float s = s_acc[v];
+    if (s != 0.f) atomicAdd(&M[static_cast<long long>(v) * n_train + b], s * scale);
+  }
+}
+
+// ---------------------------------------------------------------- train gradient
+__global__ void emb_count_kernel(const long long* __restrict__ ids, long long n_tok, int vocab,
+                                 int* __restrict__ counts) {
+  for (long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n_tok;
+       j += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long id = ids[j];
+    if (id >= 0 && id < vocab) atomicAdd(&counts[id], 1);
+  }
+}
+
+// exclusive scan of counts[0..vocab) into offsets (single block of 1024 threads)
+__global__ void __launch_bounds__(1024)
+emb_scan_kernel(const int* __restrict__ counts, int vocab, int* __restrict__ offsets) {
+  __shared__ int s_warp[32];
+  __shared__ int s_carry;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int base = 0; base < vocab; base += 1024) {
+    const int i = base + threadIdx.x;
+    const int c = (i < vocab) ? counts[i] : 0;
+    int x = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) s_warp[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      s_warp[lane] = w;   // inclusive over warps
+    }
+    __syncthreads();
+    const int warp_off = (warp == 0) ? 0 : s_warp[warp - 1];
+    const int carry = s_carry;
+    if (i < vocab) offsets[i] = carry + warp_off + x - c;
+    __syncthreads();
+    if (threadIdx.x == 1023) s_carry = carry + warp_off + x;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) offsets[vocab] = s_carry;
+}
+
+__global__ void emb_fill_kernel(const long long* __restrict__ ids, long long n_tok, int vocab,
+                                const int* __restrict__ offsets, int* __restrict__ cursor,
+                                int* __restrict__ perm) {
+  for (long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n_tok;
+       j += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long id = ids[j];
+    if (id >= 0 && id < vocab) {
+      const int pos = atomicAdd(&cursor[id], 1);
+      perm[offsets[id] + pos] = static_cast<int>(j);
+    }
+  }
+}
+
+// one warp per table row: ascending-order float32 segment sum, dtype rounding as the reference
+template <typename T>
+__global__ void __launch_bounds__(256)
+emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restrict__ offsets,
+                  const int* __restrict__ perm, float pre_scale, float divisor, int accumulate,
+                  T* __restrict__ out) {
+  const int k = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (k >= vocab) return;
+  const int off = offsets[k];
+  const int cnt = offsets[k + 1] - off;
+  int mine = INT_MAX;
+  if (cnt > 0 && cnt <= 32) {
+    if (lane < cnt) mine = perm[off + lane];
+    // bitonic sort of 32 keys across the warp, ascending
+#pragma unroll
+    for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        const int other = __shfl_xor_sync(0xffffffffu, mine, stride);
+        const bool up = ((lane & size) == 0);
+        const bool lower = ((lane & stride) == 0);
+        const int lo = min(mine, other), hi = max(mine, other);
+        mine = (lower == up) ? lo : hi;
+      }
+    }
+  }
+  for (int f0 = 0; f0 < d; f0 += 32 * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (cnt > 0 && cnt <= 32) {
+      for (int i = 0; i < cnt; ++i) {
+        const int j = __shfl_sync(0xffffffffu, mine, i);
+        const T* row = G + static_cast<long long>(j) * d;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int f = f0 + q * 32 + lane;
+          if (f < d) acc[q] += round_to<T>(ld_f32<T>(row + f) * pre_scale);
+        }
+      }
+    } else if (cnt > 32) {
+      // selection in ascending token order: next = min{perm[i] : perm[i] > last}
+      int last = -1;
+      for (int i = 0; i < cnt; ++i) {
+        int best = INT_MAX;
+        for (int q = lane; q < cnt; q += 32) {
+          const int j = perm[off + q];
+          if (j > last && j < best) best = j;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+        last = best;
+        const T* row = G + static_cast<long long>(best) * d;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int f = f0 + q * 32 + lane;
+          if (f < d) acc[q] += round_to<T>(ld_f32<T>(row + f) * pre_scale);
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int f = f0 + q * 32 + lane;
+      if (f < d) {
+        float o = round_to<T>(acc[q]);
+        o = round_to<T>(__fdiv_rn(o, divisor));
+        T* dst = out + static_cast<long long>(k) * d + f;
+        if (accumulate) o = round_to<T>(ld_f32<T>(dst) + o);
+        *dst = from_f32<T>(o);
+      }
+    }
+  }
+}
+
+static inline long long up256(long long x) { return (x + 255) / 256 * 256; }
+
+}  // namespace gb
+
+using namespace gb;
+
+extern "C" long long ghost_embedding_dot_workspace_bytes(int n_val, long long T, int vocab) {
+  return up256(4ll * vocab) + up256(4ll * n_val * T);
+}
+
+extern "C" int ghost_embedding_dot(const long long* ids, const void* G, int is_f32, int n_train, int n_val,
+                                   long long T, int d, int vocab, float scale, float* M_out, void* ws,
+                                   long long ws_bytes, void* stream) {
+  const DeviceState* ds = device_state();
+  if (!ds) return GHOST_ERR_DEVICE;
+  GB_REQUIRE(ids && G && M_out && ws, "ghost_embedding_dot: null pointer");
+  GB_REQUIRE(n_train > 0, "No training samples to compute dot product, check batch sizes.");
+  GB_REQUIRE(n_val > 0 && T > 0 && d > 0 && vocab > 0, "ghost_embedding_dot: bad dimensions");
+  GB_REQUIRE(static_cast<long long>(n_val) * T < INT_MAX && n_train <= 65535, "ghost_embedding_dot: too many tokens");
+  GB_REQUIRE(n_val <= 8192, "ghost_embedding_dot: at most 8192 validation samples");
+  GB_REQUIRE(ws_bytes >= ghost_embedding_dot_workspace_bytes(n_val, T, vocab), "ghost_embedding_dot: workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int* head = static_cast<int*>(ws);
+  int* next = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + up256(4ll * vocab));
+  const long long n_vtok = static_cast<long long>(n_val) * T;
+  GB_CUDA_OK(cudaMemsetAsync(head, 0xFF, 4ull * vocab, st));
+  GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
+  int blocks = static_cast<int>((n_vtok + 255) / 256);
+  if (blocks > ds->sm_count * 8) blocks = ds->sm_count * 8;
+  emb_chain_val_kernel<<<blocks, 256, 0, st>>>(ids + static_cast<long long>(n_train) * T, n_vtok, vocab, head, next);
+  count_launch();
+  int rc = post_launch("emb_chain_val_kernel");
+  if (rc != GHOST_OK) return rc;
+  const int tok_per_block = 64;
+  dim3 grid(ceil_div(T, tok_per_block), n_train);
+  const size_t smem = sizeof(float) * n_val;
+  if (is_f32)
+    emb_dot_kernel<float><<<grid, 256, smem, st>>>(ids, static_cast<const float*>(G), n_train, n_val, T, d, vocab, head, next, scale, M_out, tok_per_block);
+  else
+    emb_dot_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(ids, static_cast<const __nv_bfloat16*>(G), n_train, n_val, T, d, vocab, head, next, scale, M_out, tok_per_block);
+  count_launch();
+  return post_launch("emb_dot_kernel");
+}
+
+extern "C" long long ghost_embedding_wgrad_workspace_bytes(int n_train, long long T, int vocab) {
+  return 3 * up256(4ll * (vocab + 1)) + up256(4ll * n_train * T);
+}
+
+extern "C" int ghost_embedding_wgrad(const long long* ids, const void* G, int is_f32, int n_train, long long T,
+                                     int d, int vocab, float pre_scale, float divisor, int accumulate,
+                                     void* out, void* ws, long long ws_bytes, void* stream) {
+  const DeviceState* ds = device_state();
+  if (!ds) return GHOST_ERR_DEVICE;
+  GB_REQUIRE(ids && G && out && ws, "ghost_embedding_wgrad: null pointer");
+  GB_REQUIRE(n_train > 0 && T > 0 && d > 0 && vocab > 0, "ghost_embedding_wgrad: bad dimensions");
+  GB_REQUIRE(static_cast<long long>(n_train) * T < INT_MAX, "ghost_embedding_wgrad: too many tokens");
+  GB_REQUIRE(divisor != 0.f, "ghost_embedding_wgrad: divisor must be non-zero");
+  GB_REQUIRE(ws_bytes >= ghost_embedding_wgrad_workspace_bytes(n_train, T, vocab), "ghost_embedding_wgrad: workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* w = static_cast<uint8_t*>(ws);
+  const long long seg = up256(4ll * (vocab + 1));
+  int* counts = reinterpret_cast<int*>(w);
+  int* offsets = reinterpret_cast<int*>(w + seg);
+  int* cursor = reinterpret_cast<int*>(w + 2 * seg);
+  int* perm = reinterpret_cast<int*>(w + 3 * seg);
+  const long long n_tok = static_cast<long long>(n_train) * T;
+  GB_CUDA_OK(cudaMemsetAsync(counts, 0, seg, st));
+  GB_CUDA_OK(cudaMemsetAsync(cursor, 0, seg, st));
+  int blocks = static_cast<int>((n_tok + 255) / 256);
+  if (blocks > ds->sm_count * 8) blocks = ds->sm_count * 8;
+  emb_count_kernel<<<blocks, 256, 0, st>>>(ids, n_tok, vocab, counts);
+  emb_scan_kernel<<<1, 1024, 0, st>>>(counts, vocab, offsets);
+  emb_fill_kernel<<<blocks, 256, 0, st>>>(ids, n_tok, vocab, offsets, cursor, perm);
+  if (is_f32)
+    emb_segsum_kernel<float><<<ceil_div(vocab, 8), 256, 0, st>>>(static_cast<const float*>(G), d, vocab, offsets, perm, pre_scale, divisor, accumulate, static_cast<float*>(out));
+  else
+    emb_segsum_kernel<__nv_bfloat16><<<ceil_div(vocab, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(G), d, vocab, offsets, perm, pre_scale, divisor, accumulate, static_cast<__nv_bfloat16*>(out));
+  count_launch(4);
+  return post_launch("ghost_embedding_wgrad");
+}

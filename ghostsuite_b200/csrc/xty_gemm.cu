@@ -1,0 +1,483 @@
+// xty_gemm: token-contracted outer-product GEMMs  D[m, n] = sum_rows X[row, m] * Y[row, n].
+//
+// X and Y are token-major bf16 matrices ([samples, T, cols]); the contraction runs over token rows,
+// so both operands are "MN-major" for tcgen05: a shared-memory stage holds 64 token rows, and each
+// 64-column slab of them is one TMA box (64 rows x 128 bytes, 128B swizzle).  Three uses share the
+// mainloop and differ in the epilogue:
+//
+//   kEpiAccumulate  train-gradient recovery (ghostEngines/supported_layers_grad_samplers_dotprod.py
+//                   :168 and :502): contraction over all train tokens, optionally split across
+//                   CTAs; partial tiles are added into an fp32 workspace with red.global.add.
+//   kEpiStore       per-validation-sample weight gradients V[v] written to a workspace
+//                   (per-sample form of :133-134).
+//   kEpiDot         per-train-sample weight-gradient tile formed in TMEM, dotted against the
+//                   n_val stored validation gradients in the epilogue (:135, for every validation
+//                   sample separately) and, in the same pass, added into the fp32 train-gradient
+//                   workspace -- so the per-sample gradients never reach HBM and the train
+//                   gradient costs no extra tensor work.
+//
+// Linear weights are [d_out, d_in]: X = G (out-grad), Y = A (activations).  HF Conv1D weights are
+// [d_in, d_out]: X = A, Y = G.  No transposes are materialised.
+//
+// CTA layout (192 threads, persistent): warps 0-3 epilogue, warp 4 TMA producer, warp 5 TMEM
+// allocator + MMA issuer.  128 x 256 fp32 accumulator, double-buffered in TMEM (512 columns).
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace gb {
+
+enum { kEpiAccumulate = 0, kEpiStore = 1, kEpiDot = 2 };
+
+struct XtyParams {
+  int mode;
+  int m_cols, n_cols;        // output extent (X columns, Y columns)
+  int m_tiles, n_tiles;
+  int samples;               // samples contracted separately (1 for plain train-gradient recovery)
+  int sample0;               // first sample (z coordinate offset into the tensor maps)
+  long long T;               // token rows per sample
+  int k_splits;              // kEpiAccumulate: CTAs sharing one output tile
+  int kb_per_split;          // 64-row blocks per split
+  // kEpiAccumulate / kEpiDot: fp32 [m_cols, ld_acc] accumulation workspace (may be null for Dot)
+  float* acc_ws;
+  long long ld_acc;
+  // kEpiStore / kEpiDot: validation gradients [n_val][m_cols][ld_v]
+  void* vgrad;
+  long long ld_v;
+  int v_is_f32;
+  int n_val, n_train;
+  float dot_scale;
+  float* M;                  // [n_val, n_train]
+  int* err;
+};
+
+struct XtyCfg {
+  static constexpr int BM = 128, BN = 256, BK = 64;
+  static constexpr int kStageBytes = (BM + BN) * BK * 2;   // 48 KB
+  static constexpr int kStages = 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kMaxVal = 32;
+};
+
+__device__ __forceinline__ void red_add_f32(float* addr, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(192, 1)
+xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
+                const XtyParams p) {
+  using Cfg = XtyCfg;
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, kStages = Cfg::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* acc_full = bars + 2 * kStages;     // [2]
+  uint64_t* acc_empty = acc_full + 2;          // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_mn = p.m_tiles * p.n_tiles;
+  // unit -> (tile, sample, split); sample is the fastest index so that consecutive units of a CTA
+  // neighbourhood reuse the same validation-gradient tiles from L2.
+  const long long units = static_cast<long long>(tiles_mn) * p.samples * p.k_splits;
+  const int kb_sample = static_cast<int>((p.T + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_y);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto decode = [&](long long u, int& tile, int& sample, int& kb0, int& kb1) {
+    const int inner = p.samples * p.k_splits;
+    tile = static_cast<int>(u / inner);
+    const int r = static_cast<int>(u % inner);
+    sample = r / p.k_splits;
+    const int split = r % p.k_splits;
+    kb0 = split * p.kb_per_split;
+    kb1 = kb0 + p.kb_per_split;
+    if (kb1 > kb_sample) kb1 = kb_sample;
+    if (kb0 > kb1) kb0 = kb1;
+  };
+
+  if (warp == 4) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        int tile, sample, kb0, kb1;
+        decode(u, tile, sample, kb0, kb1);
+        const int m0 = (tile / p.n_tiles) * BM;
+        const int n0 = (tile % p.n_tiles) * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 411)) { ok = false; break; }
+          uint8_t* st = smem + stage * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          const int row = kb * BK;
+          const int z = p.sample0 + sample;
+#pragma unroll
+          for (int j = 0; j < BM / 64; ++j)
+            tma_load_3d(st + j * (BK * 128), &tm_x, &full_bar[stage], m0 + j * 64, row, z);
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j)
+            tma_load_3d(st + BM * BK * 2 + j * (BK * 128), &tm_y, &full_bar[stage], n0 + j * 64, row, z);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 1, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        int tile, sample, kb0, kb1;
+        decode(u, tile, sample, kb0, kb1);
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.err, 512)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t dst = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 513)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          // MN-major: LBO = distance between 64-column slabs (one TMA box), SBO = 8 token rows
+          const uint64_t adesc = make_smem_desc_sw128(sa, BK * 128, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sa + BM * BK * 2, BK * 128, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_bf16(dst, adesc + k * (16 * 128 / 16), bdesc + k * (16 * 128 / 16), idesc,
+                      (kb == kb0 && k == 0) ? 0u : 1u);
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    for (long long u = blockIdx.x; u < units; u += gridDim.x) {
+      int tile, sample, kb0, kb1;
+      decode(u, tile, sample, kb0, kb1);
+      const int m0 = (tile / p.n_tiles) * BM;
+      const int n0 = (tile % p.n_tiles) * BN;
+      if (!mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag, p.err, 114)) break;
+      tc_fence_after_sync();
+      const int m = m0 + threadIdx.x;
+      const bool m_ok = m < p.m_cols;
+      const uint32_t t_acc = tmem_base + lane_base + acc * BN;
+      const bool empty_k = (kb0 >= kb1);   // nothing was accumulated: the tile is all zero
+
+      if (p.mode == kEpiAccumulate) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (n0 + c0 >= p.n_cols) break;
+          uint32_t r[32];
+          tmem_ld32(t_acc + c0, r);
+          tmem_ld_wait();
+          if (m_ok && !empty_k) {
+            float* dst = p.acc_ws + static_cast<long long>(m) * p.ld_acc + n0 + c0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c0 + j < p.n_cols) red_add_f32(dst + j, __uint_as_float(r[j]));
+          }
+        }
+      } else if (p.mode == kEpiStore) {
+        const long long vbase = (static_cast<long long>(sample) * p.m_cols + m) * p.ld_v;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (n0 + c0 >= p.ld_v) break;
+          uint32_t r[32];
+          tmem_ld32(t_acc + c0, r);
+          tmem_ld_wait();
+          if (m_ok) {
+            // columns in [n_cols, ld_v) are written too (their accumulators are exact zeros from
+            // the TMA zero fill) so that the vector loads of the dot epilogue never see garbage
+            if (p.v_is_f32) {
+              float* dst = static_cast<float*>(p.vgrad) + vbase + n0 + c0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + c0 + j < p.ld_v) dst[j] = empty_k ? 0.f : __uint_as_float(r[j]);
+            } else {
+              __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.vgrad) + vbase + n0 + c0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + c0 + j < p.ld_v)
+                  dst[j] = __float2bfloat16_rn(empty_k ? 0.f : __uint_as_float(r[j]));
+            }
+          }
+        }
+      } else {
+        float dots[XtyCfg::kMaxVal];
+#pragma unroll
+        for (int v = 0; v < XtyCfg::kMaxVal; ++v) dots[v] = 0.f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (n0 + c0 >= p.n_cols) break;
+          uint32_t r[32];
+          tmem_ld32(t_acc + c0, r);
+          tmem_ld_wait();
+          if (m_ok && !empty_k) {
+            const int ncol = min(32, p.n_cols - (n0 + c0));
+            if (p.acc_ws) {
+              float* dst = p.acc_ws + static_cast<long long>(m) * p.ld_acc + n0 + c0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncol) red_add_f32(dst + j, __uint_as_float(r[j]));
+            }
+#pragma unroll
+            for (int v = 0; v < XtyCfg::kMaxVal; ++v) {
+              if (v >= p.n_val) break;
+              const long long vbase = (static_cast<long long>(v) * p.m_cols + m) * p.ld_v + n0 + c0;
+              float s = 0.f;
+              if (p.v_is_f32) {
+                const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.vgrad) + vbase);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  if (q * 4 < ncol) {   // ld_v and n_cols padding keep whole float4s in bounds
+                    const float4 f = __ldg(src + q);
+                    s = fmaf(f.x, __uint_as_float(r[4 * q + 0]), s);
+                    s = fmaf(f.y, __uint_as_float(r[4 * q + 1]), s);
+                    s = fmaf(f.z, __uint_as_float(r[4 * q + 2]), s);
+                    s = fmaf(f.w, __uint_as_float(r[4 * q + 3]), s);
+                  }
+                }
+              } else {
+                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.vgrad) + vbase);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  if (q * 8 < ncol) {
+                    const uint4 w = __ldg(src + q);
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float lo = __uint_as_float(ww[e] << 16);
+                      const float hi = __uint_as_float(ww[e] & 0xffff0000u);
+                      s = fmaf(lo, __uint_as_float(r[8 * q + 2 * e + 0]), s);
+                      s = fmaf(hi, __uint_as_float(r[8 * q + 2 * e + 1]), s);
+                    }
+                  }
+                }
+              }
+              dots[v] += s;
+            }
+          }
+        }
+        // hand the accumulator back, then reduce the n_val partial dots across the warp
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+#pragma unroll
+        for (int v = 0; v < XtyCfg::kMaxVal; ++v) {
+          if (v >= p.n_val) break;
+          float s = dots[v];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          if (lane == 0 && s != 0.f)
+            atomicAdd(&p.M[static_cast<long long>(v) * p.n_train + sample], s * p.dot_scale);
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// finalize: out = (accumulate ? out : 0) + scale * ws, cast to the parameter dtype
+template <typename OutT>
+__global__ void xty_finalize_kernel(const float* __restrict__ ws, long long ld_ws, OutT* __restrict__ out,
+                                    int rows, int cols, float scale, int accumulate) {
+  const long long n = static_cast<long long>(rows) * cols;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / cols), c = static_cast<int>(i % cols);
+    float v = ws[static_cast<long long>(r) * ld_ws + c] * scale;
+    if (accumulate) v += static_cast<float>(out[i]);
+    out[i] = static_cast<OutT>(v);
+  }
+}
+
+static int launch_xty(const CUtensorMap& tx, const CUtensorMap& ty, const XtyParams& p,
+                      const DeviceState* ds, cudaStream_t st) {
+  static bool attr_set[64] = {};
+  if (!attr_set[ds->device]) {
+    GB_CUDA_OK(cudaFuncSetAttribute(xty_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    XtyCfg::kSmemBytes));
+    attr_set[ds->device] = true;
+  }
+  const long long units = static_cast<long long>(p.m_tiles) * p.n_tiles * p.samples * p.k_splits;
+  const int grid = static_cast<int>(units < ds->sm_count ? units : ds->sm_count);
+  xty_gemm_kernel<<<grid, 192, XtyCfg::kSmemBytes, st>>>(tx, ty, p);
+  count_launch();
+  return post_launch("xty_gemm_kernel");
+}
+
+int finalize_xty(const float* ws, long long ld_ws, void* out, int out_is_f32, int rows, int cols,
+                 float scale, int accumulate, cudaStream_t st) {
+  const long long n = static_cast<long long>(rows) * cols;
+  const int grid = static_cast<int>(n / 256 + 1 < 148 * 8 ? n / 256 + 1 : 148 * 8);
+  if (out_is_f32)
+    xty_finalize_kernel<float><<<grid, 256, 0, st>>>(ws, ld_ws, static_cast<float*>(out), rows, cols, scale, accumulate);
+  else
+    xty_finalize_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(ws, ld_ws, static_cast<__nv_bfloat16*>(out), rows, cols, scale, accumulate);
+  count_launch();
+  return post_launch("xty_finalize_kernel");
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
+
+extern "C" long long ghost_wgrad_workspace_bytes(int m_cols, int n_cols) {
+  return static_cast<long long>(m_cols) * round_up(n_cols, 4) * 4;
+}
+
+// D[m_cols, n_cols] = scale * sum_{rows < n_rows} X[row, :]^T Y[row, :]
+extern "C" int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, int m_cols, int n_cols,
+                                long long ldx, long long ldy, float scale, int accumulate, void* out,
+                                int out_is_f32, void* ws, long long ws_bytes, void* stream) {
+  const DeviceState* ds = device_state();
+  if (!ds) return GHOST_ERR_DEVICE;
+  GB_REQUIRE(X && Y && out && ws, "ghost_wgrad_bf16: null pointer");
+  GB_REQUIRE(n_rows > 0 && m_cols > 0 && n_cols > 0, "ghost_wgrad_bf16: empty dimension");
+  GB_REQUIRE(n_rows < (1ll << 31) - 64, "ghost_wgrad_bf16: more than 2^31 token rows");
+  GB_REQUIRE(ws_bytes >= ghost_wgrad_workspace_bytes(m_cols, n_cols), "ghost_wgrad_bf16: workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  XtyParams p = {};
+  p.mode = kEpiAccumulate;
+  p.m_cols = m_cols;
+  p.n_cols = n_cols;
+  p.m_tiles = ceil_div(m_cols, XtyCfg::BM);
+  p.n_tiles = ceil_div(n_cols, XtyCfg::BN);
+  p.samples = 1;
+  p.sample0 = 0;
+  p.T = n_rows;
+  const int kb = ceil_div(n_rows, XtyCfg::BK);
+  const int tiles = p.m_tiles * p.n_tiles;
+  int splits = 1;
+  if (tiles < ds->sm_count) splits = (2 * ds->sm_count + tiles - 1) / tiles;
+  if (splits > kb) splits = kb;
+  p.kb_per_split = ceil_div(kb, splits);
+  p.k_splits = ceil_div(kb, p.kb_per_split);
+  p.acc_ws = static_cast<float*>(ws);
+  p.ld_acc = round_up(n_cols, 4);
+  p.err = ds->err_word;
+  CUtensorMap tx, ty;
+  int rc;
+  if ((rc = make_tmap_bf16_3d(&tx, X, 1, n_rows, m_cols, ldx, XtyCfg::BK)) != GHOST_OK) return rc;
+  if ((rc = make_tmap_bf16_3d(&ty, Y, 1, n_rows, n_cols, ldy, XtyCfg::BK)) != GHOST_OK) return rc;
+  GB_CUDA_OK(cudaMemsetAsync(ws, 0, static_cast<size_t>(m_cols) * p.ld_acc * 4, st));
+  if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+  return finalize_xty(p.acc_ws, p.ld_acc, out, out_is_f32, m_cols, n_cols, scale, accumulate, st);
+}
+
+extern "C" long long ghost_persample_workspace_bytes(int n_val, int m_cols, int n_cols, int v_is_f32) {
+  const long long ldv = round_up(n_cols, 8);
+  return round_up(static_cast<long long>(m_cols) * round_up(n_cols, 4) * 4, 256) +
+         static_cast<long long>(n_val) * m_cols * ldv * (v_is_f32 ? 4 : 2);
+}
+
+// Per-sample-gradient path.  X, Y: [n_train + n_val, T, cols] (train first).  Produces
+// M[v, b] = dot_scale * <X_v^T Y_v, X_b^T Y_b> and, if grad_out != null, the train gradient
+// grad_scale * sum_b X_b^T Y_b (written or accumulated, cast to the parameter dtype).
+extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_train, int n_val, long long T,
+                                        int m_cols, int n_cols, long long ldx, long long ldy,
+                                        float dot_scale, float* M_out, int v_is_f32, void* grad_out,
+                                        int grad_is_f32, float grad_scale, int grad_accumulate,
+                                        void* ws, long long ws_bytes, void* stream) {
+  const DeviceState* ds = device_state();
+  if (!ds) return GHOST_ERR_DEVICE;
+  GB_REQUIRE(X && Y && M_out && ws, "ghost_persample_dot_bf16: null pointer");
+  GB_REQUIRE(n_train > 0, "No training samples to compute dot product, check batch sizes.");
+  GB_REQUIRE(n_val > 0 && T > 0 && m_cols > 0 && n_cols > 0, "ghost_persample_dot_bf16: empty dimension");
+  GB_REQUIRE(n_val <= XtyCfg::kMaxVal, "ghost_persample_dot_bf16: at most %d validation samples per call", XtyCfg::kMaxVal);
+  GB_REQUIRE(T < (1ll << 31) - 64, "ghost_persample_dot_bf16: T too large");
+  GB_REQUIRE(ws_bytes >= ghost_persample_workspace_bytes(n_val, m_cols, n_cols, v_is_f32),
+             "ghost_persample_dot_bf16: workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long ld_acc = round_up(n_cols, 4);
+  const long long acc_bytes = round_up(static_cast<long long>(m_cols) * ld_acc * 4, 256);
+  XtyParams p = {};
+  p.m_cols = m_cols;
+  p.n_cols = n_cols;
+  p.m_tiles = ceil_div(m_cols, XtyCfg::BM);
+  p.n_tiles = ceil_div(n_cols, XtyCfg::BN);
+  p.T = T;
+  p.k_splits = 1;
+  p.kb_per_split = ceil_div(T, XtyCfg::BK);
+  p.vgrad = static_cast<uint8_t*>(ws) + acc_bytes;
+  p.ld_v = round_up(n_cols, 8);
+  p.v_is_f32 = v_is_f32;
+  p.n_val = n_val;
+  p.n_train = n_train;
+  p.dot_scale = dot_scale;
+  p.M = M_out;
+  p.err = ds->err_word;
+  CUtensorMap tx, ty;
+  int rc;
+  const long long N = static_cast<long long>(n_train) + n_val;
+  if ((rc = make_tmap_bf16_3d(&tx, X, N, T, m_cols, ldx, XtyCfg::BK)) != GHOST_OK) return rc;
+  if ((rc = make_tmap_bf16_3d(&ty, Y, N, T, n_cols, ldy, XtyCfg::BK)) != GHOST_OK) return rc;
+  GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
+  // pass 1: validation gradients
+  p.mode = kEpiStore;
+  p.samples = n_val;
+  p.sample0 = n_train;
+  if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+  // pass 2: train samples, dots (+ train gradient)
+  p.mode = kEpiDot;
+  p.samples = n_train;
+  p.sample0 = 0;
+  if (grad_out) {
+    p.acc_ws = static_cast<float*>(ws);
+    p.ld_acc = ld_acc;
+    GB_CUDA_OK(cudaMemsetAsync(ws, 0, static_cast<size_t>(m_cols) * ld_acc * 4, st));
+  }
+  if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+  if (grad_out)
+    return finalize_xty(p.acc_ws, ld_acc, grad_out, grad_is_f32, m_cols, n_cols, grad_scale, grad_accumulate, st);
+  return GHOST_OK;
+}

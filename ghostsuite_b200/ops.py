@@ -1,0 +1,460 @@
+"""Kernel entry points on torch CUDA tensors.
+
+Each function validates shapes, hands raw device pointers to ``libghost_b200.so`` on torch's current
+stream, and returns torch tensors.  torch is used for memory and stream lookup only; the
+arithmetic runs in the library's kernels.  Scratch memory comes from a grow-only arena per
+(device, stream), so no allocation happens in steady state and nothing is freed while kernels that
+use it may still be queued.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_BF16 = torch.bfloat16
+_F32 = torch.float32
+
+_arenas: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("ghostsuite_b200 kernels need CUDA tensors (no CPU fallback exists)")
+
+
+class _Arena:
+    """Bump allocator over one cached uint8 tensor; reset at the start of every public op."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.key = (device.index if device.index is not None else torch.cuda.current_device(),
+                    _stream_ptr())
+        self.requests = []
+
+    def plan(self, nbytes: int) -> int:
+        """Reserve nbytes (256-byte aligned); returns the offset."""
+        off = sum(self.requests)
+        self.requests.append((int(nbytes) + 255) // 256 * 256)
+        return off
+
+    def commit(self) -> int:
+        total = sum(self.requests) + 256
+        buf = _arenas.get(self.key)
+        if buf is None or buf.numel() < total:
+            # grow-only; the old buffer stays referenced by torch's caching allocator semantics
+            # (stream-ordered reuse), so queued kernels that still read it are safe
+            buf = torch.empty(max(total, 1 << 20), dtype=torch.uint8, device=self.device)
+            _arenas[self.key] = buf
+        base = buf.data_ptr()
+        return (base + 255) // 256 * 256
+
+
+def _dt_flag(t: torch.Tensor) -> int:
+    if t.dtype == _F32:
+        return 1
+    if t.dtype == _BF16:
+        return 0
+    raise ValueError(f"unsupported dtype {t.dtype}: the kernels take float32 or bfloat16")
+
+
+def _as3d(x: torch.Tensor) -> torch.Tensor:
+    """[N, d] -> [N, 1, d]; [N, ..., d] -> [N, T, d] (contiguous)."""
+    if x.dim() <= 2:
+        x = x.unsqueeze(1)
+    else:
+        x = x.reshape(x.shape[0], -1, x.shape[-1])
+    return x.contiguous()
+
+
+def _tma_ready(x: torch.Tensor) -> bool:
+    return x.dtype == _BF16 and x.shape[-1] % 8 == 0 and x.data_ptr() % 16 == 0
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+def _cast(lib, src: torch.Tensor, samples: int, T: int, dst_ptr: int, ld_dst: int, cpad: int,
+          kinds: Tuple[int, ...], row_stack: bool) -> None:
+    k = tuple(kinds) + (0,) * (3 - len(kinds))
+    _lib.check(lib.ghost_cast_split_bf16(src.data_ptr(), _dt_flag(src), samples, T, src.shape[-1],
+                                         src.shape[-1], dst_ptr, ld_dst, cpad, len(kinds),
+                                         k[0], k[1], k[2], 1 if row_stack else 0, _stream_ptr()))
+
+
+# hi/lo layouts of an fp32 operand pair so that  sum_k L[k] R[k] = hi*hi + lo*hi + hi*lo
+_SPLIT_LEFT = (0, 1, 0)
+_SPLIT_RIGHT = (0, 0, 1)
+
+
+# --------------------------------------------------------------------------------------------
+# Linear / Conv1D weight dot product: Gram path
+# --------------------------------------------------------------------------------------------
+def gram_dot(A: torch.Tensor, G: torch.Tensor, n_val: int, round_mode: int = 0,
+             scale: float = 1.0) -> torch.Tensor:
+    """Full ``[n_val, n_train]`` dot-product matrix through the fused Gram kernel.
+
+    bf16 inputs are used as they are (copied only if their feature size is not a multiple of 8);
+    fp32 inputs are split into bf16 hi/lo parts so the result keeps fp32-class accuracy.
+    """
+    lib = _lib.load()
+    _require_cuda(A, G)
+    A, G = _as3d(A), _as3d(G)
+    N, T, d = A.shape
+    p = G.shape[-1]
+    n_train = N - n_val
+    if n_train <= 0:
+        raise ValueError("No training samples to compute dot product, check batch sizes.")
+    if n_val <= 0:
+        raise ValueError("gram_dot needs at least one validation sample")
+    if G.shape[0] != N or G.shape[1] != T:
+        raise ValueError(f"activation {tuple(A.shape)} and out-grad {tuple(G.shape)} disagree")
+    M = torch.empty((n_val, n_train), dtype=_F32, device=A.device)
+    arena = _Arena(A.device)
+    ops = []
+    for x in (A, G):
+        f = x.shape[-1]
+        if x.dtype == _F32:
+            cp = _pad8(f)
+            off_t = arena.plan(n_train * T * 3 * cp * 2)
+            off_v = arena.plan(n_val * T * 3 * cp * 2)
+            ops.append(("split", x, cp, off_t, off_v))
+        elif _tma_ready(x):
+            ops.append(("asis", x, f, 0, 0))
+        else:
+            cp = _pad8(f)
+            off_t = arena.plan(N * T * cp * 2)
+            ops.append(("copy", x, cp, off_t, 0))
+    base = arena.commit()
+    ptrs = []
+    for kind, x, cp, off_t, off_v in ops:
+        if kind == "asis":
+            pt = x.data_ptr()
+            pv = pt + n_train * T * x.shape[-1] * 2
+            ptrs.append((pt, pv, x.shape[-1], x.shape[-1], x.shape[-1]))
+        elif kind == "copy":
+            _cast(lib, x, N, T, base + off_t, cp, cp, (0,), False)
+            pt = base + off_t
+            ptrs.append((pt, pt + n_train * T * cp * 2, cp, cp, cp))
+        else:
+            _cast(lib, x[:n_train], n_train, T, base + off_t, 3 * cp, cp, _SPLIT_LEFT, False)
+            _cast(lib, x[n_train:], n_val, T, base + off_v, 3 * cp, cp, _SPLIT_RIGHT, False)
+            ptrs.append((base + off_t, base + off_v, 3 * cp, 3 * cp, 3 * cp))
+    (at, av, ka, ld_at, ld_av), (gt, gv, kg, ld_gt, ld_gv) = ptrs
+    _lib.check(lib.ghost_gram_dot_bf16(at, av, gt, gv, n_train, n_val, T, ka, kg, ld_at, ld_av,
+                                       ld_gt, ld_gv, int(round_mode), float(scale), M.data_ptr(),
+                                       _stream_ptr()))
+    return M
+
+
+# --------------------------------------------------------------------------------------------
+# train-gradient recovery and the per-sample-gradient path
+# --------------------------------------------------------------------------------------------
+def _xty_operands(lib, arena: _Arena, X: torch.Tensor, Y: torch.Tensor, samples: int, T: int):
+    """Plan bf16 operands for the token-contracted GEMMs.  Returns a closure that materialises them
+    after ``arena.commit()`` and yields (x_ptr, y_ptr, ldx, ldy, T_eff)."""
+    split = X.dtype == _F32 or Y.dtype == _F32
+    plans = []
+    for x, kinds in ((X, _SPLIT_LEFT), (Y, _SPLIT_RIGHT)):
+        f = x.shape[-1]
+        cp = _pad8(f)
+        if split:
+            plans.append(("split", x, cp, arena.plan(samples * 3 * T * cp * 2), kinds))
+        elif _tma_ready(x):
+            plans.append(("asis", x, f, 0, kinds))
+        else:
+            plans.append(("copy", x, cp, arena.plan(samples * T * cp * 2), kinds))
+
+    def materialise(base: int):
+        out = []
+        for kind, x, cp, off, kinds in plans:
+            if kind == "asis":
+                out.append((x.data_ptr(), x.shape[-1]))
+            elif kind == "copy":
+                _cast(lib, x, samples, T, base + off, cp, cp, (0,), True)
+                out.append((base + off, cp))
+            else:
+                _cast(lib, x, samples, T, base + off, cp, cp, kinds, True)
+                out.append((base + off, cp))
+        return out[0][0], out[1][0], out[0][1], out[1][1], (3 * T if split else T)
+
+    return materialise, split
+
+
+def wgrad(X: torch.Tensor, Y: torch.Tensor, scale: float, out_dtype: torch.dtype,
+          out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """``scale * sum over all rows of X^T Y`` -> ``[X.shape[-1], Y.shape[-1]]`` in ``out_dtype``.
+
+    ``X``/``Y`` are ``[samples, T, cols]`` (train samples only).
+    """
+    lib = _lib.load()
+    _require_cuda(X, Y)
+    X, Y = _as3d(X), _as3d(Y)
+    S, T, m = X.shape
+    n = Y.shape[-1]
+    if Y.shape[0] != S or Y.shape[1] != T:
+        raise ValueError("wgrad operands disagree on the token layout")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=X.device)
+        accumulate = False
+    arena = _Arena(X.device)
+    ws_bytes = int(lib.ghost_wgrad_workspace_bytes(m, n))
+    off_ws = arena.plan(ws_bytes)
+    mat, _ = _xty_operands(lib, arena, X, Y, S, T)
+    base = arena.commit()
+    xp, yp, ldx, ldy, T_eff = mat(base)
+    _lib.check(lib.ghost_wgrad_bf16(xp, yp, S * T_eff, m, n, ldx, ldy, float(scale),
+                                    1 if accumulate else 0, out.data_ptr(), _dt_flag(out),
+                                    base + off_ws, ws_bytes, _stream_ptr()))
+    return out
+
+
+MAX_VAL_PER_CALL = 32
+
+
+def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float = 1.0,
+                  want_grad: bool = False, grad_scale: float = 1.0,
+                  grad_dtype: Optional[torch.dtype] = None
+                  ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Dot-product matrix through explicit per-sample weight gradients kept in tensor memory.
+
+    ``X``/``Y``: ``[N, T, cols]``, train first.  Returns ``(M[n_val, n_train], train_grad or None)``
+    with ``train_grad = grad_scale * sum_b X_b^T Y_b`` of shape ``[X cols, Y cols]``.
+    """
+    lib = _lib.load()
+    _require_cuda(X, Y)
+    X, Y = _as3d(X), _as3d(Y)
+    N, T, m = X.shape
+    n = Y.shape[-1]
+    n_train = N - n_val
+    if n_train <= 0:
+        raise ValueError("No training samples to compute dot product, check batch sizes.")
+    if n_val <= 0:
+        raise ValueError("persample_dot needs at least one validation sample")
+    if Y.shape[0] != N or Y.shape[1] != T:
+        raise ValueError("persample_dot operands disagree on the token layout")
+    M = torch.empty((n_val, n_train), dtype=_F32, device=X.device)
+    grad = None
+    if want_grad:
+        grad = torch.empty((m, n), dtype=grad_dtype or X.dtype, device=X.device)
+    for v0 in range(0, n_val, MAX_VAL_PER_CALL):
+        v1 = min(n_val, v0 + MAX_VAL_PER_CALL)
+        nv = v1 - v0
+        if v0 == 0 and v1 == n_val:
+            Xc, Yc = X, Y
+        else:
+            Xc = torch.cat((X[:n_train], X[n_train + v0:n_train + v1]))
+            Yc = torch.cat((Y[:n_train], Y[n_train + v0:n_train + v1]))
+        arena = _Arena(X.device)
+        mat, split = _xty_operands(lib, arena, Xc, Yc, n_train + nv, T)
+        v_f32 = 1 if split else 0
+        ws_bytes = int(lib.ghost_persample_workspace_bytes(nv, m, n, v_f32))
+        off_ws = arena.plan(ws_bytes)
+        base = arena.commit()
+        xp, yp, ldx, ldy, T_eff = mat(base)
+        do_grad = want_grad and v0 == 0
+        Mc = M if (v0 == 0 and v1 == n_val) else torch.empty((nv, n_train), dtype=_F32, device=X.device)
+        _lib.check(lib.ghost_persample_dot_bf16(
+            xp, yp, n_train, nv, T_eff, m, n, ldx, ldy, float(dot_scale), Mc.data_ptr(), v_f32,
+            grad.data_ptr() if do_grad else None, _dt_flag(grad) if do_grad else 0,
+            float(grad_scale), 0, base + off_ws, ws_bytes, _stream_ptr()))
+        if Mc is not M:
+            M[v0:v1].copy_(Mc)
+    return M, grad
+
+
+# --------------------------------------------------------------------------------------------
+# bias / LayerNorm / small reductions
+# --------------------------------------------------------------------------------------------
+def colsum(G: torch.Tensor) -> torch.Tensor:
+    """Per-sample column sums over tokens: ``[N, T, p] -> [N, p]`` float32."""
+    lib = _lib.load()
+    _require_cuda(G)
+    G = _as3d(G)
+    N, T, p = G.shape
+    out = torch.empty((N, p), dtype=_F32, device=G.device)
+    _lib.check(lib.ghost_colsum(G.data_ptr(), _dt_flag(G), N, T, p, p, out.data_ptr(), _stream_ptr()))
+    return out
+
+
+def small_gram(X: torch.Tensor, n_val: int, scale: float = 1.0) -> torch.Tensor:
+    """``M[v, b] = scale * <X[n_train + v], X[b]>`` for per-sample float32 vectors ``X[N, F]``."""
+    lib = _lib.load()
+    _require_cuda(X)
+    if X.dtype != _F32 or X.dim() != 2 or not X.is_contiguous():
+        raise ValueError("small_gram takes a contiguous float32 [N, F] tensor")
+    n_train = X.shape[0] - n_val
+    if n_train <= 0:
+        raise ValueError("No training samples to compute dot product, check batch sizes.")
+    M = torch.empty((n_val, n_train), dtype=_F32, device=X.device)
+    _lib.check(lib.ghost_small_gram_f32(X.data_ptr(), n_train, n_val, X.shape[1], float(scale),
+                                        M.data_ptr(), _stream_ptr()))
+    return M
+
+
+def rows_sum(X: torch.Tensor, n_rows: int, scale: float, out_dtype: torch.dtype,
+             out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """``scale * X[:n_rows].sum(0)`` cast to ``out_dtype`` (optionally accumulated into ``out``)."""
+    lib = _lib.load()
+    _require_cuda(X)
+    if X.dtype != _F32 or X.dim() != 2 or not X.is_contiguous():
+        raise ValueError("rows_sum takes a contiguous float32 [N, F] tensor")
+    if out is None:
+        out = torch.empty((X.shape[1],), dtype=out_dtype, device=X.device)
+        accumulate = False
+    _lib.check(lib.ghost_rows_sum(X.data_ptr(), int(n_rows), X.shape[1], float(scale), out.data_ptr(),
+                                  _dt_flag(out), 1 if accumulate else 0, _stream_ptr()))
+    return out
+
+
+def layernorm_persample(A: torch.Tensor, G: torch.Tensor, eps: float
+                        ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-sample LayerNorm gamma/beta gradients ``([N, F], [N, F])`` float32 in one pass."""
+    lib = _lib.load()
+    _require_cuda(A, G)
+    if A.dtype != G.dtype:
+        common = torch.promote_types(A.dtype, G.dtype)
+        A, G = A.to(common), G.to(common)
+    A, G = _as3d(A), _as3d(G)
+    N, T, F = A.shape
+    if G.shape != A.shape:
+        raise ValueError("LayerNorm input and out-grad shapes differ")
+    gw = torch.empty((N, F), dtype=_F32, device=A.device)
+    gb = torch.empty((N, F), dtype=_F32, device=A.device)
+    _lib.check(lib.ghost_layernorm_persample(A.data_ptr(), G.data_ptr(), _dt_flag(A), N, T, F,
+                                             float(eps), gw.data_ptr(), gb.data_ptr(), _stream_ptr()))
+    return gw, gb
+
+
+# --------------------------------------------------------------------------------------------
+# Embedding
+# --------------------------------------------------------------------------------------------
+def _ids2d(ids: torch.Tensor) -> torch.Tensor:
+    ids = ids.reshape(ids.shape[0], -1)
+    if ids.dtype != torch.int64:
+        ids = ids.long()
+    return ids.contiguous()
+
+
+def embedding_dot(ids: torch.Tensor, G: torch.Tensor, n_val: int, vocab: int,
+                  scale: float = 1.0) -> torch.Tensor:
+    lib = _lib.load()
+    _require_cuda(ids, G)
+    ids = _ids2d(ids)
+    G = _as3d(G)
+    N, T, d = G.shape
+    if ids.shape[0] != N or ids.shape[1] != T:
+        raise ValueError("embedding ids and out-grad disagree on [batch, tokens]")
+    n_train = N - n_val
+    if n_train <= 0:
+        raise ValueError("No training samples to compute dot product, check batch sizes.")
+    M = torch.empty((n_val, n_train), dtype=_F32, device=G.device)
+    arena = _Arena(G.device)
+    ws_bytes = int(lib.ghost_embedding_dot_workspace_bytes(n_val, T, vocab))
+    off = arena.plan(ws_bytes)
+    base = arena.commit()
+    _lib.check(lib.ghost_embedding_dot(ids.data_ptr(), G.data_ptr(), _dt_flag(G), n_train, n_val, T,
+                                       d, int(vocab), float(scale), M.data_ptr(), base + off,
+                                       ws_bytes, _stream_ptr()))
+    return M
+
+
+def embedding_wgrad(ids: torch.Tensor, G: torch.Tensor, n_train: int, vocab: int, pre_scale: float,
+                    divisor: float, out: Optional[torch.Tensor] = None,
+                    accumulate: bool = False) -> torch.Tensor:
+    """Averaged train gradient of an embedding table ``[vocab, d]`` in the dtype of ``G``."""
+    lib = _lib.load()
+    _require_cuda(ids, G)
+    ids = _ids2d(ids)
+    G = _as3d(G)
+    N, T, d = G.shape
+    if out is None:
+        out = torch.empty((vocab, d), dtype=G.dtype, device=G.device)
+        accumulate = False
+    elif out.dtype != G.dtype:
+        raise ValueError("embedding_wgrad output must have the dtype of the out-grad")
+    arena = _Arena(G.device)
+    ws_bytes = int(lib.ghost_embedding_wgrad_workspace_bytes(n_train, T, vocab))
+    off = arena.plan(ws_bytes)
+    base = arena.commit()
+    _lib.check(lib.ghost_embedding_wgrad(ids.data_ptr(), G.data_ptr(), _dt_flag(G), n_train, T, d,
+                                         int(vocab), float(pre_scale), float(divisor),
+                                         1 if accumulate else 0, out.data_ptr(), base + off,
+                                         ws_bytes, _stream_ptr()))
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# GradProj
+# --------------------------------------------------------------------------------------------
+def prepare_projection(P: torch.Tensor, split: bool) -> torch.Tensor:
+    """bf16 copy of a projection matrix ``[k, n]`` laid out for the kernel: columns padded to a
+    multiple of 8; for fp32 models the hi/lo split matching ``_SPLIT_RIGHT``."""
+    lib = _lib.load()
+    _require_cuda(P)
+    P = P.contiguous()
+    k, n = P.shape
+    cp = _pad8(n)
+    parts = _SPLIT_RIGHT if split else (0,)
+    out = torch.empty((k, len(parts) * cp), dtype=_BF16, device=P.device)
+    _cast(lib, P, 1, k, out.data_ptr(), len(parts) * cp, cp, parts, False)
+    return out
+
+
+def gradproj_dense(G: torch.Tensor, A: torch.Tensor, P_r: torch.Tensor, P_c: torch.Tensor,
+                   k_r: int, k_c: int, scale: float, out: torch.Tensor) -> torch.Tensor:
+    """``out[b] = scale * (G_b P_r^T)^T (A_b P_c^T)`` written into ``out`` (``[B, >= k_r*k_c]`` fp32,
+    possibly a column slice of a wider row-major buffer).  ``P_r``/``P_c`` come from
+    :func:`prepare_projection` (split layout iff the activations are fp32)."""
+    lib = _lib.load()
+    _require_cuda(G, A, P_r, P_c, out)
+    G, A = _as3d(G), _as3d(A)
+    B, T, n_r = G.shape
+    n_c = A.shape[-1]
+    if A.shape[0] != B or A.shape[1] != T:
+        raise RuntimeError("Batch size mismatch between activations and output gradients")
+    if out.dtype != _F32 or out.dim() != 2 or out.shape[0] != B or out.stride(1) != 1 \
+            or out.shape[1] < k_r * k_c:
+        raise ValueError("gradproj output must be a float32 [B, >= k_r*k_c] row-major view")
+    split = G.dtype == _F32 or A.dtype == _F32
+    arena = _Arena(G.device)
+    plans = []
+    for x in (G, A):
+        cp = _pad8(x.shape[-1])
+        if split:
+            plans.append(("split", x, cp, arena.plan(B * T * 3 * cp * 2)))
+        elif _tma_ready(x):
+            plans.append(("asis", x, x.shape[-1], 0))
+        else:
+            plans.append(("copy", x, cp, arena.plan(B * T * cp * 2)))
+    base = arena.commit()
+    ptrs = []
+    for kind, x, cp, off in plans:
+        if kind == "asis":
+            ptrs.append((x.data_ptr(), cp, cp))
+        elif kind == "copy":
+            _cast(lib, x, B, T, base + off, cp, cp, (0,), False)
+            ptrs.append((base + off, cp, cp))
+        else:
+            _cast(lib, x, B, T, base + off, 3 * cp, cp, _SPLIT_LEFT, False)
+            ptrs.append((base + off, 3 * cp, 3 * cp))
+    (gp, kr_len, ldg), (ap, kc_len, lda) = ptrs
+    if P_r.shape[1] != kr_len or P_c.shape[1] != kc_len:
+        raise ValueError("projection matrices were prepared for a different dtype/feature size")
+    _lib.check(lib.ghost_gradproj_dense_bf16(gp, ap, B, T, kr_len, kc_len, ldg, lda, P_r.data_ptr(),
+                                             P_c.data_ptr(), int(k_r), int(k_c), P_r.shape[1],
+                                             P_c.shape[1], float(scale), out.data_ptr(),
+                                             out.stride(0), _stream_ptr()))
+    return out
+
+
+def launch_count() -> int:
+    return _lib.launch_count()

@@ -1,0 +1,155 @@
+/*
+ * ghost_b200.h -- C ABI of libghost_b200.so: the per-sample-gradient ("ghost") layer math of
+ * GhostSuite as hand-written sm_100a CUDA kernels.
+ *
+ * Conventions
+ *   - Every function returns an int status: GHOST_OK (0) or a negative GHOST_ERR_* code;
+ *     ghost_last_error() returns a thread-local message for the last failure.  Nothing aborts
+ *     and nothing falls back to another implementation: an unsupported shape, dtype or GPU is an
+ *     error.
+ *   - All data pointers are DEVICE pointers owned by the caller (inputs, outputs, workspaces).
+ *     The library never allocates device memory.  `stream` is a cudaStream_t passed as void*;
+ *     work is enqueued on it and no call synchronises the device, except ghost_poll_kernel_error.
+ *   - Batch layout: train samples first, validation samples last along the leading dimension
+ *     (GhostSuite: ghostEngines/engine_manager.py:201-202).
+ *   - Sizes are in elements, pitches ("ld") in elements of the pointed-to type.
+ *   - bf16 operands that feed TMA need a 16-byte aligned base and a pitch that is a multiple of
+ *     8 elements; ghost_cast_split_bf16 produces such copies from any fp32 / bf16 tensor.
+ *   - Dot-product outputs are always the full matrix M[n_val, n_train] (row-major fp32);
+ *     GhostSuite's grad_dot_prod vector is its column sum over the validation samples.
+ *
+ * "Replaces" comments cite the GhostSuite source (file:line) whose computation the entry point
+ * takes over.
+ */
+#ifndef GHOST_B200_H_
+#define GHOST_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  GHOST_OK = 0,
+  GHOST_ERR_INVALID = -1,        /* bad argument (the Python layer raises ValueError) */
+  GHOST_ERR_CUDA = -2,           /* a CUDA runtime / driver call failed */
+  GHOST_ERR_DEVICE = -3,         /* current device is not sm_100 */
+  GHOST_ERR_KERNEL_TIMEOUT = -4  /* a kernel gave up a bounded wait (see ghost_poll_kernel_error) */
+};
+
+/* ---- library / device ---------------------------------------------------------------------- */
+const char* ghost_version(void);
+const char* ghost_last_error(void);
+/* GHOST_OK iff the current CUDA device is a B200-class (sm_100) GPU. */
+int ghost_device_check(void);
+int ghost_sm_count(void);
+/* Number of kernels this library has launched in this process (all threads, all devices). */
+long long ghost_launch_count(void);
+/* Reads (synchronously) the per-device word that kernels set when a bounded mbarrier wait ran out.
+ * Returns GHOST_OK or GHOST_ERR_KERNEL_TIMEOUT; `clear` resets the word. */
+int ghost_poll_kernel_error(int clear);
+
+/* ---- operand preparation --------------------------------------------------------------------- */
+/* dst (bf16) <- src (fp32 if src_is_f32 else bf16), rows = samples * T, zero-padded to `cpad`
+ * columns, written `parts` (1..3) times.  kind_i = 0 writes bf16(x); kind_i = 1 writes the residual
+ * bf16(x - bf16(x)), so that fp32 inputs can be contracted on the bf16 tensor pipe with fp32-class
+ * accuracy (hi*hi + lo*hi + hi*lo).  row_stack = 0: parts side by side along columns
+ * (ld_dst >= parts * cpad); row_stack = 1: parts stacked along rows inside each sample, i.e. dst is
+ * [samples, parts * T, cpad].
+ * Replaces the .to(torch.bfloat16) casts of
+ * ghostEngines/supported_layers_grad_samplers_dotprod.py:92-93, 396-397. */
+int ghost_cast_split_bf16(const void* src, int src_is_f32, long long samples, long long T, int cols,
+                          long long ld_src, void* dst, long long ld_dst, int cpad, int parts,
+                          int kind0, int kind1, int kind2, int row_stack, void* stream);
+
+/* ---- Linear / Conv1D weight dot product, Gram ("ghost") path --------------------------------- */
+/* M[v,b] = scale * sum_{t in b, s in v} (a_train[t] . a_val[s]) * (g_train[t] . g_val[s]).
+ * a_*: [n_* * T, ka] bf16, g_*: [n_* * T, kg] bf16.  round_mode 0: fp32 Gram entries multiplied in
+ * fp32; round_mode 1: Gram entries and their product rounded to bf16 as GhostSuite does.
+ * One fused tcgen05/TMEM kernel; the Gram matrices are never written to memory.
+ * Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:119-130 (Linear) and :416-437
+ * (Conv1D), per validation sample. */
+int ghost_gram_dot_bf16(const void* a_train, const void* a_val, const void* g_train,
+                        const void* g_val, int n_train, int n_val, long long T, int ka, int kg,
+                        long long ld_at, long long ld_av, long long ld_gt, long long ld_gv,
+                        int round_mode, float scale, float* M_out, void* stream);
+
+/* ---- train-gradient recovery ------------------------------------------------------------------- */
+/* out[m_cols, n_cols] (= or +=) scale * sum_{row < n_rows} X[row, :]^T Y[row, :].
+ * nn.Linear weight [d_out, d_in]: X = out-grad, Y = activations; HF Conv1D weight [d_in, d_out]:
+ * X = activations, Y = out-grad.  ws: fp32 scratch of ghost_wgrad_workspace_bytes().
+ * Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:155-173 and :474-506 together
+ * with the batch-size rescale of ghostEngines/autograd_grad_sample_dotprod.py:132-134 (folded into
+ * `scale`). */
+long long ghost_wgrad_workspace_bytes(int m_cols, int n_cols);
+int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, int m_cols, int n_cols,
+                     long long ldx, long long ldy, float scale, int accumulate, void* out,
+                     int out_is_f32, void* ws, long long ws_bytes, void* stream);
+
+/* ---- Linear / Conv1D weight dot product, per-sample-gradient path ---------------------------- */
+/* X, Y: [n_train + n_val, T, cols] bf16.  M[v,b] = dot_scale * <X_v^T Y_v, X_b^T Y_b>.  Per-sample
+ * weight gradients are formed tile by tile in TMEM and dotted against the stored validation
+ * gradients in the epilogue; if grad_out != NULL the same pass also produces the train gradient
+ * grad_scale * sum_b X_b^T Y_b (so ghost_wgrad_bf16 is not needed for that layer).
+ * v_is_f32 selects the storage type of the validation gradients in the workspace.
+ * Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:131-135 and :443-447, per
+ * validation sample (the reference's version sums the validation batch first). */
+long long ghost_persample_workspace_bytes(int n_val, int m_cols, int n_cols, int v_is_f32);
+int ghost_persample_dot_bf16(const void* X, const void* Y, int n_train, int n_val, long long T,
+                             int m_cols, int n_cols, long long ldx, long long ldy, float dot_scale,
+                             float* M_out, int v_is_f32, void* grad_out, int grad_is_f32,
+                             float grad_scale, int grad_accumulate, void* ws, long long ws_bytes,
+                             void* stream);
+
+/* ---- bias / LayerNorm / small reductions ------------------------------------------------------- */
+/* out[n, c] = sum_t G[n, t, c]  (fp32).  Replaces the token sums of
+ * ghostEngines/supported_layers_grad_samplers_dotprod.py:138-146, 454-471 and
+ * ghostEngines/autograd_grad_sample_dotprod.py:199-222. */
+int ghost_colsum(const void* G, int is_f32, int N, long long T, int cols, long long ld, float* out,
+                 void* stream);
+/* Per-sample LayerNorm parameter gradients in one pass over A and G:
+ * gw[n,f] = sum_t G[n,t,f] * xhat[n,t,f], gb[n,f] = sum_t G[n,t,f], xhat = layer norm of A over the
+ * last dim without affine.  Replaces
+ * ghostEngines/supported_layers_grad_samplers_dotprod.py:262-300 and :347-363. */
+int ghost_layernorm_persample(const void* A, const void* G, int is_f32, int N, long long T, int F,
+                              float eps, float* gw, float* gb, void* stream);
+/* M[v,b] = scale * <X[n_train + v, :], X[b, :]> for per-sample vectors X[N, F] fp32.  Replaces the
+ * einsum('p,bp->b') / einsum('bf,f->b') contractions of the bias and LayerNorm paths. */
+int ghost_small_gram_f32(const float* X, int n_train, int n_val, int F, float scale, float* M_out,
+                         void* stream);
+/* out[c] (= or +=) scale * sum_{n < n_rows} X[n, c], cast to fp32 or bf16: averaged train gradient
+ * of a bias / LayerNorm parameter from the per-sample vectors. */
+int ghost_rows_sum(const float* X, int n_rows, int F, float scale, void* out, int out_is_f32,
+                   int accumulate, void* stream);
+
+/* ---- Embedding -------------------------------------------------------------------------------- */
+/* M[v,b] = scale * sum_{t,s : ids_b[t] == ids_v[s]} <G_b[t], G_v[s]>.  ids: int64 [N, T]; G: [N, T, d].
+ * Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:181-211. */
+long long ghost_embedding_dot_workspace_bytes(int n_val, long long T, int vocab);
+int ghost_embedding_dot(const long long* ids, const void* G, int is_f32, int n_train, int n_val,
+                        long long T, int d, int vocab, float scale, float* M_out, void* ws,
+                        long long ws_bytes, void* stream);
+/* out[vocab, d] (= or +=) round(sum over train tokens with that id of round(G * pre_scale)) / divisor
+ * in the table dtype, accumulated in fp32 in ascending token order (bit-identical to the CPU
+ * index_add_).  Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:214-235. */
+long long ghost_embedding_wgrad_workspace_bytes(int n_train, long long T, int vocab);
+int ghost_embedding_wgrad(const long long* ids, const void* G, int is_f32, int n_train, long long T,
+                          int d, int vocab, float pre_scale, float divisor, int accumulate, void* out,
+                          void* ws, long long ws_bytes, void* stream);
+
+/* ---- GradProj ------------------------------------------------------------------------------------ */
+/* out + b * out_stride <- scale * (G_b P_r^T)^T (A_b P_c^T), [k_r, k_c] fp32 row-major, for every
+ * sample b.  G: [B, T, n_r], A: [B, T, n_c], P_r: [k_r, n_r], P_c: [k_c, n_c], all bf16.
+ * nn.Linear: (G, P_r) = (out-grad, P_o), (A, P_c) = (activations, P_i).  HF Conv1D: the reference
+ * projects the out-grad with P_i and the activations with P_o, i.e. P_r = P_i, P_c = P_o.
+ * Replaces ghostEngines/gradProjection/autograd_gradproj.py:120-165 and the per-layer
+ * reshape + cat of ghostEngines/gradProjection/gradproj_engine.py:240-263 (results land directly
+ * in the caller's [B, total_proj_dim] slices). */
+int ghost_gradproj_dense_bf16(const void* G, const void* A, int B, long long T, int n_r, int n_c,
+                              long long ldg, long long lda, const void* P_r, const void* P_c, int k_r,
+                              int k_c, long long ldpr, long long ldpc, float scale, float* out,
+                              long long out_stride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GHOST_B200_H_ */

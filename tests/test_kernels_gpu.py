@@ -1,0 +1,263 @@
+"""Parity of every CUDA kernel (called through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import as_dtype
+from oracle import ghost_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}   # relative Frobenius, per the north star
+
+
+def ops():
+    from ghostsuite_b200 import ops as _ops
+    return _ops
+
+
+def make(N, T, d, p, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    A = (torch.randn(N, T, d, generator=g) / d ** 0.5).to(dtype)
+    G = (torch.randn(N, T, p, generator=g) / p ** 0.5).to(dtype)
+    return A, G
+
+
+def after():
+    from ghostsuite_b200 import _lib
+    torch.cuda.synchronize()
+    _lib.poll_kernel_error()
+
+
+LIN_CASES = [
+    # n_train, n_val, T, d, p
+    (5, 3, 6, 16, 24),        # several samples per tile, ragged everything
+    (64, 16, 1, 512, 1024),   # MLP config: T = 1
+    (3, 1, 130, 72, 40),      # T just above one tile, single validation sample
+    (2, 2, 300, 200, 136),    # validation rows straddle the 256-wide tile
+    (4, 2, 128, 64, 64),      # exactly tile-aligned
+    (2, 3, 37, 10, 50),       # feature sizes that are not multiples of 8
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", LIN_CASES)
+def test_gram_dot(case, dtype):
+    n_t, n_v, T, d, p = case
+    A, G = make(n_t + n_v, T, d, p, dtype)
+    M = ops().gram_dot(A.cuda(), G.cuda(), n_v)
+    after()
+    ref = O.linear_dot_exact(A, G, n_v)
+    assert M.shape == (n_v, n_t)
+    assert O.rel_fro(M, ref) < TOL[dtype]
+
+
+def test_gram_dot_reference_rounding_mode():
+    """round_mode=1 reproduces the reference's bf16-rounded Grams (vector = column sums)."""
+    n_t, n_v, T, d, p = 5, 3, 6, 16, 24
+    A, G = make(n_t + n_v, T, d, p, torch.bfloat16, seed=3)
+    M = ops().gram_dot(A.cuda(), G.cuda(), n_v, round_mode=1)
+    after()
+    ref = O.linear_dot_reference(A, G, n_v, use_ghost=True)
+    assert O.rel_fro(M.sum(0), ref) < 2e-3
+
+
+def test_gram_dot_golden(golden):
+    for tag, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        A = as_dtype(golden[f"lin_{tag}_A"], tag)
+        G = as_dtype(golden[f"lin_{tag}_G"], tag)
+        M = ops().gram_dot(A.cuda(), G.cuda(), 3)
+        after()
+        rows = torch.from_numpy(golden[f"lin_{tag}_rows_materialised"])
+        assert O.rel_fro(M, rows) < TOL[dt]
+        assert O.rel_fro(M.sum(0), torch.from_numpy(golden[f"lin_{tag}_nv3_ghost1_w"])) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", LIN_CASES)
+def test_wgrad(case, dtype):
+    n_t, n_v, T, d, p = case
+    A, G = make(n_t + n_v, T, d, p, dtype, seed=1)
+    N = n_t + n_v
+    scale = N / n_t
+    out = ops().wgrad(G[:n_t].cuda(), A[:n_t].cuda(), scale, dtype)        # Linear layout [p, d]
+    outc = ops().wgrad(A[:n_t].cuda(), G[:n_t].cuda(), scale, dtype)       # Conv1D layout [d, p]
+    after()
+    ref = torch.einsum("btp,btd->pd", G[:n_t].double(), A[:n_t].double()) * scale
+    assert out.shape == (p, d) and out.dtype == dtype
+    tol = 1e-4 if dtype == torch.float32 else 1e-2
+    assert O.rel_fro(out, ref) < tol
+    assert O.rel_fro(outc, ref.t()) < tol
+    # against the reference formula in its own dtype
+    ref2 = O.linear_train_grad(A, G * N, n_v)
+    assert O.rel_fro(out, ref2) < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+def test_wgrad_accumulate():
+    A, G = make(6, 40, 64, 48, torch.bfloat16, seed=5)
+    o = ops()
+    base = torch.randn(48, 64).to(torch.float32).cuda()
+    out = base.clone()
+    o.wgrad(G.cuda(), A.cuda(), 0.5, torch.float32, out=out, accumulate=True)
+    after()
+    ref = base.cpu().double() + 0.5 * torch.einsum("btp,btd->pd", G.double(), A.double())
+    assert O.rel_fro(out, ref) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", LIN_CASES)
+def test_persample_dot(case, dtype):
+    n_t, n_v, T, d, p = case
+    A, G = make(n_t + n_v, T, d, p, dtype, seed=2)
+    N = n_t + n_v
+    M, grad = ops().persample_dot(G.cuda(), A.cuda(), n_v, want_grad=True, grad_scale=N / n_t,
+                                  grad_dtype=dtype)
+    after()
+    ref = O.linear_dot_exact(A, G, n_v)
+    assert O.rel_fro(M, ref) < TOL[dtype]
+    gref = torch.einsum("btp,btd->pd", G[:n_t].double(), A[:n_t].double()) * (N / n_t)
+    assert O.rel_fro(grad, gref) < (1e-4 if dtype == torch.float32 else 1e-2)
+    # both paths agree with each other far inside the tolerance
+    M2 = ops().gram_dot(A.cuda(), G.cuda(), n_v)
+    after()
+    assert O.rel_fro(M, M2.cpu()) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(8, 6, 24), (12, 1, 10), (5, 300, 520), (3, 1024, 768)])
+def test_colsum_and_bias(shape, dtype):
+    N, T, p = shape
+    g = torch.Generator().manual_seed(4)
+    G = torch.randn(N, T, p, generator=g).to(dtype)
+    o = ops()
+    cs = o.colsum(G.cuda())
+    n_v = 2
+    M = o.small_gram(cs, n_v)
+    bgrad = o.rows_sum(cs, N - n_v, N / (N - n_v), dtype)
+    after()
+    ref = G.double().sum(1)
+    assert O.rel_fro(cs, ref) < 1e-5
+    assert O.rel_fro(M, O.bias_dot_exact(G, n_v)) < 1e-4
+    assert O.rel_fro(bgrad, O.bias_train_grad((G * N).clone(), n_v)) < (1e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(8, 6, 16), (5, 70, 768), (4, 33, 1024), (3, 9, 20), (2, 5, 1536)])
+def test_layernorm(shape, dtype):
+    N, T, F = shape
+    g = torch.Generator().manual_seed(6)
+    A = (torch.randn(N, T, F, generator=g) * 1.5 + 0.3).to(dtype)
+    G = (torch.randn(N, T, F, generator=g) / F ** 0.5).to(dtype)
+    gw, gb = ops().layernorm_persample(A.cuda(), G.cuda(), 1e-5)
+    after()
+    rw, rb = O.layernorm_persample_exact(A, G, 1e-5)
+    assert O.rel_fro(gw, rw) < 1e-4
+    assert O.rel_fro(gb, rb) < 1e-4
+
+
+def test_layernorm_golden(golden):
+    eps = float(golden["ln_eps"][0])
+    for tag in ("f32", "bf16"):
+        A = as_dtype(golden[f"ln_{tag}_A"], tag)
+        G = as_dtype(golden[f"ln_{tag}_G"], tag)
+        o = ops()
+        gw, gb = o.layernorm_persample(A.cuda(), G.cuda(), eps)
+        Mw, Mb = o.small_gram(gw, 3), o.small_gram(gb, 3)
+        after()
+        assert O.rel_fro(Mw.sum(0), torch.from_numpy(golden[f"ln_{tag}_nv3_w"])) < 2e-2
+        assert O.rel_fro(Mb.sum(0), torch.from_numpy(golden[f"ln_{tag}_nv3_b"])) < 2e-2
+        tw = o.rows_sum(gw, 5, 8 / 5, torch.float32)
+        after()
+        assert O.rel_fro(tw, torch.from_numpy(golden[f"ln_{tag}_train_grad_w"])) < (1e-5 if tag == "f32" else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", [(5, 3, 6, 8, 11), (4, 2, 64, 40, 50), (3, 2, 100, 768, 7), (6, 1, 33, 16, 1000)])
+def test_embedding(case, dtype):
+    n_t, n_v, T, d, vocab = case
+    N = n_t + n_v
+    g = torch.Generator().manual_seed(8)
+    ids = torch.randint(0, vocab, (N, T), generator=g)
+    G = (torch.randn(N, T, d, generator=g) / d ** 0.5).to(dtype)
+    o = ops()
+    M = o.embedding_dot(ids.cuda(), G.cuda(), n_v, vocab)
+    grad = o.embedding_wgrad(ids.cuda(), G.cuda(), n_t, vocab, float(N), float(n_t))
+    after()
+    assert O.rel_fro(M, O.embedding_dot_exact(ids, G, n_v)) < (1e-5 if dtype == torch.float32 else 1e-4)
+    ref = O.embedding_train_grad(ids, G * N, n_v, vocab, sequential=True)
+    # index / gather work: bit-exact against the CPU sequential order
+    assert torch.equal(grad.cpu().float(), ref.float())
+
+
+def test_embedding_position_ids_and_golden(golden):
+    # position-embedding pattern: every sample has ids 0..T-1 (all buckets hold n_train tokens)
+    n_t, n_v, T, d = 40, 2, 16, 24
+    ids = torch.arange(T).repeat(n_t + n_v, 1)
+    G = torch.randn(n_t + n_v, T, d, generator=torch.Generator().manual_seed(1))
+    o = ops()
+    M = o.embedding_dot(ids.cuda(), G.cuda(), n_v, T)
+    grad = o.embedding_wgrad(ids.cuda(), G.cuda(), n_t, T, float(n_t + n_v), float(n_t))
+    after()
+    assert O.rel_fro(M, O.embedding_dot_exact(ids, G, n_v)) < 1e-5
+    assert torch.equal(grad.cpu(), O.embedding_train_grad(ids, G * (n_t + n_v), n_v, T))
+    ids = torch.from_numpy(golden["emb_ids"])
+    for tag in ("f32", "bf16"):
+        G = as_dtype(golden[f"emb_{tag}_G"], tag)
+        M = o.embedding_dot(ids.cuda(), G.cuda(), 3, 11)
+        grad = o.embedding_wgrad(ids.cuda(), G.cuda(), 5, 11, 8.0, 5.0)
+        after()
+        assert O.rel_fro(M.sum(0), torch.from_numpy(golden[f"emb_{tag}_nv3_w"])) < 2e-2
+        assert np.array_equal(grad.cpu().float().numpy(), golden[f"emb_{tag}_train_grad"])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", [(8, 6, 16, 24, 4, 6), (4, 130, 72, 200, 32, 32), (2, 300, 512, 136, 64, 64),
+                                  (3, 1, 10, 20, 5, 3), (2, 257, 128, 256, 120, 34)])
+def test_gradproj_dense(case, dtype):
+    B, T, n_i, n_o, k_i, k_o = case
+    A, G = make(B, T, n_i, n_o, dtype, seed=9)
+    g = torch.Generator().manual_seed(10)
+    P_i = torch.randn(k_i, n_i, generator=g) / k_i ** 0.5
+    P_o = torch.randn(k_o, n_o, generator=g) / k_o ** 0.5
+    o = ops()
+    split = dtype == torch.float32
+    Pr = o.prepare_projection(P_o.cuda(), split)
+    Pc = o.prepare_projection(P_i.cuda(), split)
+    total = k_o * k_i + 7
+    buf = torch.full((B, total), 123.0, device="cuda")
+    o.gradproj_dense(G.cuda(), A.cuda(), Pr, Pc, k_o, k_i, float(B), buf[:, 3:3 + k_o * k_i])
+    after()
+    ref = O.gradproj_dense(A, G, P_i, P_o, compute_dtype=torch.float64)
+    got = buf[:, 3:3 + k_o * k_i].reshape(B, k_o, k_i)
+    assert O.rel_fro(got, ref) < (1e-4 if split else 2e-2)
+    # neighbours of the slice are untouched
+    assert torch.all(buf[:, :3] == 123.0) and torch.all(buf[:, 3 + k_o * k_i:] == 123.0)
+
+
+def test_gradproj_golden(golden):
+    A = torch.from_numpy(golden["lin_f32_A"])
+    G = torch.from_numpy(golden["lin_f32_G"])
+    o = ops()
+    P_i, P_o = torch.from_numpy(golden["gp_P_i"]), torch.from_numpy(golden["gp_P_o"])
+    out = torch.empty(8, 24, device="cuda")
+    o.gradproj_dense(G.cuda(), A.cuda(), o.prepare_projection(P_o.cuda(), True),
+                     o.prepare_projection(P_i.cuda(), True), 6, 4, 8.0, out)
+    after()
+    assert torch.allclose(out.cpu().reshape(8, 6, 4), torch.from_numpy(golden["gp_linear"]), rtol=1e-4, atol=1e-5)
+    # Conv1D: the out-grad is projected with P_i, the activations with P_o -> [k_i, k_o]
+    P_i, P_o = torch.from_numpy(golden["gp_c1d_P_i"]), torch.from_numpy(golden["gp_c1d_P_o"])
+    o.gradproj_dense(G.cuda(), A.cuda(), o.prepare_projection(P_i.cuda(), True),
+                     o.prepare_projection(P_o.cuda(), True), 4, 6, 8.0, out)
+    after()
+    assert torch.allclose(out.cpu().reshape(8, 4, 6), torch.from_numpy(golden["gp_c1d"]), rtol=1e-4, atol=1e-5)
+
+
+def test_error_codes_are_python_exceptions():
+    o = ops()
+    A = torch.randn(4, 3, 8, device="cuda")
+    with pytest.raises(ValueError):
+        o.gram_dot(A, A, 4)            # no training samples
+    with pytest.raises(ValueError):
+        o.small_gram(A.reshape(4, 24), 4)
+    with pytest.raises(RuntimeError):
+        o.colsum(A.cpu())
