@@ -191,7 +191,7 @@ emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restri
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int f = f0 + q * 32 + lane;
-          if (f < d) acc[q] += round_to<T>(ld_f32<T>(row + f) * pre_scale);
+          if (f < d) acc[q] = __fadd_rn(acc[q], round_to<T>(__fmul_rn(ld_f32<T>(row + f), pre_scale)));  // no fma contraction: two roundings, as the reference
         }
       }
     } else if (cnt > 32) {
@@ -210,7 +210,7 @@ emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restri
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int f = f0 + q * 32 + lane;
-          if (f < d) acc[q] += round_to<T>(ld_f32<T>(row + f) * pre_scale);
+          if (f < d) acc[q] = __fadd_rn(acc[q], round_to<T>(__fmul_rn(ld_f32<T>(row + f), pre_scale)));  // no fma contraction: two roundings, as the reference
         }
       }
     }
@@ -221,7 +221,7 @@ emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restri
         float o = round_to<T>(acc[q]);
         o = round_to<T>(__fdiv_rn(o, divisor));
         T* dst = out + static_cast<long long>(k) * d + f;
-        if (accumulate) o = round_to<T>(ld_f32<T>(dst) + o);
+        if (accumulate) o = round_to<T>(__fadd_rn(ld_f32<T>(dst), o));
         *dst = from_f32<T>(o);
       }
     }

@@ -37,7 +37,7 @@ template <int KMAX>   // largest padded rank this instantiation handles (32, 64 
 struct GpCfg {
   static constexpr int BM = 128, BK = 64;
   static constexpr int kStageBytes = (BM + KMAX) * BK * 2;
-  static constexpr int kStages = 4;
+  static constexpr int kStages = (KMAX == 128) ? 3 : 4;   // 3 keeps KMAX = 128 inside 227 KB
   static constexpr int kProjBytes = 2 * BM * KMAX * 4;     // fp32 staging of both projected blocks
   static constexpr int kSmemBytes = kStages * kStageBytes + kProjBytes + 1024 + 256;
   static constexpr int RT = KMAX / 16;   // output rows per thread (16 thread rows)

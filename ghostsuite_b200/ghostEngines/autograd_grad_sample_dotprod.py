@@ -1,0 +1,145 @@
+"""Forward/backward hook plumbing for the gradient-dot-product engine.
+
+Drop-in for GhostSuite's ``ghostEngines/autograd_grad_sample_dotprod.py`` (``add_hooks`` :23-81,
+``remove_hooks`` :84-89, ``_capture_activations`` :92-94, ``backward_hook`` closure :58-71): same
+names, signatures, attributes (``layer.activations``, ``layer.backprops``, ``layer.name``,
+``model.autograd_grad_sample_hooks``) and exceptions.  The hook bodies call the CUDA-backed layer
+functions of ``supported_layers_grad_samplers_dotprod``.
+
+One deliberate difference inside the hook: the reference multiplies the whole out-grad tensor by
+the batch size (a full extra read and write per layer, :132-134) before the train-gradient pass.
+Here the raw out-grad is kept and the factor is recorded in ``layer._ghost_backprop_scale``; the
+kernels fold it into their epilogue scale.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .supported_layers_grad_samplers_dotprod import (
+    _supported_layers_dotprod,
+    _create_or_accumulate_train_grad,
+)
+
+
+def requires_grad(module: nn.Module) -> bool:
+    """True if any parameter of ``module`` was trainable when the engine was built."""
+    return any(getattr(p, "initially_requires_grad", p.requires_grad) for p in module.parameters())
+
+
+def add_hooks(model: nn.Module, val_batch_size: int, loss_reduction: str = "mean"):
+    """Register the activation-capture and dot-product/train-gradient hooks on every supported
+    layer that has a trainable parameter.  Calling it twice on one model raises ValueError."""
+    if hasattr(model, "autograd_grad_sample_hooks"):
+        raise ValueError("Trying to add hooks twice to the same model")
+    if loss_reduction not in ("mean", "sum"):
+        raise ValueError(f"loss_reduction must be 'mean' or 'sum', got {loss_reduction!r}")
+
+    handles = []
+    for name, layer in model.named_modules():
+        if type(layer) in _supported_layers_dotprod and requires_grad(layer):
+            layer.name = name
+            handles.append(layer.register_forward_hook(_capture_activations))
+
+            def backward_hook(this_layer, grad_input, grad_output):
+                _prepare_sample_grad_or_dotprod(this_layer, grad_output, val_batch_size, loss_reduction)
+                _apply_train_grad(this_layer, val_batch_size)
+                return None
+
+            handles.append(layer.register_full_backward_hook(backward_hook))
+        elif not list(layer.children()) and requires_grad(layer):
+            print(f"WARNING: Skipping atomic layer '{name}' of type {type(layer)} because it is not supported.")
+
+    model.__dict__.setdefault("autograd_grad_sample_hooks", []).extend(handles)
+
+
+def remove_hooks(model: nn.Module):
+    """Remove everything ``add_hooks`` registered."""
+    if hasattr(model, "autograd_grad_sample_hooks"):
+        for handle in model.autograd_grad_sample_hooks:
+            handle.remove()
+        del model.autograd_grad_sample_hooks
+
+
+def _capture_activations(layer: nn.Module, inputs: Tuple, outputs: Tuple):
+    """Forward hook: keep the layer input for the backward hook."""
+    layer.activations = inputs[0].detach()
+
+
+def _prepare_sample_grad_or_dotprod(layer: nn.Module, grad_output: Tuple[torch.Tensor],
+                                    val_batch_size: int, loss_reduction: str = "mean"):
+    """Backward hook, part 1: dot products of this layer's parameters (reference :97-137)."""
+    backprops = grad_output[0].detach()
+    if not hasattr(layer, "activations"):
+        layer.activations = None
+    A = layer.activations
+    dot_fn, _ = _supported_layers_dotprod[type(layer)]
+
+    # mixed precision: bring both operands to the common floating type (ids stay integer)
+    if A is not None and A.is_floating_point() and A.dtype != backprops.dtype:
+        common = torch.promote_types(A.dtype, backprops.dtype)
+        A = A.to(common)
+        backprops = backprops.to(common)
+        layer.activations = A
+
+    # 'mean' losses carry a 1/batch factor; the train-gradient kernels undo it in their epilogue
+    layer._ghost_backprop_scale = float(backprops.shape[0]) if loss_reduction == "mean" else 1.0
+    dot_fn(layer, A, backprops, val_batch_size=val_batch_size)
+    layer.backprops = backprops
+
+
+def _apply_train_grad(layer: nn.Module, val_batch_size: int, loss_reduction: str = "mean"):
+    """Backward hook, part 2: averaged train gradients into ``param.train_grad`` (reference :140-196)."""
+    _, train_grad_fn = _supported_layers_dotprod.get(type(layer), (None, None))
+    if not train_grad_fn:
+        raise ValueError(
+            f"Layer {layer.__class__.__name__} is not supported for training gradient computation. "
+            "Ensure it is included in the _supported_layers_dotprod dictionary.")
+    try:
+        if isinstance(layer, nn.LayerNorm):
+            train_grad_fn(layer, layer.activations, layer.backprops, val_batch_size)
+        else:
+            weight = getattr(layer, "weight", None)
+            if weight is not None and getattr(weight, "initially_requires_grad", weight.requires_grad):
+                grad_weight = train_grad_fn(layer, layer.activations, layer.backprops, val_batch_size)
+                if grad_weight is None:
+                    raise ValueError(
+                        f"Layer {layer.__class__.__name__} returned None for weight gradient. "
+                        "Ensure the compute_layer_train_grad function is implemented correctly.")
+                _create_or_accumulate_train_grad(weight, grad_weight)
+            bias = getattr(layer, "bias", None)
+            if bias is not None and getattr(bias, "initially_requires_grad", bias.requires_grad):
+                grad_bias = _train_grad_bias_from_layer(layer, val_batch_size, loss_reduction)
+                _create_or_accumulate_train_grad(bias, grad_bias)
+    finally:
+        for attr in ("activations", "backprops", "_ghost_backprop_scale", "_ghost_colsums",
+                     "_ghost_cached_train_grad", "_ghost_ln_cache"):
+            layer.__dict__.pop(attr, None)
+
+
+def _train_grad_bias_from_layer(layer: nn.Module, val_batch_size: int, loss_reduction: str):
+    """Bias train gradient from the per-sample column sums the dot-product pass already made."""
+    B = layer.backprops
+    n_train = B.size(0) - val_batch_size
+    if n_train <= 0:
+        raise ValueError("No training samples to compute gradients, check batch sizes.")
+    colsums = layer.__dict__.get("_ghost_colsums")
+    if colsums is None:
+        colsums = ops.colsum(B)
+    scale = float(getattr(layer, "_ghost_backprop_scale", 1.0))
+    if loss_reduction == "mean":
+        scale /= n_train
+    return ops.rows_sum(colsums, n_train, scale, layer.bias.dtype if B.dtype == layer.bias.dtype else B.dtype)
+
+
+def _compute_train_grad_bias(B: torch.Tensor, val_batch_size: int, loss_reduction: str = "mean") -> torch.Tensor:
+    """Sum (or, for 'mean', average over the train samples) of the already scaled out-grad over
+    batch and tokens -> ``[features]`` (reference :199-222)."""
+    n_train = B.size(0) - val_batch_size
+    if n_train <= 0:
+        raise ValueError("No training samples to compute gradients, check batch sizes.")
+    colsums = ops.colsum(B)
+    return ops.rows_sum(colsums, n_train, 1.0 / n_train if loss_reduction == "mean" else 1.0, B.dtype)

@@ -1,0 +1,163 @@
+"""GradDotProdEngine: lifecycle around the dot-product hooks.
+
+Drop-in for GhostSuite's ``ghostEngines/graddotprod_engine.py`` (class at :17-272): same
+constructor, methods and on-disk artefacts (``valset.pt``, ``dot_prod_log_iter_{n}.pt`` holding a
+list of ``{dot_product, X_train, Y_train, iter_num, batch_idx}`` dicts).  Additions: the aggregated
+full matrix is kept next to the vector (``dot_product_matrix`` in each log entry) and
+``aggregate_and_log`` checks the device error word that kernels set when a bounded wait ran out.
+"""
+from __future__ import annotations
+
+import os
+import warnings
+from typing import Optional
+
+import torch
+from torch import nn
+
+from .. import _lib
+from . import autograd_grad_sample_dotprod
+from . import transformers_support
+
+
+class GradDotProdEngine:
+    """Computes, inside one ordinary backward pass over ``cat(train, val)``, the dot product of
+    every validation sample's gradient with every train sample's gradient, and recovers the
+    averaged train gradient for the optimizer."""
+
+    def __init__(self, module: nn.Module, val_batch_size: int, loss_reduction: str = "mean",
+                 use_dummy_bias: bool = False, dot_prod_save_path: Optional[str] = None):
+        self.module = module
+        self.val_batch_size = val_batch_size
+        self.loss_reduction = loss_reduction
+        self.dot_prod_save_path = dot_prod_save_path
+        self.named_params = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
+        self._grad_creation_locked = False
+        self.dot_product_log = []
+        self.batch_idx_lst = []
+        self.X_train = self.Y_train = None
+        self.iter_num = None
+        self.batch_idx = None
+
+        # remember what was trainable; in dummy-bias mode autograd then only computes
+        # activation gradients (the hooks produce every weight gradient themselves)
+        for _, param in module.named_parameters():
+            param.initially_requires_grad = bool(param.requires_grad)
+            param.requires_grad = not use_dummy_bias
+        transformers_support.forward_swapper(module=module)
+
+    # ------------------------------------------------------------------ attach / detach
+    def attach(self, optimizer: torch.optim.Optimizer):
+        self.optimizer = optimizer
+        autograd_grad_sample_dotprod.add_hooks(model=self.module, val_batch_size=self.val_batch_size,
+                                               loss_reduction=self.loss_reduction)
+        optimizer.grad_dot_prod_engine = self
+
+    def detach(self):
+        optimizer = self.optimizer
+        if hasattr(optimizer, "grad_dot_prod_engine"):
+            del optimizer.grad_dot_prod_engine
+        autograd_grad_sample_dotprod.remove_hooks(self.module)
+        self.module.zero_grad()
+        for param in self.module.parameters():
+            for attr in ("train_grad", "grad_dot_prod", "grad_dot_prod_matrix", "activations", "backprops"):
+                if hasattr(param, attr):
+                    delattr(param, attr)
+
+    # ------------------------------------------------------------------ gradients
+    def _lock_grad_creation(self):
+        self._grad_creation_locked = True
+
+    def _unlock_grad_creation(self):
+        self._grad_creation_locked = False
+
+    def _prepare_and_apply_train_grad(self):
+        if self._grad_creation_locked:
+            return
+        for name, param in self.module.named_parameters():
+            if not param.initially_requires_grad or "dummy_bias" in name:
+                continue
+            if not hasattr(param, "train_grad"):
+                raise ValueError(f"Parameter {name} requires grad but does not have 'train_grad' attribute. ")
+            if param.train_grad is None:
+                raise ValueError(f"Parameter {name} requires grad has no accumulated training gradient. ")
+            param.grad = param.train_grad
+        self._lock_grad_creation()
+
+    def _clear_train_grad(self):
+        for param in self.module.parameters():
+            if hasattr(param, "train_grad"):
+                del param.train_grad
+        self._unlock_grad_creation()
+
+    def prepare_gradients(self):
+        """Move ``param.train_grad`` into ``param.grad`` for the optimizer."""
+        self._prepare_and_apply_train_grad()
+
+    def clear_gradients(self):
+        """Drop the stored train gradients after the optimizer step."""
+        self._clear_train_grad()
+
+    # ------------------------------------------------------------------ dot products
+    def aggregate_and_log(self):
+        self._aggregate_and_log_dot_products()
+
+    def _aggregate_and_log_dot_products(self):
+        total = None
+        total_matrix = None
+        for _, param in self.module.named_parameters():
+            if hasattr(param, "grad_dot_prod") and param.initially_requires_grad:
+                if param.grad_dot_prod.numel() > 0:
+                    if total is None:
+                        total = param.grad_dot_prod.clone()
+                    else:
+                        total += param.grad_dot_prod
+                    m = getattr(param, "grad_dot_prod_matrix", None)
+                    if m is not None:
+                        total_matrix = m.clone() if total_matrix is None else total_matrix.add_(m)
+                delattr(param, "grad_dot_prod")
+                if hasattr(param, "grad_dot_prod_matrix"):
+                    delattr(param, "grad_dot_prod_matrix")
+        if total is None:
+            warnings.warn("No gradient dot products computed for this iteration.")
+            return
+        entry = {
+            "dot_product": to_device(total, "cpu"),      # device -> host: also the step's sync point
+            "X_train": to_device(self.X_train, "cpu") if self.X_train is not None else None,
+            "Y_train": to_device(self.Y_train, "cpu") if self.Y_train is not None else None,
+            "iter_num": self.iter_num,
+            "batch_idx": self.batch_idx,
+        }
+        if total_matrix is not None:
+            entry["dot_product_matrix"] = to_device(total_matrix, "cpu")
+        if total.is_cuda:
+            _lib.poll_kernel_error()
+        self.dot_product_log.append(entry)
+
+    def save_dot_product_log(self, iter_num: int):
+        if not self.dot_product_log:
+            raise ValueError("No gradient dot products found to save for this iteration.")
+        print(f"[INFO] Saving dot product log at iteration {iter_num} ...")
+        path = os.path.join(self.dot_prod_save_path, f"dot_prod_log_iter_{iter_num}.pt")
+        torch.save(self.dot_product_log, path)
+        self.dot_product_log.clear()
+
+    def attach_and_store_valset(self, X_val, Y_val):
+        path = os.path.join(self.dot_prod_save_path, "valset.pt")
+        torch.save({"X_val": to_device(X_val, "cpu"), "Y_val": to_device(Y_val, "cpu")}, path)
+        print(f"[INFO] Saved validation set to {path}")
+
+    def attach_train_batch(self, X_train, Y_train, iter_num, batch_idx=None):
+        self.X_train = X_train
+        self.Y_train = Y_train
+        self.iter_num = iter_num
+        self.batch_idx = batch_idx
+
+
+def to_device(data, device):
+    """Move a tensor or a dict of tensors to ``device``."""
+    if isinstance(data, dict):
+        return {k: (v.to(device) if hasattr(v, "to") else v) for k, v in data.items()}
+    if hasattr(data, "to"):
+        return data.to(device)
+    raise TypeError(f"Unsupported data type for moving to GPU: {type(data)}. Expected tensor or dict of tensors.")

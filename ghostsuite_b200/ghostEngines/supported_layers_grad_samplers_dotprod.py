@@ -1,0 +1,265 @@
+"""Per-layer dot-product and train-gradient functions backed by the sm_100a kernels.
+
+Drop-in for GhostSuite's ``ghostEngines/supported_layers_grad_samplers_dotprod.py``: the registry
+``_supported_layers_dotprod`` maps a layer type to ``(dot_fn, train_grad_fn)`` with
+
+    dot_fn(layer, A, B, val_batch_size) -> None      sets  <param>.grad_dot_prod  ([n_train])
+    train_grad_fn(layer, A, B_scaled, val_batch_size) -> Tensor | None
+
+exactly as the reference (registry at :596-602 there).  Differences, all additive:
+
+* every parameter also gets ``grad_dot_prod_matrix`` -- the full ``[n_val, n_train]`` float32
+  matrix; ``grad_dot_prod`` is its sum over the validation samples, which is the quantity the
+  reference defines.  The reference's Conv1D and materialised-Linear branches sum the validation
+  batch before the outer product and are therefore only right for one validation sample; here
+  every validation sample is treated separately.
+* dot products are float32 and computed without the reference's bf16 rounding of intermediates.
+* the layer math runs in ``libghost_b200.so``; without a B200 these functions raise.
+
+Two tensor-core paths exist for Linear / Conv1D weights: the Gram ("ghost") kernel and the
+per-sample-gradient kernel.  ``layer.use_ghost_computation`` (same attribute as the reference,
+computed once and cached; pre-setting it overrides the choice) selects the Gram kernel when True.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+try:  # HF Conv1D is optional at import time; it is a registry key when transformers is present
+    from transformers.pytorch_utils import Conv1D as _HFConv1D
+except Exception:  # pragma: no cover
+    _HFConv1D = None
+
+from .. import ops
+
+#: 'cost'      -- pick the cheaper tensor-core path for the full [n_val, n_train] matrix
+#: 'reference' -- GhostSuite's rule, Gram path iff 2*T^2 <= weight.numel()
+#: 'gram' / 'persample' -- force one kernel (benchmarks and tests)
+PATH_RULE = "cost"
+
+# relative cost of the per-sample path's epilogue (validation-gradient dots) per tensor flop
+_PERSAMPLE_OVERHEAD = 1.25
+
+
+def _token_count(A: torch.Tensor) -> int:
+    if A.dim() <= 2:
+        return 1
+    t = 1
+    for s in A.shape[1:-1]:
+        t *= int(s)
+    return t
+
+
+def _should_use_ghost_computation(layer: nn.Module, A: torch.Tensor, B: torch.Tensor,
+                                  conv: bool = False, val_batch_size: int = None):
+    """Decide once per layer whether the Gram kernel is used (cached in
+    ``layer.use_ghost_computation``, as in the reference at :7-41).
+
+    With ``PATH_RULE == 'reference'`` (or when the batch split is unknown) this is the reference's
+    test ``2*T^2 <= weight.numel()``.  With ``'cost'`` the two kernels' tensor work for the full
+    matrix is compared: Gram ``2*n_t*n_v*T^2*(d+p)`` against per-sample ``2*(n_t+n_v)*T*d*p``.
+    """
+    if hasattr(layer, "use_ghost_computation"):
+        return
+    if conv:
+        T, d, p = int(A.shape[-1]), int(A.shape[1]), int(B.shape[1])
+    else:
+        T, d, p = _token_count(A), int(A.shape[-1]), int(B.shape[-1])
+    if PATH_RULE in ("gram", "persample"):
+        layer.use_ghost_computation = PATH_RULE == "gram"
+        return
+    if PATH_RULE == "reference" or val_batch_size is None:
+        layer.use_ghost_computation = bool(2 * T ** 2 <= layer.weight.numel())
+        return
+    n_v = int(val_batch_size)
+    n_t = int(A.shape[0]) - n_v
+    gram = 2.0 * n_t * n_v * T * T * (d + p)
+    per = 2.0 * (n_t + n_v) * T * d * p * _PERSAMPLE_OVERHEAD
+    layer.use_ghost_computation = bool(gram <= per)
+
+
+def _create_or_accumulate_train_grad(param: torch.Tensor, grad: torch.Tensor) -> None:
+    """``param.train_grad`` is created on first use and added to afterwards (reference :44-69)."""
+    assert grad.shape == param.shape, \
+        f"Gradient shape ({grad.shape}) does not match parameter shape ({param.shape})"
+    grad = grad.detach()
+    if hasattr(param, "train_grad"):
+        param.train_grad.add_(grad)
+    else:
+        param.train_grad = grad
+
+
+def _set_dot(param: torch.Tensor, M: torch.Tensor) -> None:
+    param.grad_dot_prod_matrix = M
+    param.grad_dot_prod = M.sum(dim=0)
+
+
+def _check_batch(A, B, val_batch_size: int) -> int:
+    if A is None:
+        raise ValueError("Input activations A cannot be None.")
+    if B is None:
+        raise ValueError("Output gradients B cannot be None.")
+    n_train = A.size(0) - val_batch_size
+    if n_train <= 0:
+        raise ValueError("No training samples to compute dot product, check batch sizes.")
+    return n_train
+
+
+def _backprop_scale(layer: nn.Module) -> float:
+    """Factor that turns the stored out-grad into the reference's ``B * batch_size``.
+
+    The hook plumbing stores the raw out-grad and records the factor here instead of making a
+    scaled copy of the whole tensor; direct callers that pass an already scaled ``B`` leave the
+    attribute unset (factor 1).
+    """
+    return float(getattr(layer, "_ghost_backprop_scale", 1.0))
+
+
+def _bias_terms(layer: nn.Module, B: torch.Tensor, val_batch_size: int) -> None:
+    """Bias dot products from per-sample column sums of the out-grad (reference :138-146)."""
+    colsums = ops.colsum(B)                       # [N, p] float32, one pass over B
+    _set_dot(layer.bias, ops.small_gram(colsums, val_batch_size))
+    layer._ghost_colsums = colsums               # reused by the bias train gradient
+
+
+# --------------------------------------------------------------------------------------------
+# Linear and HF Conv1D
+# --------------------------------------------------------------------------------------------
+def _dense_dot_product(layer: nn.Module, A: torch.Tensor, B: torch.Tensor, val_batch_size: int,
+                       weight_is_in_by_out: bool) -> None:
+    n_train = _check_batch(A, B, val_batch_size)
+    A = A.detach()
+    B = B.detach()
+    _should_use_ghost_computation(layer, A, B, val_batch_size=val_batch_size)
+    if val_batch_size > 0:
+        if layer.use_ghost_computation:
+            M = ops.gram_dot(A, B, val_batch_size)
+        else:
+            # per-sample path: the train gradient falls out of the same pass
+            N = A.size(0)
+            X, Y = (A, B) if weight_is_in_by_out else (B, A)
+            want = bool(getattr(layer.weight, "initially_requires_grad", True))
+            M, grad = ops.persample_dot(X, Y, val_batch_size, want_grad=want,
+                                        grad_scale=_backprop_scale(layer) / n_train,
+                                        grad_dtype=A.dtype)
+            if want:
+                layer._ghost_cached_train_grad = (A.data_ptr(), B.data_ptr(), N, grad)
+        _set_dot(layer.weight, M)
+    if getattr(layer, "bias", None) is not None and val_batch_size > 0:
+        _bias_terms(layer, B, val_batch_size)
+
+
+def _dense_train_grad(layer: nn.Module, A: torch.Tensor, B: torch.Tensor, val_batch_size: int,
+                      weight_is_in_by_out: bool):
+    n_train = A.size(0) - val_batch_size
+    if n_train <= 0:
+        return None
+    cached = layer.__dict__.pop("_ghost_cached_train_grad", None)
+    if cached is not None and cached[0] == A.data_ptr() and cached[1] == B.data_ptr() \
+            and cached[2] == A.size(0):
+        return cached[3]
+    scale = _backprop_scale(layer) / n_train
+    A_t, B_t = A[:n_train], B[:n_train]
+    X, Y = (A_t, B_t) if weight_is_in_by_out else (B_t, A_t)
+    return ops.wgrad(X, Y, scale, A.dtype)
+
+
+def _compute_linear_dot_product(layer: nn.Linear, A: torch.Tensor, B: torch.Tensor,
+                                val_batch_size: int):
+    """nn.Linear: weight and bias dot products (reference :75-146)."""
+    _dense_dot_product(layer, A, B, val_batch_size, weight_is_in_by_out=False)
+
+
+def _compute_linear_train_grad(layer: nn.Linear, A: torch.Tensor, B: torch.Tensor,
+                               val_batch_size: int):
+    """nn.Linear: averaged train gradient ``[d_out, d_in]`` (reference :155-173)."""
+    return _dense_train_grad(layer, A, B, val_batch_size, weight_is_in_by_out=False)
+
+
+def _compute_Conv1D_dot_product(layer: nn.Module, A: torch.Tensor, B: torch.Tensor,
+                                val_batch_size: int) -> None:
+    """HF Conv1D (weight ``[d_in, d_out]``): dot products (reference :369-471)."""
+    if A is not None and A.dim() > 3:
+        raise ValueError("Currently we only expect 3D input tensors (batch, seq_len, features). "
+                         "Extending this to 4D or higher requires additional handling.")
+    _dense_dot_product(layer, A, B, val_batch_size, weight_is_in_by_out=True)
+
+
+def _compute_Conv1D_train_grad(layer: nn.Module, A: torch.Tensor, B: torch.Tensor,
+                               val_batch_size: int):
+    """HF Conv1D: averaged train gradient ``[d_in, d_out]`` (reference :474-506)."""
+    return _dense_train_grad(layer, A, B, val_batch_size, weight_is_in_by_out=True)
+
+
+# --------------------------------------------------------------------------------------------
+# Embedding
+# --------------------------------------------------------------------------------------------
+def _compute_embedding_dot_product(layer: nn.Embedding, A: torch.Tensor, B: torch.Tensor,
+                                   val_batch_size: int):
+    """nn.Embedding: id-equality-masked Gram of the out-grad rows (reference :181-211)."""
+    _check_batch(A, B, val_batch_size)
+    M = ops.embedding_dot(A.detach(), B.detach(), val_batch_size, layer.weight.shape[0])
+    _set_dot(layer.weight, M)
+
+
+def _compute_embedding_train_grad(layer: nn.Embedding, A: torch.Tensor, B: torch.Tensor,
+                                  val_batch_size: int):
+    """nn.Embedding: averaged train gradient ``[vocab, d]`` (reference :214-235)."""
+    n_train = A.size(0) - val_batch_size
+    if n_train <= 0:
+        return None
+    grad = ops.embedding_wgrad(A, B, n_train, layer.weight.shape[0], _backprop_scale(layer),
+                               float(n_train))
+    if grad.dtype != layer.weight.dtype:
+        grad = grad.to(layer.weight.dtype)
+    return grad
+
+
+# --------------------------------------------------------------------------------------------
+# LayerNorm
+# --------------------------------------------------------------------------------------------
+def _layernorm_vectors(layer: nn.LayerNorm, A: torch.Tensor, B: torch.Tensor):
+    if len(layer.normalized_shape) != 1:
+        raise ValueError("LayerNorm over more than the last dimension is not supported")
+    key = (A.data_ptr(), B.data_ptr(), A.size(0))
+    cached = layer.__dict__.get("_ghost_ln_cache")
+    if cached is not None and cached[0] == key:
+        return cached[1], cached[2]
+    gw, gb = ops.layernorm_persample(A.detach(), B.detach(), layer.eps)
+    layer._ghost_ln_cache = (key, gw, gb)
+    return gw, gb
+
+
+def _compute_layernorm_dot_product(layer: nn.LayerNorm, A: torch.Tensor, B: torch.Tensor,
+                                   val_batch_size: int):
+    """nn.LayerNorm: gamma and beta dot products from one pass over A and B (reference :242-300)."""
+    if A.size(0) - val_batch_size <= 0:
+        return
+    gw, gb = _layernorm_vectors(layer, A, B)
+    _set_dot(layer.weight, ops.small_gram(gw, val_batch_size))
+    if layer.bias is not None:
+        _set_dot(layer.bias, ops.small_gram(gb, val_batch_size))
+
+
+def _compute_layernorm_train_grad(layer: nn.LayerNorm, A: torch.Tensor, B: torch.Tensor,
+                                  val_batch_size: int) -> None:
+    """nn.LayerNorm: applies both train gradients itself and returns None (reference :303-366)."""
+    n_train = A.size(0) - val_batch_size
+    if n_train <= 0:
+        raise ValueError("No training samples to compute gradients, check batch sizes.")
+    gw, gb = _layernorm_vectors(layer, A, B)
+    layer.__dict__.pop("_ghost_ln_cache", None)
+    scale = _backprop_scale(layer) / n_train
+    _create_or_accumulate_train_grad(layer.weight, ops.rows_sum(gw, n_train, scale, layer.weight.dtype))
+    if layer.bias is not None:
+        _create_or_accumulate_train_grad(layer.bias, ops.rows_sum(gb, n_train, scale, layer.bias.dtype))
+    return None
+
+
+_supported_layers_dotprod = {
+    nn.Linear: (_compute_linear_dot_product, _compute_linear_train_grad),
+    nn.Embedding: (_compute_embedding_dot_product, _compute_embedding_train_grad),
+    nn.LayerNorm: (_compute_layernorm_dot_product, _compute_layernorm_train_grad),
+}
+if _HFConv1D is not None:
+    _supported_layers_dotprod[_HFConv1D] = (_compute_Conv1D_dot_product, _compute_Conv1D_train_grad)

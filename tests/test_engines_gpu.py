@@ -1,0 +1,355 @@
+"""Engine-level parity on a B200: the ghostEngines mirror driven like GhostSuite's own examples."""
+import contextlib
+import io
+import os
+
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from oracle import ghost_oracle as O
+from oracle.ghost_engine_cpu import OracleDotProdEngine
+
+pytestmark = pytest.mark.gpu
+
+
+def _load_flat(model, flat):
+    off = 0
+    with torch.no_grad():
+        for p in model.parameters():
+            n = p.numel()
+            p.copy_(torch.from_numpy(flat[off:off + n]).view_as(p))
+            off += n
+
+
+def test_mlp_three_steps_match_reference_run(golden):
+    """Same model, data and SGD steps as the golden run of the reference's GradDotProdEngine."""
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    model = nn.Sequential(nn.Linear(10, 8), nn.ReLU(), nn.Linear(8, 4))
+    _load_flat(model, golden["mlp_init"])
+    model.cuda()
+    X = torch.from_numpy(golden["mlp_X"]).cuda()
+    Y = torch.from_numpy(golden["mlp_Y"]).cuda()
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    eng = GradDotProdEngine(module=model, val_batch_size=4, loss_reduction="mean", use_dummy_bias=False)
+    eng.attach(opt)
+    for step in range(3):
+        eng.attach_train_batch(X[:8], Y[:8], step, 0)
+        loss = nn.functional.cross_entropy(model(X), Y)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        for name, q in model.named_parameters():
+            ref = torch.from_numpy(golden[f"mlp_step{step}_{name}_dot"])
+            assert q.grad_dot_prod.shape == ref.shape
+            assert q.grad_dot_prod_matrix.shape == (4, 8)
+            # the reference's weight path rounds its Grams to bf16; biases are exact there
+            tol = 2e-2 if name.endswith("weight") else 1e-4
+            assert O.rel_fro(q.grad_dot_prod, ref) < tol, (step, name)
+            tg = torch.from_numpy(golden[f"mlp_step{step}_{name}_train_grad"])
+            assert O.rel_fro(q.train_grad, tg) < 1e-4, (step, name)
+        eng.aggregate_and_log()
+        agg = eng.dot_product_log[-1]["dot_product"]
+        assert O.rel_fro(agg, torch.from_numpy(golden[f"mlp_step{step}_agg"])) < 2e-2
+        assert eng.dot_product_log[-1]["dot_product_matrix"].shape == (4, 8)
+        eng.prepare_gradients()
+        opt.step()
+        eng.clear_gradients()
+    final = np.concatenate([q.detach().cpu().numpy().ravel() for q in model.parameters()])
+    assert np.allclose(final, golden["mlp_final"], rtol=1e-4, atol=1e-6)
+    eng.detach()
+    assert not hasattr(model, "autograd_grad_sample_hooks")
+
+
+def test_mlp_config1_exact_parity_fp32():
+    """512 -> 1024 -> 1024 -> 10, 64 train + 16 val, fp32: every parameter's full matrix within 1e-4
+    of the float64 per-sample-gradient oracle, train gradients within 1e-4 of autograd's."""
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    from ghostsuite_b200.workloads import make_mlp
+    torch.manual_seed(0)
+    model = make_mlp()
+    cpu_model = make_mlp()
+    cpu_model.load_state_dict(model.state_dict())
+    X = torch.randn(80, 512)
+    Y = torch.randint(0, 10, (80,))
+    model.cuda()
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    eng = GradDotProdEngine(module=model, val_batch_size=16)
+    eng.attach(opt)
+    ora = OracleDotProdEngine(cpu_model, 16, exact=True)
+    ora.attach()
+    for step in range(2):
+        nn.functional.cross_entropy(model(X.cuda()), Y.cuda()).backward()
+        nn.functional.cross_entropy(cpu_model(X), Y).backward()
+        for (name, p), (_, q) in zip(model.named_parameters(), cpu_model.named_parameters()):
+            assert O.rel_fro(p.grad_dot_prod_matrix, q.grad_dot_prod_matrix) < 1e-4, (step, name)
+            assert O.rel_fro(p.train_grad, q.train_grad) < 1e-4, (step, name)
+        # autograd's own gradient of the train-only mean loss equals the recovered train gradient
+        ref_model = make_mlp()
+        ref_model.load_state_dict(cpu_model.state_dict())
+        nn.functional.cross_entropy(ref_model(X[:64]), Y[:64]).backward()
+        for (name, p), (_, r) in zip(model.named_parameters(), ref_model.named_parameters()):
+            assert O.rel_fro(p.train_grad, r.grad) < 1e-4, name
+        eng.aggregate_and_log()
+        eng.prepare_gradients()
+        opt.step()
+        eng.clear_gradients()
+        ora.prepare_gradients()
+        with torch.no_grad():
+            for q in cpu_model.parameters():
+                q -= 0.1 * q.grad
+        cpu_model.zero_grad(set_to_none=True)
+        ora.clear_gradients()
+    eng.detach()
+    ora.detach()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("path_rule", ["cost", "reference", "persample"])
+def test_gpt2_like_per_module_parity(dtype, path_rule):
+    """GPT-2 architecture (tied head, Conv1D, LayerNorm, two embeddings), dummy-bias mode.  The
+    (A, B) pairs seen by every hook are captured on the GPU and the oracle is evaluated on exactly
+    those tensors, per (module, parameter role) because tied parameters keep the last hook's value."""
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as L
+    from ghostsuite_b200.workloads import GPT2Like, GPT2Config
+    torch.manual_seed(1)
+    cfg = GPT2Config(vocab_size=211, n_positions=48, n_embd=64, n_layer=2, n_head=4)
+    model = GPT2Like(cfg).to(dtype).cuda()
+    n_t, n_v, T = 3, 2, 40
+    ids = torch.randint(0, cfg.vocab_size, (n_t + n_v, T)).cuda()
+    opt = torch.optim.SGD(model.parameters(), lr=0.0)
+    old_rule = L.PATH_RULE
+    L.PATH_RULE = path_rule
+    try:
+        eng = GradDotProdEngine(module=model, val_batch_size=n_v, loss_reduction="mean", use_dummy_bias=True)
+        eng.attach(opt)
+        captured = {}
+        results = {}
+
+        def cap_fwd(name):
+            def f(layer, inputs, output):
+                captured.setdefault(name, {})["A"] = inputs[0].detach().cpu()
+            return f
+
+        def cap_bwd(name):
+            def f(layer, grad_input, grad_output):
+                captured[name]["B"] = grad_output[0].detach().cpu()
+                for role in ("weight", "bias"):
+                    q = getattr(layer, role, None)
+                    if q is not None and hasattr(q, "grad_dot_prod_matrix"):
+                        results[(name, role)] = q.grad_dot_prod_matrix.detach().cpu()
+            return f
+
+        handles = []
+        hooked = [(n, m) for n, m in model.named_modules() if type(m) in L._supported_layers_dotprod]
+        for n, m in hooked:
+            handles.append(m.register_forward_hook(cap_fwd(n)))
+            # registered after the engine's hook, so it observes the values that hook just wrote
+            handles.append(m.register_full_backward_hook(cap_bwd(n)))
+        loss, _ = model(ids, labels=ids)
+        loss.backward()
+        torch.cuda.synchronize()
+        tol = 1e-4 if dtype == torch.float32 else 2e-2
+        N = n_t + n_v
+        assert len(hooked) == 2 + 2 * 6 + 1 + 1   # 2 embeddings, 2 blocks x (2 LN + 4 Conv1D), ln_f, head
+        for name, m in hooked:
+            A, B = captured[name]["A"], captured[name]["B"]
+            if isinstance(m, nn.Embedding):
+                ref = O.embedding_dot_exact(A, B, n_v)
+                assert O.rel_fro(results[(name, "weight")], ref) < tol, name
+            elif isinstance(m, nn.LayerNorm):
+                rw, rb = O.layernorm_dot_exact(A, B, n_v, m.eps)
+                assert O.rel_fro(results[(name, "weight")], rw) < tol, name
+                assert O.rel_fro(results[(name, "bias")], rb) < tol, name
+            else:
+                ref = O.linear_dot_exact(A, B, n_v)
+                assert O.rel_fro(results[(name, "weight")], ref) < tol, name
+                if getattr(m, "bias", None) is not None:
+                    assert O.rel_fro(results[(name, "bias")], O.bias_dot_exact(B, n_v)) < tol, name
+        # recovered train gradients == autograd on the train-only batch mean of per-sample losses
+        eng.prepare_gradients()
+        got = {n: p.grad.detach().float().cpu() for n, p in model.named_parameters() if "dummy_bias" not in n}
+        eng.clear_gradients()
+        eng.detach()
+        for h in handles:
+            h.remove()
+        for p in model.parameters():
+            p.requires_grad = True
+        model.zero_grad(set_to_none=True)
+        # the engine's convention: (N / n_t) * d(mean loss over the concatenated batch)/dW restricted
+        # to the train samples' tokens == gradient of the train-only token-mean loss
+        loss_t, _ = model(ids[:n_t], labels=ids[:n_t])
+        loss_t.backward()
+        for n, p in model.named_parameters():
+            if "dummy_bias" in n:
+                continue
+            assert O.rel_fro(got[n], p.grad.float().cpu()) < (1e-3 if dtype == torch.float32 else 5e-2), n
+    finally:
+        L.PATH_RULE = old_rule
+
+
+def test_double_attach_and_error_types():
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    from ghostsuite_b200.ghostEngines import autograd_grad_sample_dotprod as H
+    model = nn.Sequential(nn.Linear(8, 8)).cuda()
+    eng = GradDotProdEngine(model, val_batch_size=2)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    eng.attach(opt)
+    with pytest.raises(ValueError):
+        H.add_hooks(model, 2)
+    # no training samples -> ValueError out of backward
+    x = torch.randn(2, 8, device="cuda")
+    with pytest.raises(ValueError):
+        model(x).sum().backward()
+    eng.detach()
+    with pytest.raises(ValueError):
+        eng.prepare_gradients()   # nothing accumulated
+
+
+def test_gradproj_engine_matches_reference_run(golden, tmp_path):
+    from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoraEngine
+    model = nn.Sequential()
+    model.add_module("fc1", nn.Linear(10, 20))
+    model.add_module("relu", nn.ReLU())
+    model.add_module("fc2", nn.Linear(20, 5))
+    _load_flat(model, golden["gpmlp_init"])
+    model.cuda()
+    with contextlib.redirect_stdout(io.StringIO()):
+        eng = GradProjLoraEngine(model, proj_layers="fc", proj_rank_total=16, proj_rank_min=2, proj_seed=42,
+                                 proj_dtype="float32", proj_dir=str(tmp_path / "proj"), proj_save_interval=1)
+        eng.attach()
+    dims = [eng.projection_dims[k] for k in sorted(eng.matched_layers)]
+    assert np.array_equal(np.array(dims), golden["gpmlp_dims"])
+    # CUDA generators differ from the CPU ones: load the reference's matrices for a like-for-like check
+    for k in sorted(eng.matched_layers):
+        P_i = torch.from_numpy(golden[f"gpmlp_P_i_{k}"]).cuda()
+        P_o = torch.from_numpy(golden[f"gpmlp_P_o_{k}"]).cuda()
+        eng.projection_matrices[k] = (P_i, P_o)
+        eng.hooks[k].P_i, eng.hooks[k].P_o = P_i, P_o
+    X = torch.from_numpy(golden["gpmlp_X"]).cuda()
+    Y = torch.from_numpy(golden["gpmlp_Y"]).cuda()
+    for it in range(2):
+        model.zero_grad()
+        nn.functional.cross_entropy(model(X), Y).backward()
+        proj = eng.collect_batch(batch_indices=[0, 1, 2, 3])
+        assert proj.shape == (4, eng.total_proj_dim)
+        assert torch.allclose(proj.cpu(), torch.from_numpy(golden["gpmlp_proj"]), rtol=1e-4, atol=1e-5)
+        eng.clear_gradients()
+    eng.flush()
+    files = sorted(os.listdir(tmp_path / "proj"))
+    assert files == ["metadata.json", "proj_iter_000000.pt", "proj_iter_000001.pt"]
+    saved = torch.load(tmp_path / "proj" / "proj_iter_000001.pt")
+    assert saved["iter"] == 1 and saved["batch_size"] == 4 and saved["batch_idx"] == [0, 1, 2, 3]
+    assert torch.allclose(saved["proj"], torch.from_numpy(golden["gpmlp_proj"]), rtol=1e-4, atol=1e-5)
+    eng.cleanup()
+
+
+def test_gradproj_naive_equality_and_non_interference(tmp_path):
+    """The reference's two self-checks (Examples/ghost_gradproj_mlp.py: naive_check, non_interf)."""
+    from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoraEngine
+
+    def build():
+        torch.manual_seed(3)
+        m = nn.Sequential()
+        m.add_module("fc1", nn.Linear(10, 20))
+        m.add_module("relu", nn.ReLU())
+        m.add_module("fc2", nn.Linear(20, 5))
+        return m.cuda()
+
+    X = torch.randn(4, 10, device="cuda")
+    Y = torch.randint(0, 5, (4,), device="cuda")
+    model = build()
+    with contextlib.redirect_stdout(io.StringIO()):
+        eng = GradProjLoraEngine(model, "fc", 16, 2, 42, "float32", str(tmp_path / "p"),
+                                 proj_save_interval=10 ** 9)
+        eng.attach()
+    eng.iteration = 1
+    model.zero_grad()
+    nn.functional.cross_entropy(model(X), Y).backward()
+    ghost = eng.collect_batch().cpu()
+    naive = []
+    for b in range(4):
+        model.zero_grad()
+        nn.functional.cross_entropy(model(X[b:b + 1]), Y[b:b + 1]).backward()
+        parts = []
+        for name in sorted(eng.matched_layers):
+            P_i, P_o = eng.projection_matrices[name]
+            parts.append((P_o @ eng.matched_layers[name].weight.grad @ P_i.t()).reshape(-1))
+        naive.append(torch.cat(parts))
+    naive = torch.stack(naive).cpu()
+    assert torch.allclose(ghost, naive, rtol=1e-4, atol=1e-5)
+    eng.detach()
+
+    # non-interference: identical loss trajectory and weights with and without the engine
+    def run(with_engine):
+        m = build()
+        opt = torch.optim.SGD(m.parameters(), lr=0.01)
+        e = None
+        if with_engine:
+            with contextlib.redirect_stdout(io.StringIO()):
+                e = GradProjLoraEngine(m, "fc", 16, 2, 42, "float32", str(tmp_path / "q"),
+                                       proj_save_interval=10 ** 9)
+                e.attach()
+            e.iteration = 1
+        losses = []
+        for _ in range(10):
+            opt.zero_grad()
+            loss = nn.functional.cross_entropy(m(X), Y)
+            loss.backward()
+            if e is not None:
+                e.collect_batch()
+                e.clear_gradients()
+            opt.step()
+            losses.append(loss.item())
+        if e is not None:
+            e.detach()
+        return losses, [p.detach().cpu().numpy() for p in m.parameters()]
+
+    l0, w0 = run(False)
+    l1, w1 = run(True)
+    assert np.allclose(l0, l1, rtol=1e-5, atol=1e-6)
+    for a, b in zip(w0, w1):
+        assert np.allclose(a, b, rtol=1e-5, atol=1e-6)
+
+
+def test_manager_facade(tmp_path):
+    from ghostsuite_b200.ghostEngines import GhostEngineManager
+    from ghostsuite_b200.workloads import GPT2Like, GPT2Config
+
+    class Cfg:
+        method = "GradDotProd"
+        result_dir = str(tmp_path)
+        val_batch_size = 1
+        dot_prod_save_interval = 2
+
+    torch.manual_seed(0)
+    model = GPT2Like(GPT2Config(vocab_size=101, n_positions=16, n_embd=32, n_layer=1, n_head=2)).cuda()
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    Xv = torch.randint(0, 101, (1, 16)).cuda()
+    with contextlib.redirect_stdout(io.StringIO()):
+        mgr = GhostEngineManager(Cfg, model, opt, {"master_process": True}, val_data=(Xv, Xv))
+    assert mgr.is_active() and mgr.get_method() == "GradDotProd"
+    assert os.path.exists(tmp_path / "grad_dotprods" / "valset.pt")
+    before = model.h[0].mlp.c_fc.weight.detach().clone()
+    for it in range(1, 4):
+        Xt = torch.randint(0, 101, (3, 16)).cuda()
+        mgr.attach_train_batch(Xt, Xt, it, batch_idx=it)
+        Xc, Yc = mgr.prepare_forward_input(Xt, Xt)
+        assert Xc.shape[0] == 4 and torch.equal(Xc[-1:], Xv)
+        loss, _ = model(Xc, labels=Yc)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        mgr.prepare_gradients()
+        opt.step()
+        mgr.aggregate_and_log()
+        mgr.clear_gradients()
+        if mgr.should_save_metrics(it):
+            with contextlib.redirect_stdout(io.StringIO()):
+                mgr.save_metrics(it)
+    assert not torch.equal(before, model.h[0].mlp.c_fc.weight.detach())   # the optimizer got gradients
+    log = torch.load(tmp_path / "grad_dotprods" / "dot_prod_log_iter_2.pt")
+    assert len(log) == 2 and log[0]["dot_product"].shape == (3,) and log[0]["iter_num"] == 1
+    with contextlib.redirect_stdout(io.StringIO()):
+        mgr.cleanup()
+    assert os.path.exists(tmp_path / "grad_dotprods" / "dot_prod_log_iter_-1.pt")
