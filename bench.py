@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Benchmark of the ghost hot path on the GPT-2-small GradDotProd configuration.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the hot path over one synthetic batch: forward and backward of a GPT-2-small
+architecture (12 layers, d=768, 12 heads, vocab 50257, random init, bf16) on cat(32 train, 8 val)
+sequences of 1024 uniform-random token ids, with every hooked layer's dot-product matrix [8 x 32]
+and train gradient produced by the CUDA kernels inside the backward hooks, then
+prepare_gradients, the optimizer step, and aggregate_and_log.  Metric: train tokens per second
+(n_train * T * n_gpus / step time), the definition used for the CPU baseline as well.
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank works on its own 32
+train sequences plus the replicated validation batch (weak scaling); after backward the
+per-parameter dot-product blocks are all-gathered and the train gradients all-reduced over NCCL.
+
+`--impl reference` times the CPU restatement of the reference's own PyTorch path (the reference is
+pure Python and cannot be shipped to the GPU machine) on the host cores, on a bounded sample.
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_TRAIN, N_VAL, SEQ = 32, 8, 1024
+WORKLOAD = "GradDotProd, GPT-2-small architecture (12L, d768, 12H, vocab 50257, tied head), bf16, " \
+           "T=1024, 32 train + 8 val sequences per GPU, full 8x32 dot-product matrix per parameter"
+METRIC = "train tokens/sec (ghost dot-prod + train grad, GPT-2 124M)"
+
+
+# ------------------------------------------------------------------------------------------------
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"tensor": float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", 1400.0))),
+                "hbm": float(d.get("hbm_gbs", 6650.0)), "source": "measured (sustained bf16 GEMM / copy)"}
+    return {"tensor": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.gpu)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons = [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    out["sm_max_mhz"] = float(f[2])
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                      "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            # under load = samples in the upper half of what was seen
+            busy = [x for x in sm if x >= 0.5 * max(sm)]
+            out["sm_mhz"] = statistics.median(busy)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs (oracle port of the reference's PyTorch path)
+# ------------------------------------------------------------------------------------------------
+def cpu_step_factory(n_train: int, n_val: int, seed: int = 0):
+    from ghostsuite_b200.workloads import GPT2Like, GPT2Config
+    from oracle.ghost_engine_cpu import OracleDotProdEngine
+    torch.manual_seed(seed)
+    torch.set_num_threads(os.cpu_count() or 1)
+    model = GPT2Like(GPT2Config()).to(torch.bfloat16)
+    engine = OracleDotProdEngine(model, n_val, use_dummy_bias=True)
+    engine.attach()
+    opt = torch.optim.AdamW([p for n, p in model.named_parameters() if "dummy_bias" not in n], lr=1e-4)
+    g = torch.Generator().manual_seed(seed + 1)
+    ids = torch.randint(0, 50257, (n_train + n_val, SEQ), generator=g)
+
+    def step():
+        loss, _ = model(ids, labels=ids)
+        loss.backward()
+        engine.prepare_gradients()
+        opt.step()
+        total = engine.aggregate()
+        engine.clear_gradients()
+        opt.zero_grad(set_to_none=True)
+        return float(total.sum())
+
+    return step
+
+
+def run_reference_arm(args, rank: int):
+    """The reference's own CPU path, restated (oracle/), on the host cores; rank 0 only."""
+    if rank != 0:
+        return None
+    n_train, n_val = 1, 1
+    step = cpu_step_factory(n_train, n_val)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    val = n_train * SEQ / dt
+    sample = (f"{n_train} train + {n_val} val sequences x {SEQ} tokens per step (full 12-layer model, "
+              "reference's bf16 arithmetic and path rule, AdamW step included)")
+    cores = torch.get_num_threads()
+    return {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "cpu_sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def cpu_baseline_leg():
+    n_train, n_val = 2, 1
+    step = cpu_step_factory(n_train, n_val)
+    step()
+    t0 = time.perf_counter()
+    reps = 2
+    for _ in range(reps):
+        step()
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": n_train * SEQ / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n_train} train + {n_val} val sequences x {SEQ} tokens, full 12-layer model, "
+                      f"{reps} timed steps after 1 warm-up ({dt:.1f} s/step)"}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch.distributed as dist
+    from ghostsuite_b200 import ops, _lib, dist as gdist
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    from ghostsuite_b200.workloads import GPT2Like, GPT2Config
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a B200: the kernels have no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    _lib.check(_lib.load().ghost_device_check())
+
+    torch.manual_seed(0)
+    model = GPT2Like(GPT2Config()).to(torch.bfloat16).to(dev)
+    params = [p for p in model.parameters()]
+    opt = torch.optim.AdamW(params, lr=1e-4, fused=True)
+    engine = GradDotProdEngine(module=model, val_batch_size=N_VAL, loss_reduction="mean", use_dummy_bias=True)
+    engine.attach(opt)
+    group = dist.group.WORLD if world > 1 else None
+
+    g = torch.Generator().manual_seed(1)
+    val_ids = torch.randint(0, 50257, (N_VAL, SEQ), generator=g)              # replicated
+    g.manual_seed(100 + rank)
+    n_batches = 4
+    host_train = [torch.randint(0, 50257, (N_TRAIN, SEQ), generator=g).pin_memory() for _ in range(n_batches)]
+    host_val = val_ids.pin_memory()
+    dev_val = val_ids.to(dev)
+    dev_train = [t.to(dev) for t in host_train]
+    h2d_bytes = host_train[0].numel() * 8
+    d2h_bytes = N_TRAIN * 4 + N_VAL * N_TRAIN * 4
+
+    def step(i: int, from_host: bool):
+        if from_host:
+            x_train = host_train[i % n_batches].to(dev, non_blocking=True)
+        else:
+            x_train = dev_train[i % n_batches]
+        engine.attach_train_batch(x_train, x_train, i, i)
+        x = torch.cat((x_train, dev_val), dim=0)
+        loss, _ = model(x, labels=x)
+        loss.backward()
+        if world > 1:
+            gdist.sync_engine(engine, group)
+        engine.prepare_gradients()
+        opt.step()
+        engine.aggregate_and_log()          # device -> host read of the step's result
+        engine.clear_gradients()
+        opt.zero_grad(set_to_none=True)
+        engine.dot_product_log.clear()
+
+    def timed(from_host: bool, profile: bool):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        l0 = _lib.launch_count()
+        if profile:
+            ops.start_kernel_timing()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(i, from_host)
+        e1.record()
+        torch.cuda.synchronize()
+        prof = ops.stop_kernel_timing() if profile else None
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            dist.barrier()
+        return ms, _lib.launch_count() - l0, prof
+
+    for i in range(args.warmup):
+        step(i, False)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_dev, launches, prof = timed(False, True)
+    ms_e2e, _, _ = timed(True, False)
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.poll_kernel_error()
+
+    if rank != 0:
+        return None
+    tok = N_TRAIN * SEQ * world
+    value = tok * args.steps / (ms_dev * 1e-3)
+    e2e = tok * args.steps / (ms_e2e * 1e-3)
+    peaks = _peaks()
+    roof = dominant_kernel_roofline(prof, peaks)
+    out = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "parallelism": f"train batch sharded over {world} GPU(s), val replicated",
+                   "l2": "working set per step (activations + out-grads, > 10 GB) exceeds the 126 MB L2",
+                   "optimizer": "AdamW (fused)", "path_rule": "cost"},
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roof,
+        "kernel_time_share": prof["share"] if prof else None,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline_leg()
+    return out
+
+
+def dominant_kernel_roofline(prof, peaks):
+    """Roofline of the kernel group with the largest share of library time in the timed region."""
+    if not prof or not prof["ops"]:
+        return None
+    name, rec = max(prof["ops"].items(), key=lambda kv: kv[1]["ms"])
+    calls = max(1, rec["calls"])
+    avg_s = rec["ms"] * 1e-3 / calls
+    if rec["flops"] > 0 and rec["bound"] == "tensor":
+        achieved = rec["flops"] / calls / avg_s / 1e12
+        return {"kernel": name, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor"],
+                "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": None,
+                "launches": calls, "avg_ms": avg_s * 1e3, "peak_source": peaks["source"]}
+    achieved = rec["bytes"] / calls / avg_s / 1e9
+    return {"kernel": name, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+            "frac": achieved / peaks["hbm"], "traffic": None, "launches": calls, "avg_ms": avg_s * 1e3,
+            "peak_source": peaks["source"]}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        line = run_reference_arm(args, rank)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        line = run_ours(args, rank, world, local_rank)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -20,6 +20,53 @@ _F32 = torch.float32
 _arenas: Dict[Tuple[int, int], torch.Tensor] = {}
 
 
+_timing: Optional[list] = None
+
+
+def start_kernel_timing() -> None:
+    """Bracket every library call with CUDA events on the launching stream (opt-in; used by the
+    benchmark to attribute device time and algorithmic work to kernel groups)."""
+    global _timing
+    _timing = []
+
+
+def stop_kernel_timing() -> dict:
+    """Synchronise and return ``{'ops': {name: {calls, ms, flops, bytes, bound}}, 'share': {...}}``."""
+    global _timing
+    records, _timing = _timing or [], None
+    torch.cuda.synchronize()
+    out: Dict[str, dict] = {}
+    for name, bound, flops, nbytes, e0, e1 in records:
+        r = out.setdefault(name, {"calls": 0, "ms": 0.0, "flops": 0.0, "bytes": 0.0, "bound": bound})
+        r["calls"] += 1
+        r["ms"] += e0.elapsed_time(e1)
+        r["flops"] += flops
+        r["bytes"] += nbytes
+    total = sum(r["ms"] for r in out.values()) or 1.0
+    return {"ops": out, "share": {k: round(v["ms"] / total, 4) for k, v in out.items()},
+            "total_ms": total}
+
+
+class _Timed:
+    """``with _Timed(name, bound, flops, bytes):`` around the library calls of one op."""
+
+    def __init__(self, name: str, bound: str, flops: float, nbytes: float):
+        self.rec = (name, bound, float(flops), float(nbytes))
+
+    def __enter__(self):
+        if _timing is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _timing is not None and exc[0] is None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            _timing.append(self.rec + (self.e0, e1))
+        return False
+
+
 def _stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -134,6 +181,10 @@ def gram_dot(A: torch.Tensor, G: torch.Tensor, n_val: int, round_mode: int = 0,
             off_t = arena.plan(N * T * cp * 2)
             ops.append(("copy", x, cp, off_t, 0))
     base = arena.commit()
+    # algorithmic work (the fp32 hi/lo split executes three times this on the tensor pipe)
+    timer = _Timed("ghost_gram_kernel", "tensor", 2.0 * n_train * T * n_val * T * (d + p),
+                   float(A.element_size()) * N * T * (d + p))
+    timer.__enter__()
     ptrs = []
     for kind, x, cp, off_t, off_v in ops:
         if kind == "asis":
@@ -152,6 +203,7 @@ def gram_dot(A: torch.Tensor, G: torch.Tensor, n_val: int, round_mode: int = 0,
     _lib.check(lib.ghost_gram_dot_bf16(at, av, gt, gv, n_train, n_val, T, ka, kg, ld_at, ld_av,
                                        ld_gt, ld_gv, int(round_mode), float(scale), M.data_ptr(),
                                        _stream_ptr()))
+    timer.__exit__(None, None, None)
     return M
 
 
@@ -210,10 +262,11 @@ def wgrad(X: torch.Tensor, Y: torch.Tensor, scale: float, out_dtype: torch.dtype
     off_ws = arena.plan(ws_bytes)
     mat, _ = _xty_operands(lib, arena, X, Y, S, T)
     base = arena.commit()
-    xp, yp, ldx, ldy, T_eff = mat(base)
-    _lib.check(lib.ghost_wgrad_bf16(xp, yp, S * T_eff, m, n, ldx, ldy, float(scale),
-                                    1 if accumulate else 0, out.data_ptr(), _dt_flag(out),
-                                    base + off_ws, ws_bytes, _stream_ptr()))
+    with _Timed("xty_gemm_kernel[wgrad]", "tensor", 2.0 * S * T * m * n, 2.0 * S * T * (m + n)):
+        xp, yp, ldx, ldy, T_eff = mat(base)
+        _lib.check(lib.ghost_wgrad_bf16(xp, yp, S * T_eff, m, n, ldx, ldy, float(scale),
+                                        1 if accumulate else 0, out.data_ptr(), _dt_flag(out),
+                                        base + off_ws, ws_bytes, _stream_ptr()))
     return out
 
 
@@ -259,13 +312,16 @@ def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float
         ws_bytes = int(lib.ghost_persample_workspace_bytes(nv, m, n, v_f32))
         off_ws = arena.plan(ws_bytes)
         base = arena.commit()
-        xp, yp, ldx, ldy, T_eff = mat(base)
         do_grad = want_grad and v0 == 0
         Mc = M if (v0 == 0 and v1 == n_val) else torch.empty((nv, n_train), dtype=_F32, device=X.device)
-        _lib.check(lib.ghost_persample_dot_bf16(
-            xp, yp, n_train, nv, T_eff, m, n, ldx, ldy, float(dot_scale), Mc.data_ptr(), v_f32,
-            grad.data_ptr() if do_grad else None, _dt_flag(grad) if do_grad else 0,
-            float(grad_scale), 0, base + off_ws, ws_bytes, _stream_ptr()))
+        with _Timed("xty_gemm_kernel[persample]", "tensor",
+                    2.0 * (n_train + nv) * T * m * n + 2.0 * nv * n_train * m * n,
+                    2.0 * (n_train + nv) * T * (m + n)):
+            xp, yp, ldx, ldy, T_eff = mat(base)
+            _lib.check(lib.ghost_persample_dot_bf16(
+                xp, yp, n_train, nv, T_eff, m, n, ldx, ldy, float(dot_scale), Mc.data_ptr(), v_f32,
+                grad.data_ptr() if do_grad else None, _dt_flag(grad) if do_grad else 0,
+                float(grad_scale), 0, base + off_ws, ws_bytes, _stream_ptr()))
         if Mc is not M:
             M[v0:v1].copy_(Mc)
     return M, grad
@@ -281,7 +337,8 @@ def colsum(G: torch.Tensor) -> torch.Tensor:
     G = _as3d(G)
     N, T, p = G.shape
     out = torch.empty((N, p), dtype=_F32, device=G.device)
-    _lib.check(lib.ghost_colsum(G.data_ptr(), _dt_flag(G), N, T, p, p, out.data_ptr(), _stream_ptr()))
+    with _Timed("colsum_kernel", "hbm", 0.0, float(N) * T * p * G.element_size()):
+        _lib.check(lib.ghost_colsum(G.data_ptr(), _dt_flag(G), N, T, p, p, out.data_ptr(), _stream_ptr()))
     return out
 
 
@@ -295,8 +352,9 @@ def small_gram(X: torch.Tensor, n_val: int, scale: float = 1.0) -> torch.Tensor:
     if n_train <= 0:
         raise ValueError("No training samples to compute dot product, check batch sizes.")
     M = torch.empty((n_val, n_train), dtype=_F32, device=X.device)
-    _lib.check(lib.ghost_small_gram_f32(X.data_ptr(), n_train, n_val, X.shape[1], float(scale),
-                                        M.data_ptr(), _stream_ptr()))
+    with _Timed("small_gram_kernel", "hbm", 0.0, 4.0 * X.numel()):
+        _lib.check(lib.ghost_small_gram_f32(X.data_ptr(), n_train, n_val, X.shape[1], float(scale),
+                                            M.data_ptr(), _stream_ptr()))
     return M
 
 
@@ -310,8 +368,9 @@ def rows_sum(X: torch.Tensor, n_rows: int, scale: float, out_dtype: torch.dtype,
     if out is None:
         out = torch.empty((X.shape[1],), dtype=out_dtype, device=X.device)
         accumulate = False
-    _lib.check(lib.ghost_rows_sum(X.data_ptr(), int(n_rows), X.shape[1], float(scale), out.data_ptr(),
-                                  _dt_flag(out), 1 if accumulate else 0, _stream_ptr()))
+    with _Timed("rows_sum_kernel", "hbm", 0.0, 4.0 * n_rows * X.shape[1]):
+        _lib.check(lib.ghost_rows_sum(X.data_ptr(), int(n_rows), X.shape[1], float(scale), out.data_ptr(),
+                                      _dt_flag(out), 1 if accumulate else 0, _stream_ptr()))
     return out
 
 
@@ -329,8 +388,9 @@ def layernorm_persample(A: torch.Tensor, G: torch.Tensor, eps: float
         raise ValueError("LayerNorm input and out-grad shapes differ")
     gw = torch.empty((N, F), dtype=_F32, device=A.device)
     gb = torch.empty((N, F), dtype=_F32, device=A.device)
-    _lib.check(lib.ghost_layernorm_persample(A.data_ptr(), G.data_ptr(), _dt_flag(A), N, T, F,
-                                             float(eps), gw.data_ptr(), gb.data_ptr(), _stream_ptr()))
+    with _Timed("layernorm_persample_kernel", "hbm", 0.0, 2.0 * N * T * F * A.element_size() + 8.0 * N * F):
+        _lib.check(lib.ghost_layernorm_persample(A.data_ptr(), G.data_ptr(), _dt_flag(A), N, T, F,
+                                                 float(eps), gw.data_ptr(), gb.data_ptr(), _stream_ptr()))
     return gw, gb
 
 
@@ -361,9 +421,10 @@ def embedding_dot(ids: torch.Tensor, G: torch.Tensor, n_val: int, vocab: int,
     ws_bytes = int(lib.ghost_embedding_dot_workspace_bytes(n_val, T, vocab))
     off = arena.plan(ws_bytes)
     base = arena.commit()
-    _lib.check(lib.ghost_embedding_dot(ids.data_ptr(), G.data_ptr(), _dt_flag(G), n_train, n_val, T,
-                                       d, int(vocab), float(scale), M.data_ptr(), base + off,
-                                       ws_bytes, _stream_ptr()))
+    with _Timed("emb_dot_kernel", "hbm", 0.0, float(N) * T * d * G.element_size() + 8.0 * N * T):
+        _lib.check(lib.ghost_embedding_dot(ids.data_ptr(), G.data_ptr(), _dt_flag(G), n_train, n_val, T,
+                                           d, int(vocab), float(scale), M.data_ptr(), base + off,
+                                           ws_bytes, _stream_ptr()))
     return M
 
 
@@ -385,10 +446,12 @@ def embedding_wgrad(ids: torch.Tensor, G: torch.Tensor, n_train: int, vocab: int
     ws_bytes = int(lib.ghost_embedding_wgrad_workspace_bytes(n_train, T, vocab))
     off = arena.plan(ws_bytes)
     base = arena.commit()
-    _lib.check(lib.ghost_embedding_wgrad(ids.data_ptr(), G.data_ptr(), _dt_flag(G), n_train, T, d,
-                                         int(vocab), float(pre_scale), float(divisor),
-                                         1 if accumulate else 0, out.data_ptr(), base + off,
-                                         ws_bytes, _stream_ptr()))
+    with _Timed("emb_segsum_kernel", "hbm", 0.0,
+                (float(n_train) * T * d + float(vocab) * d) * G.element_size() + 8.0 * n_train * T):
+        _lib.check(lib.ghost_embedding_wgrad(ids.data_ptr(), G.data_ptr(), _dt_flag(G), n_train, T, d,
+                                             int(vocab), float(pre_scale), float(divisor),
+                                             1 if accumulate else 0, out.data_ptr(), base + off,
+                                             ws_bytes, _stream_ptr()))
     return out
 
 
@@ -436,6 +499,10 @@ def gradproj_dense(G: torch.Tensor, A: torch.Tensor, P_r: torch.Tensor, P_c: tor
         else:
             plans.append(("copy", x, cp, arena.plan(B * T * cp * 2)))
     base = arena.commit()
+    timer = _Timed("gradproj_kernel", "hbm", 2.0 * B * T * (n_r * k_r + n_c * k_c + k_r * k_c),
+                   float(B) * T * (n_r + n_c) * G.element_size() + 2.0 * (k_r * n_r + k_c * n_c)
+                   + 4.0 * B * k_r * k_c)
+    timer.__enter__()
     ptrs = []
     for kind, x, cp, off in plans:
         if kind == "asis":
@@ -453,6 +520,7 @@ def gradproj_dense(G: torch.Tensor, A: torch.Tensor, P_r: torch.Tensor, P_c: tor
                                              P_c.data_ptr(), int(k_r), int(k_c), P_r.shape[1],
                                              P_c.shape[1], float(scale), out.data_ptr(),
                                              out.stride(0), _stream_ptr()))
+    timer.__exit__(None, None, None)
     return out
 
 

@@ -243,13 +243,15 @@ def test_gradproj_golden(golden):
     o.gradproj_dense(G.cuda(), A.cuda(), o.prepare_projection(P_o.cuda(), True),
                      o.prepare_projection(P_i.cuda(), True), 6, 4, 8.0, out)
     after()
-    assert torch.allclose(out.cpu().reshape(8, 6, 4), torch.from_numpy(golden["gp_linear"]), rtol=1e-4, atol=1e-5)
+    assert O.rel_fro(out.reshape(8, 6, 4), torch.from_numpy(golden["gp_linear"])) < 1e-4
+    assert torch.allclose(out.cpu().reshape(8, 6, 4), torch.from_numpy(golden["gp_linear"]), rtol=1e-3, atol=1e-4)
     # Conv1D: the out-grad is projected with P_i, the activations with P_o -> [k_i, k_o]
     P_i, P_o = torch.from_numpy(golden["gp_c1d_P_i"]), torch.from_numpy(golden["gp_c1d_P_o"])
     o.gradproj_dense(G.cuda(), A.cuda(), o.prepare_projection(P_i.cuda(), True),
                      o.prepare_projection(P_o.cuda(), True), 4, 6, 8.0, out)
     after()
-    assert torch.allclose(out.cpu().reshape(8, 4, 6), torch.from_numpy(golden["gp_c1d"]), rtol=1e-4, atol=1e-5)
+    assert O.rel_fro(out.reshape(8, 4, 6), torch.from_numpy(golden["gp_c1d"])) < 1e-4
+    assert torch.allclose(out.cpu().reshape(8, 4, 6), torch.from_numpy(golden["gp_c1d"]), rtol=1e-3, atol=1e-4)
 
 
 def test_error_codes_are_python_exceptions():
