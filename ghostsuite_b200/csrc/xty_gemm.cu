@@ -10,11 +10,16 @@
 //                   CTAs; partial tiles are added into an fp32 workspace with red.global.add.
 //   kEpiStore       per-validation-sample weight gradients V[v] written to a workspace
 //                   (per-sample form of :133-134).
-//   kEpiDot         per-train-sample weight-gradient tile formed in TMEM, dotted against the
-//                   n_val stored validation gradients in the epilogue (:135, for every validation
-//                   sample separately) and, in the same pass, added into the fp32 train-gradient
-//                   workspace -- so the per-sample gradients never reach HBM and the train
-//                   gradient costs no extra tensor work.
+//   kEpiDot         per-train-sample weight-gradient tiles dotted against the n_val stored
+//                   validation gradients in the epilogue (:135, for every validation sample
+//                   separately).  A CTA walks consecutive train samples of one output tile and
+//                   never clears its two TMEM accumulators in between (samples alternate between
+//                   them): each accumulator holds a running sum of per-sample gradients, the
+//                   epilogue dots that running sum with the validation tiles and subtracts the
+//                   previous value of the same dot, which is the dot of the newest sample alone.
+//                   When the CTA leaves the tile the running sums ARE the train-gradient tile and
+//                   are added to the fp32 workspace once -- so per-sample gradients never reach
+//                   HBM and the train gradient costs no extra tensor work and almost no atomics.
 //
 // Linear weights are [d_out, d_in]: X = G (out-grad), Y = A (activations).  HF Conv1D weights are
 // [d_in, d_out]: X = A, Y = G.  No transposes are materialised.
@@ -37,6 +42,7 @@ struct XtyParams {
   long long T;               // token rows per sample
   int k_splits;              // kEpiAccumulate: CTAs sharing one output tile
   int kb_per_split;          // 64-row blocks per split
+  int units_per_cta;         // each CTA takes a contiguous range of units
   // kEpiAccumulate / kEpiDot: fp32 [m_cols, ld_acc] accumulation workspace (may be null for Dot)
   float* acc_ws;
   long long ld_acc;
@@ -54,12 +60,30 @@ struct XtyCfg {
   static constexpr int BM = 128, BN = 256, BK = 64;
   static constexpr int kStageBytes = (BM + BN) * BK * 2;   // 48 KB
   static constexpr int kStages = 4;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
   static constexpr int kMaxVal = 32;
+  static constexpr int kPrevBytes = 2 * kMaxVal * 128 * 4;   // previous partial dots, per thread
+  static constexpr int kSmemBytes = kStages * kStageBytes + kPrevBytes + 1024 + 256;
 };
 
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+// 32 consecutive accumulator columns of one output row -> fp32 workspace (16-byte aligned rows)
+__device__ __forceinline__ void red_add_row32(float* dst, const uint32_t (&r)[32], int ncol) {
+  if (ncol >= 32) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      red_add_f32x4(dst + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                    __uint_as_float(r[j + 3]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncol) red_add_f32(dst + j, __uint_as_float(r[j]));
+  }
 }
 
 __global__ void __launch_bounds__(192, 1)
@@ -70,7 +94,8 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  float* s_prev = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);   // [2][kMaxVal][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kPrevBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* acc_full = bars + 2 * kStages;     // [2]
@@ -85,6 +110,13 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   // neighbourhood reuse the same validation-gradient tiles from L2.
   const long long units = static_cast<long long>(tiles_mn) * p.samples * p.k_splits;
   const int kb_sample = static_cast<int>((p.T + BK - 1) / BK);
+  const long long u_begin = static_cast<long long>(blockIdx.x) * p.units_per_cta;
+  const long long u_end = (u_begin + p.units_per_cta < units) ? u_begin + p.units_per_cta : units;
+  const int inner_units = p.samples * p.k_splits;
+  // kEpiDot: an accumulator keeps summing while the CTA stays on one output tile.  `fresh` = first
+  // use of this accumulator (parity) on the tile, `last` = last use before the CTA moves on.
+  auto run_fresh = [&](long long u) { return (u - 2 < u_begin) || ((u - 2) / inner_units != u / inner_units); };
+  auto run_last = [&](long long u) { return (u + 2 >= u_end) || ((u + 2) / inner_units != u / inner_units); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -128,7 +160,7 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      for (long long u = u_begin; u < u_end && ok; ++u) {
         int tile, sample, kb0, kb1;
         decode(u, tile, sample, kb0, kb1);
         const int m0 = (tile / p.n_tiles) * BM;
@@ -157,12 +189,13 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      for (long long u = u_begin; u < u_end && ok; ++u) {
         int tile, sample, kb0, kb1;
         decode(u, tile, sample, kb0, kb1);
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.err, 512)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t dst = tmem_base + acc * BN;
+        const bool keep = (p.mode == kEpiDot) && !run_fresh(u);   // continue the running sum
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 513)) { ok = false; break; }
           tc_fence_after_sync();
@@ -173,7 +206,7 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             umma_bf16(dst, adesc + k * (16 * 128 / 16), bdesc + k * (16 * 128 / 16), idesc,
-                      (kb == kb0 && k == 0) ? 0u : 1u);
+                      (kb == kb0 && k == 0 && !keep) ? 0u : 1u);
           umma_commit(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -186,7 +219,7 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    for (long long u = blockIdx.x; u < units; u += gridDim.x) {
+    for (long long u = u_begin; u < u_end; ++u) {
       int tile, sample, kb0, kb1;
       decode(u, tile, sample, kb0, kb1);
       const int m0 = (tile / p.n_tiles) * BM;
@@ -205,12 +238,8 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
           uint32_t r[32];
           tmem_ld32(t_acc + c0, r);
           tmem_ld_wait();
-          if (m_ok && !empty_k) {
-            float* dst = p.acc_ws + static_cast<long long>(m) * p.ld_acc + n0 + c0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n0 + c0 + j < p.n_cols) red_add_f32(dst + j, __uint_as_float(r[j]));
-          }
+          if (m_ok && !empty_k)
+            red_add_row32(p.acc_ws + static_cast<long long>(m) * p.ld_acc + n0 + c0, r, p.n_cols - (n0 + c0));
         }
       } else if (p.mode == kEpiStore) {
         const long long vbase = (static_cast<long long>(sample) * p.m_cols + m) * p.ld_v;
@@ -241,20 +270,18 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
         float dots[XtyCfg::kMaxVal];
 #pragma unroll
         for (int v = 0; v < XtyCfg::kMaxVal; ++v) dots[v] = 0.f;
+        const bool fresh = run_fresh(u);
+        const bool flush = run_last(u) && (p.acc_ws != nullptr);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           if (n0 + c0 >= p.n_cols) break;
           uint32_t r[32];
           tmem_ld32(t_acc + c0, r);
           tmem_ld_wait();
-          if (m_ok && !empty_k) {
+          if (m_ok) {
             const int ncol = min(32, p.n_cols - (n0 + c0));
-            if (p.acc_ws) {
-              float* dst = p.acc_ws + static_cast<long long>(m) * p.ld_acc + n0 + c0;
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < ncol) red_add_f32(dst + j, __uint_as_float(r[j]));
-            }
+            if (flush)   // the running sum of this accumulator is its share of the train gradient
+              red_add_row32(p.acc_ws + static_cast<long long>(m) * p.ld_acc + n0 + c0, r, ncol);
 #pragma unroll
             for (int v = 0; v < XtyCfg::kMaxVal; ++v) {
               if (v >= p.n_val) break;
@@ -300,7 +327,10 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
 #pragma unroll
         for (int v = 0; v < XtyCfg::kMaxVal; ++v) {
           if (v >= p.n_val) break;
-          float s = dots[v];
+          // dots[v] is <V_v, running sum>; minus its previous value = <V_v, newest sample's tile>
+          float* prev = s_prev + (acc * XtyCfg::kMaxVal + v) * 128 + threadIdx.x;
+          float s = fresh ? dots[v] : dots[v] - *prev;
+          *prev = dots[v];
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
           if (lane == 0 && s != 0.f)
@@ -338,7 +368,7 @@ __global__ void xty_finalize_kernel(const float* __restrict__ ws, long long ld_w
   }
 }
 
-static int launch_xty(const CUtensorMap& tx, const CUtensorMap& ty, const XtyParams& p,
+static int launch_xty(const CUtensorMap& tx, const CUtensorMap& ty, XtyParams p,
                       const DeviceState* ds, cudaStream_t st) {
   static bool attr_set[64] = {};
   if (!attr_set[ds->device]) {
@@ -347,7 +377,9 @@ static int launch_xty(const CUtensorMap& tx, const CUtensorMap& ty, const XtyPar
     attr_set[ds->device] = true;
   }
   const long long units = static_cast<long long>(p.m_tiles) * p.n_tiles * p.samples * p.k_splits;
-  const int grid = static_cast<int>(units < ds->sm_count ? units : ds->sm_count);
+  int grid = static_cast<int>(units < ds->sm_count ? units : ds->sm_count);
+  p.units_per_cta = static_cast<int>((units + grid - 1) / grid);
+  grid = static_cast<int>((units + p.units_per_cta - 1) / p.units_per_cta);
   xty_gemm_kernel<<<grid, 192, XtyCfg::kSmemBytes, st>>>(tx, ty, p);
   count_launch();
   return post_launch("xty_gemm_kernel");
