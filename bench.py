@@ -305,6 +305,106 @@ def dominant_kernel_roofline(prof, peaks):
             "peak_source": peaks["source"]}
 
 
+# ------------------------------------------------------------------------------------------------
+# kernel-level microbenchmarks (used for the ncu captures and the per-kernel roofline table)
+# ------------------------------------------------------------------------------------------------
+KERNEL_CASES = {
+    # name: (kind, dict of sizes)
+    "gram_T128": ("gram", dict(n_t=256, n_v=32, T=128, d=4096, p=11008)),       # single-layer config, T = 128
+    "gram_T512": ("gram", dict(n_t=256, n_v=32, T=512, d=4096, p=11008)),
+    "gram_small": ("gram", dict(n_t=64, n_v=8, T=256, d=2048, p=4096)),          # sized for an ncu capture
+    "persample_cfc": ("persample", dict(n_t=32, n_v=8, T=1024, d=768, p=3072)),  # GPT-2 mlp.c_fc
+    "persample_T512": ("persample", dict(n_t=256, n_v=32, T=512, d=4096, p=11008)),
+    "persample_T2048": ("persample", dict(n_t=64, n_v=32, T=2048, d=4096, p=11008)),
+    "wgrad_cfc": ("wgrad", dict(n_t=32, n_v=8, T=1024, d=768, p=3072)),
+    "wgrad_big": ("wgrad", dict(n_t=64, n_v=0, T=1024, d=4096, p=11008)),
+    "layernorm_768": ("layernorm", dict(N=40, T=1024, F=768)),
+    "colsum_3072": ("colsum", dict(N=40, T=1024, p=3072)),
+    "embedding_wte": ("embedding", dict(n_t=32, n_v=8, T=1024, d=768, vocab=50257)),
+    "gradproj_llama_q": ("gradproj", dict(B=8, T=4096, n_i=4096, n_o=4096, k=64)),
+    "gradproj_llama_gate": ("gradproj", dict(B=8, T=4096, n_i=4096, n_o=14336, k=64)),
+    "gradproj_pythia_fc": ("gradproj", dict(B=16, T=2048, n_i=1024, n_o=4096, k=32)),
+    "gradproj_small": ("gradproj", dict(B=4, T=2048, n_i=2048, n_o=4096, k=64)),   # sized for an ncu capture
+}
+
+
+def run_kernels(args):
+    """Times single kernels on seeded N(0,1)/sqrt(d) inputs that exceed the L2 (or with an L2 flush
+    between iterations), CUDA events on the launching stream.  Prints one JSON object."""
+    from ghostsuite_b200 import ops, _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    burst = peaks["tensor"]
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        burst = float(json.load(open(path)).get("bf16_tflops", burst))
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    names = args.only.split(",") if args.only else list(KERNEL_CASES)
+    g = torch.Generator(device=dev).manual_seed(0)
+    results = {}
+    for name in names:
+        kind, c = KERNEL_CASES[name]
+
+        def rnd(*shape, scale=1.0, dtype=torch.bfloat16):
+            return (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
+
+        if kind in ("gram", "persample", "wgrad"):
+            N = c["n_t"] + c["n_v"]
+            A = rnd(N, c["T"], c["d"], scale=c["d"] ** -0.5)
+            G = rnd(N, c["T"], c["p"], scale=c["p"] ** -0.5)
+            if kind == "gram":
+                fn = lambda: ops.gram_dot(A, G, c["n_v"])
+            elif kind == "persample":
+                fn = lambda: ops.persample_dot(G, A, c["n_v"], want_grad=True, grad_scale=1.0, grad_dtype=torch.bfloat16)
+            else:
+                fn = lambda: ops.wgrad(G[:c["n_t"]], A[:c["n_t"]], 1.0, torch.bfloat16)
+        elif kind == "layernorm":
+            A = rnd(c["N"], c["T"], c["F"]); G = rnd(c["N"], c["T"], c["F"])
+            fn = lambda: ops.layernorm_persample(A, G, 1e-5)
+        elif kind == "colsum":
+            G = rnd(c["N"], c["T"], c["p"])
+            fn = lambda: ops.colsum(G)
+        elif kind == "embedding":
+            N = c["n_t"] + c["n_v"]
+            ids = torch.randint(0, c["vocab"], (N, c["T"]), generator=g, device=dev)
+            G = rnd(N, c["T"], c["d"])
+            fn = lambda: (ops.embedding_dot(ids, G, c["n_v"], c["vocab"]),
+                          ops.embedding_wgrad(ids, G, c["n_t"], c["vocab"], float(N), float(c["n_t"])))
+        elif kind == "gradproj":
+            A = rnd(c["B"], c["T"], c["n_i"], scale=c["n_i"] ** -0.5)
+            G = rnd(c["B"], c["T"], c["n_o"], scale=c["n_o"] ** -0.5)
+            P_i = ops.prepare_projection(torch.randn(c["k"], c["n_i"], generator=g, device=dev) / c["k"] ** 0.5, False)
+            P_o = ops.prepare_projection(torch.randn(c["k"], c["n_o"], generator=g, device=dev) / c["k"] ** 0.5, False)
+            out = torch.empty(c["B"], c["k"] * c["k"], device=dev)
+            fn = lambda: ops.gradproj_dense(G, A, P_o, P_i, c["k"], c["k"], float(c["B"]), out)
+        for _ in range(max(1, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        ops.start_kernel_timing()
+        for _ in range(args.steps):
+            flush_buf.zero_()            # evict the L2 between timed iterations
+            fn()
+        prof = ops.stop_kernel_timing()
+        _lib.poll_kernel_error()
+        entry = {"sizes": c, "ops": {}}
+        for op_name, rec in prof["ops"].items():
+            ms = rec["ms"] / rec["calls"]
+            e = {"avg_ms": ms, "calls": rec["calls"]}
+            if rec["bound"] == "tensor":
+                tf = rec["flops"] / rec["calls"] / (ms * 1e-3) / 1e12
+                e.update(bound="tensor", achieved_tflops=tf, frac_of_measured_burst=tf / burst)
+            else:
+                gb = rec["bytes"] / rec["calls"] / (ms * 1e-3) / 1e9
+                e.update(bound="hbm", achieved_gbs=gb, frac_of_measured=gb / peaks["hbm"])
+            entry["ops"][op_name] = e
+        results[name] = entry
+        del fn
+        torch.cuda.empty_cache()
+    print(json.dumps({"mode": "kernels", "peaks": {"tensor_burst_tflops": burst, "hbm_gbs": peaks["hbm"],
+                                                    "source": peaks["source"]}, "results": results}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -312,11 +412,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="step", choices=["step", "kernels"],
+                    help="step: the driver's benchmark line; kernels: per-kernel microbenchmarks")
+    ap.add_argument("--only", default="", help="kernels mode: comma-separated case names")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    if args.mode == "kernels":
+        run_kernels(args)
+        return
     if args.impl == "reference":
         line = run_reference_arm(args, rank)
         if line is not None:

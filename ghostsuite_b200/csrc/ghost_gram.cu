@@ -65,6 +65,18 @@ ghost_gram_kernel(const __grid_constant__ CUtensorMap tm_at, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.m_tiles * p.n_tiles;
+  // Tiles are walked in bands of kBandM train tiles: inside a band the train index runs fastest, so
+  // the ~148 tiles in flight at any time cover a near-square (train x val) patch and every operand
+  // slice is fetched from HBM about once per patch and then shared through the L2.
+  constexpr int kBandM = 16;
+  auto tile_coords = [&](int tile, int& tm, int& tn) {
+    const int band = tile / (kBandM * p.n_tiles);
+    const int first = band * kBandM;
+    const int rows = (p.m_tiles - first < kBandM) ? p.m_tiles - first : kBandM;
+    const int local = tile - band * kBandM * p.n_tiles;
+    tm = first + local % rows;
+    tn = local / rows;
+  };
   const int kb_a = (p.ka + BK - 1) / BK;
   const int kb_total = kb_a + (p.kg + BK - 1) / BK;
 
@@ -102,8 +114,10 @@ ghost_gram_kernel(const __grid_constant__ CUtensorMap tm_at, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / p.n_tiles) * BM;
-        const int n0 = (tile % p.n_tiles) * BN;
+        int tm, tn;
+        tile_coords(tile, tm, tn);
+        const int m0 = tm * BM;
+        const int n0 = tn * BN;
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 401)) { ok = false; break; }
           uint8_t* st = smem + stage * Cfg::kStageBytes;
@@ -157,8 +171,10 @@ ghost_gram_kernel(const __grid_constant__ CUtensorMap tm_at, const __grid_consta
     uint32_t acc_phase = 0;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const long long m0 = static_cast<long long>(tile / p.n_tiles) * BM;
-      const long long n0 = static_cast<long long>(tile % p.n_tiles) * BN;
+      int tm, tn;
+      tile_coords(tile, tm, tn);
+      const long long m0 = static_cast<long long>(tm) * BM;
+      const long long n0 = static_cast<long long>(tn) * BN;
       if (!mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag, p.err, 104)) break;
       tc_fence_after_sync();
 

@@ -149,14 +149,11 @@ __global__ void colsum_kernel(const T* __restrict__ G, long long Tn, int cols, l
 template <typename T, int NCHUNK>
 __global__ void __launch_bounds__(256)
 layernorm_persample_kernel(const T* __restrict__ A, const T* __restrict__ G, long long Tn, int F,
-                           float eps, float* __restrict__ gw, float* __restrict__ gb, int t_splits) {
-  extern __shared__ float sm[];   // [2][F]
-  float* s_gw = sm;
-  float* s_gb = sm + F;
+                           float eps, float* __restrict__ gw, float* __restrict__ gb,
+                           float* __restrict__ part, int t_splits) {
+  extern __shared__ float sm[];   // [8 warps][2][F]
   const int n = blockIdx.y, split = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < 2 * F; i += blockDim.x) sm[i] = 0.f;
-  __syncthreads();
   const long long per = (Tn + t_splits - 1) / t_splits;
   const long long t0 = split * per;
   const long long t1 = (t0 + per < Tn) ? t0 + per : Tn;
@@ -168,20 +165,23 @@ layernorm_persample_kernel(const T* __restrict__ A, const T* __restrict__ G, lon
   const float invF = 1.f / static_cast<float>(F);
   for (long long t = t0 + warp; t < t1; t += 8) {
     const long long off = (static_cast<long long>(n) * Tn + t) * F;
-    float x[NCHUNK][8];
+    float x[NCHUNK][8], g[NCHUNK][8];
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) {
+    for (int i = 0; i < NCHUNK; ++i) {       // both rows are requested before any arithmetic
       const int f = (i * 32 + lane) * 8;
       if (f < F) {
         Vec8<T>::load(A + off + f, x[i]);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) s += x[i][j];
+        Vec8<T>::load(G + off + f, g[i]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[i][j] = 0.f;
+        for (int j = 0; j < 8; ++j) { x[i][j] = 0.f; g[i][j] = 0.f; }
       }
     }
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += x[i][j];
     const float mean = warp_sum(s) * invF;
     float q = 0.f;
 #pragma unroll
@@ -194,35 +194,48 @@ layernorm_persample_kernel(const T* __restrict__ A, const T* __restrict__ G, lon
     }
     const float rstd = rsqrtf(warp_sum(q) * invF + eps);
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) {
-      const int f = (i * 32 + lane) * 8;
-      if (f < F) {
-        float g[8];
-        Vec8<T>::load(G + off + f, g);
+    for (int i = 0; i < NCHUNK; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          aw[i][j] = fmaf(g[j], x[i][j] * rstd, aw[i][j]);
-          ab[i][j] += g[j];
-        }
+      for (int j = 0; j < 8; ++j) {
+        aw[i][j] = fmaf(g[i][j], x[i][j] * rstd, aw[i][j]);
+        ab[i][j] += g[i][j];
       }
-    }
   }
+  float* mine = sm + static_cast<size_t>(warp) * 2 * F;
 #pragma unroll
   for (int i = 0; i < NCHUNK; ++i) {
     const int f = (i * 32 + lane) * 8;
     if (f < F) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        atomicAdd(&s_gw[f + j], aw[i][j]);
-        atomicAdd(&s_gb[f + j], ab[i][j]);
-      }
+      for (int j = 0; j < 8; ++j) { mine[f + j] = aw[i][j]; mine[F + f + j] = ab[i][j]; }
     }
   }
   __syncthreads();
-  for (int f = threadIdx.x; f < F; f += blockDim.x) {
-    const long long o = static_cast<long long>(n) * F + f;
-    if (t_splits > 1) { atomicAdd(&gw[o], s_gw[f]); atomicAdd(&gb[o], s_gb[f]); }
-    else { gw[o] = s_gw[f]; gb[o] = s_gb[f]; }
+  for (int f = threadIdx.x; f < 2 * F; f += blockDim.x) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) v += sm[static_cast<size_t>(w) * 2 * F + f];
+    if (t_splits > 1) {
+      part[(static_cast<long long>(split) * gridDim.y + n) * 2 * F + f] = v;
+    } else if (f < F) {
+      gw[static_cast<long long>(n) * F + f] = v;
+    } else {
+      gb[static_cast<long long>(n) * F + f - F] = v;
+    }
+  }
+}
+
+// second stage: sum the per-split partials in a fixed order (deterministic)
+__global__ void layernorm_reduce_kernel(const float* __restrict__ part, int N, int F, int t_splits,
+                                        float* __restrict__ gw, float* __restrict__ gb) {
+  const long long total = static_cast<long long>(N) * 2 * F;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < t_splits; ++s) v += part[static_cast<long long>(s) * total + i];
+    const int n = static_cast<int>(i / (2 * F)), f = static_cast<int>(i % (2 * F));
+    if (f < F) gw[static_cast<long long>(n) * F + f] = v;
+    else gb[static_cast<long long>(n) * F + f - F] = v;
   }
 }
 
@@ -372,9 +385,61 @@ extern "C" int ghost_colsum(const void* G, int is_f32, int N, long long T, int c
   return post_launch("colsum_kernel");
 }
 
+static int ln_splits(long long Tn, int N, int sm_count) {
+  long long want = (2ll * sm_count + N - 1) / N;
+  const long long maxs = (Tn + 63) / 64;
+  if (want > maxs) want = maxs;
+  if (want < 1) want = 1;
+  if (want > 65535) want = 65535;
+  return static_cast<int>(want);
+}
+
+extern "C" long long ghost_layernorm_workspace_bytes(int N, long long T, int F) {
+  // upper bound over devices: at most 1024 splits are ever used
+  long long splits = (T + 63) / 64;
+  if (splits > 1024) splits = 1024;
+  return splits * N * 2 * F * 4 + 256;
+}
+
 template <typename T>
 static int launch_ln(const T* A, const T* G, int N, long long Tn, int F, float eps, float* gw, float* gb,
-                     const DeviceState* ds, cudaStream_t st) {
+                     float* ws, long long ws_bytes, const DeviceState* ds, cudaStream_t st) {
+  const bool fast = (F % 8 == 0) && (F <= 1024) &&
+                    ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0);
+  if (fast) {
+    int splits = ln_splits(Tn, N, ds->sm_count);
+    if (splits > 1024) splits = 1024;
+    if (splits > 1) {
+      GB_REQUIRE(ws && ws_bytes >= static_cast<long long>(splits) * N * 2 * F * 4,
+                 "ghost_layernorm_persample: workspace too small");
+    }
+    dim3 grid(splits, N);
+    const size_t smem = sizeof(float) * 8 * 2 * static_cast<size_t>(F);
+    const int nchunk = (F + 255) / 256;
+#define GB_LN_LAUNCH(NC)                                                                              \
+    do {                                                                                              \
+      if (smem > 48 * 1024)                                                                           \
+        GB_CUDA_OK(cudaFuncSetAttribute(layernorm_persample_kernel<T, NC>,                            \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));     \
+      layernorm_persample_kernel<T, NC><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, ws, splits); \
+    } while (0)
+    switch (nchunk) {
+      case 1: GB_LN_LAUNCH(1); break;
+      case 2: GB_LN_LAUNCH(2); break;
+      case 3: GB_LN_LAUNCH(3); break;
+      default: GB_LN_LAUNCH(4); break;
+    }
+#undef GB_LN_LAUNCH
+    count_launch();
+    int rc = post_launch("layernorm_persample_kernel");
+    if (rc != GHOST_OK || splits == 1) return rc;
+    const long long total = static_cast<long long>(N) * 2 * F;
+    long long blocks = (total + 255) / 256;
+    if (blocks > ds->sm_count * 8) blocks = ds->sm_count * 8;
+    layernorm_reduce_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(ws, N, F, splits, gw, gb);
+    count_launch();
+    return post_launch("layernorm_reduce_kernel");
+  }
   const int splits = pick_splits(Tn, N, ds->sm_count, 32);
   if (splits > 1) {
     GB_CUDA_OK(cudaMemsetAsync(gw, 0, sizeof(float) * static_cast<size_t>(N) * F, st));
@@ -382,36 +447,26 @@ static int launch_ln(const T* A, const T* G, int N, long long Tn, int F, float e
   }
   dim3 grid(splits, N);
   const size_t smem = sizeof(float) * (2 * static_cast<size_t>(F) + 32);
-  const bool fast = (F % 8 == 0) && (F <= 1024) &&
-                    ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0);
-  if (fast) {
-    const int nchunk = (F + 255) / 256;
-    switch (nchunk) {
-      case 1: layernorm_persample_kernel<T, 1><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, splits); break;
-      case 2: layernorm_persample_kernel<T, 2><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, splits); break;
-      case 3: layernorm_persample_kernel<T, 3><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, splits); break;
-      default: layernorm_persample_kernel<T, 4><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, splits); break;
-    }
-  } else {
-    if (smem > 48 * 1024)
-      GB_CUDA_OK(cudaFuncSetAttribute(layernorm_persample_generic_kernel<T>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    layernorm_persample_generic_kernel<T><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, splits);
-  }
+  if (smem > 48 * 1024)
+    GB_CUDA_OK(cudaFuncSetAttribute(layernorm_persample_generic_kernel<T>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  layernorm_persample_generic_kernel<T><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, splits);
   count_launch();
-  return post_launch("layernorm_persample_kernel");
+  return post_launch("layernorm_persample_generic_kernel");
 }
 
 extern "C" int ghost_layernorm_persample(const void* A, const void* G, int is_f32, int N, long long T,
-                                         int F, float eps, float* gw, float* gb, void* stream) {
+                                         int F, float eps, float* gw, float* gb, void* ws,
+                                         long long ws_bytes, void* stream) {
   const DeviceState* ds = device_state();
   if (!ds) return GHOST_ERR_DEVICE;
   GB_REQUIRE(A && G && gw && gb, "ghost_layernorm_persample: null pointer");
   GB_REQUIRE(N > 0 && T > 0 && F > 0 && N <= 65535, "ghost_layernorm_persample: bad dimensions");
   GB_REQUIRE(F <= 24 * 1024, "ghost_layernorm_persample: normalized size above 24576 is not supported");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (is_f32) return launch_ln<float>(static_cast<const float*>(A), static_cast<const float*>(G), N, T, F, eps, gw, gb, ds, st);
-  return launch_ln<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(G), N, T, F, eps, gw, gb, ds, st);
+  float* w = static_cast<float*>(ws);
+  if (is_f32) return launch_ln<float>(static_cast<const float*>(A), static_cast<const float*>(G), N, T, F, eps, gw, gb, w, ws_bytes, ds, st);
+  return launch_ln<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(G), N, T, F, eps, gw, gb, w, ws_bytes, ds, st);
 }
 
 extern "C" int ghost_small_gram_f32(const float* X, int n_train, int n_val, int F, float scale,

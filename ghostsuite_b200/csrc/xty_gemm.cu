@@ -10,16 +10,10 @@
 //                   CTAs; partial tiles are added into an fp32 workspace with red.global.add.
 //   kEpiStore       per-validation-sample weight gradients V[v] written to a workspace
 //                   (per-sample form of :133-134).
-//   kEpiDot         per-train-sample weight-gradient tiles dotted against the n_val stored
-//                   validation gradients in the epilogue (:135, for every validation sample
-//                   separately).  A CTA walks consecutive train samples of one output tile and
-//                   never clears its two TMEM accumulators in between (samples alternate between
-//                   them): each accumulator holds a running sum of per-sample gradients, the
-//                   epilogue dots that running sum with the validation tiles and subtracts the
-//                   previous value of the same dot, which is the dot of the newest sample alone.
-//                   When the CTA leaves the tile the running sums ARE the train-gradient tile and
-//                   are added to the fp32 workspace once -- so per-sample gradients never reach
-//                   HBM and the train gradient costs no extra tensor work and almost no atomics.
+//   kEpiStoreTiles  per-sample weight-gradient tiles (train and validation samples alike) written
+//                   tile-major as bf16 (fp32 for split fp32 inputs); tile_dot.cu then contracts
+//                   them into the [n_val, n_train] matrix and the train-gradient sum in one
+//                   streaming pass (per-sample form of :133-135).
 //
 // Linear weights are [d_out, d_in]: X = G (out-grad), Y = A (activations).  HF Conv1D weights are
 // [d_in, d_out]: X = A, Y = G.  No transposes are materialised.
@@ -31,7 +25,7 @@
 
 namespace gb {
 
-enum { kEpiAccumulate = 0, kEpiStore = 1, kEpiDot = 2 };
+enum { kEpiAccumulate = 0, kEpiStore = 1, kEpiStoreTiles = 2 };
 
 struct XtyParams {
   int mode;
@@ -43,16 +37,13 @@ struct XtyParams {
   int k_splits;              // kEpiAccumulate: CTAs sharing one output tile
   int kb_per_split;          // 64-row blocks per split
   int units_per_cta;         // each CTA takes a contiguous range of units
-  // kEpiAccumulate / kEpiDot: fp32 [m_cols, ld_acc] accumulation workspace (may be null for Dot)
+  // kEpiAccumulate: fp32 [m_cols, ld_acc] accumulation workspace
   float* acc_ws;
   long long ld_acc;
-  // kEpiStore / kEpiDot: validation gradients [n_val][m_cols][ld_v]
+  // kEpiStore: row-major [sample][m_cols][ld_v]; kEpiStoreTiles: tile-major [tile][sample][128][256]
   void* vgrad;
   long long ld_v;
   int v_is_f32;
-  int n_val, n_train;
-  float dot_scale;
-  float* M;                  // [n_val, n_train]
   int* err;
 };
 
@@ -60,9 +51,7 @@ struct XtyCfg {
   static constexpr int BM = 128, BN = 256, BK = 64;
   static constexpr int kStageBytes = (BM + BN) * BK * 2;   // 48 KB
   static constexpr int kStages = 4;
-  static constexpr int kMaxVal = 32;
-  static constexpr int kPrevBytes = 2 * kMaxVal * 128 * 4;   // previous partial dots, per thread
-  static constexpr int kSmemBytes = kStages * kStageBytes + kPrevBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
 
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
@@ -94,8 +83,7 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* s_prev = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);   // [2][kMaxVal][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kPrevBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* acc_full = bars + 2 * kStages;     // [2]
@@ -112,12 +100,6 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   const int kb_sample = static_cast<int>((p.T + BK - 1) / BK);
   const long long u_begin = static_cast<long long>(blockIdx.x) * p.units_per_cta;
   const long long u_end = (u_begin + p.units_per_cta < units) ? u_begin + p.units_per_cta : units;
-  const int inner_units = p.samples * p.k_splits;
-  // kEpiDot: an accumulator keeps summing while the CTA stays on one output tile.  `fresh` = first
-  // use of this accumulator (parity) on the tile, `last` = last use before the CTA moves on.
-  auto run_fresh = [&](long long u) { return (u - 2 < u_begin) || ((u - 2) / inner_units != u / inner_units); };
-  auto run_last = [&](long long u) { return (u + 2 >= u_end) || ((u + 2) / inner_units != u / inner_units); };
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -195,7 +177,6 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.err, 512)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t dst = tmem_base + acc * BN;
-        const bool keep = (p.mode == kEpiDot) && !run_fresh(u);   // continue the running sum
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 513)) { ok = false; break; }
           tc_fence_after_sync();
@@ -206,7 +187,7 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             umma_bf16(dst, adesc + k * (16 * 128 / 16), bdesc + k * (16 * 128 / 16), idesc,
-                      (kb == kb0 && k == 0 && !keep) ? 0u : 1u);
+                      (kb == kb0 && k == 0) ? 0u : 1u);
           umma_commit(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -267,77 +248,40 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
           }
         }
       } else {
-        float dots[XtyCfg::kMaxVal];
-#pragma unroll
-        for (int v = 0; v < XtyCfg::kMaxVal; ++v) dots[v] = 0.f;
-        const bool fresh = run_fresh(u);
-        const bool flush = run_last(u) && (p.acc_ws != nullptr);
+        // kEpiStoreTiles: the whole 128 x 256 tile (zero padded), tile-major:
+        //   dst[(tile * samples + sample)][row][col], one 512- or 1024-byte row per thread
+        const long long tbase = (static_cast<long long>(tile) * p.samples + sample) * (BM * BN) +
+                                static_cast<long long>(threadIdx.x) * BN;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
-          if (n0 + c0 >= p.n_cols) break;
           uint32_t r[32];
           tmem_ld32(t_acc + c0, r);
           tmem_ld_wait();
-          if (m_ok) {
-            const int ncol = min(32, p.n_cols - (n0 + c0));
-            if (flush)   // the running sum of this accumulator is its share of the train gradient
-              red_add_row32(p.acc_ws + static_cast<long long>(m) * p.ld_acc + n0 + c0, r, ncol);
+          if (empty_k) {
 #pragma unroll
-            for (int v = 0; v < XtyCfg::kMaxVal; ++v) {
-              if (v >= p.n_val) break;
-              const long long vbase = (static_cast<long long>(v) * p.m_cols + m) * p.ld_v + n0 + c0;
-              float s = 0.f;
-              if (p.v_is_f32) {
-                const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.vgrad) + vbase);
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+          if (p.v_is_f32) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.vgrad) + tbase + c0);
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  if (q * 4 < ncol) {   // ld_v and n_cols padding keep whole float4s in bounds
-                    const float4 f = __ldg(src + q);
-                    s = fmaf(f.x, __uint_as_float(r[4 * q + 0]), s);
-                    s = fmaf(f.y, __uint_as_float(r[4 * q + 1]), s);
-                    s = fmaf(f.z, __uint_as_float(r[4 * q + 2]), s);
-                    s = fmaf(f.w, __uint_as_float(r[4 * q + 3]), s);
-                  }
-                }
-              } else {
-                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.vgrad) + vbase);
+            for (int q = 0; q < 8; ++q)
+              dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                   __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.vgrad) + tbase + c0);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  if (q * 8 < ncol) {
-                    const uint4 w = __ldg(src + q);
-                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            for (int q = 0; q < 4; ++q) {
+              uint32_t w[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                      const float lo = __uint_as_float(ww[e] << 16);
-                      const float hi = __uint_as_float(ww[e] & 0xffff0000u);
-                      s = fmaf(lo, __uint_as_float(r[8 * q + 2 * e + 0]), s);
-                      s = fmaf(hi, __uint_as_float(r[8 * q + 2 * e + 1]), s);
-                    }
-                  }
-                }
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * e]),
+                                                               __uint_as_float(r[8 * q + 2 * e + 1]));
+                w[e] = *reinterpret_cast<const uint32_t*>(&h);
               }
-              dots[v] += s;
+              dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
             }
           }
         }
-        // hand the accumulator back, then reduce the n_val partial dots across the warp
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[acc]);
-#pragma unroll
-        for (int v = 0; v < XtyCfg::kMaxVal; ++v) {
-          if (v >= p.n_val) break;
-          // dots[v] is <V_v, running sum>; minus its previous value = <V_v, newest sample's tile>
-          float* prev = s_prev + (acc * XtyCfg::kMaxVal + v) * 128 + threadIdx.x;
-          float s = fresh ? dots[v] : dots[v] - *prev;
-          *prev = dots[v];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-          if (lane == 0 && s != 0.f)
-            atomicAdd(&p.M[static_cast<long long>(v) * p.n_train + sample], s * p.dot_scale);
-        }
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-        continue;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -446,10 +390,32 @@ extern "C" int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, 
   return finalize_xty(p.acc_ws, p.ld_acc, out, out_is_f32, m_cols, n_cols, scale, accumulate, st);
 }
 
-extern "C" long long ghost_persample_workspace_bytes(int n_val, int m_cols, int n_cols, int v_is_f32) {
-  const long long ldv = round_up(n_cols, 8);
-  return round_up(static_cast<long long>(m_cols) * round_up(n_cols, 4) * 4, 256) +
-         static_cast<long long>(n_val) * m_cols * ldv * (v_is_f32 ? 4 : 2);
+namespace gb {
+int launch_tile_dot(const void* V, const void* W, int is_f32, long long tiles, int n_val, int n_grp, int b0,
+                    int n_train, float scale, float* M, float* sum, int sum_init, const DeviceState* ds,
+                    cudaStream_t st);
+int launch_tile_sum_finalize(const float* sum, int n_tiles_n, void* out, int out_is_f32, int rows, int cols,
+                             float scale, int accumulate, const DeviceState* ds, cudaStream_t st);
+}
+
+// Workspace of the per-sample path: fp32 tile-major train-gradient sum, validation tiles, and the
+// tiles of one group of train samples.  The group size is the largest that keeps the workspace
+// under `budget_bytes` (at least one sample).
+static const long long kTileElems = 128 * 256;
+static int persample_group(int n_train, int n_val, long long tiles, int esize, long long budget_bytes) {
+  const long long per_sample = tiles * kTileElems * esize;
+  long long g = (budget_bytes - tiles * kTileElems * 4) / per_sample - n_val;
+  if (g < 1) g = 1;
+  if (g > n_train) g = n_train;
+  return static_cast<int>(g);
+}
+static const long long kPersampleBudget = 6ll << 30;
+
+extern "C" long long ghost_persample_workspace_bytes(int n_train, int n_val, int m_cols, int n_cols, int v_is_f32) {
+  const long long tiles = static_cast<long long>(ceil_div(m_cols, XtyCfg::BM)) * ceil_div(n_cols, XtyCfg::BN);
+  const int esize = v_is_f32 ? 4 : 2;
+  const int g = persample_group(n_train, n_val, tiles, esize, kPersampleBudget);
+  return tiles * kTileElems * 4 + (static_cast<long long>(n_val) + g) * tiles * kTileElems * esize + 512;
 }
 
 // Per-sample-gradient path.  X, Y: [n_train + n_val, T, cols] (train first).  Produces
@@ -465,14 +431,14 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   GB_REQUIRE(X && Y && M_out && ws, "ghost_persample_dot_bf16: null pointer");
   GB_REQUIRE(n_train > 0, "No training samples to compute dot product, check batch sizes.");
   GB_REQUIRE(n_val > 0 && T > 0 && m_cols > 0 && n_cols > 0, "ghost_persample_dot_bf16: empty dimension");
-  GB_REQUIRE(n_val <= XtyCfg::kMaxVal, "ghost_persample_dot_bf16: at most %d validation samples per call", XtyCfg::kMaxVal);
   GB_REQUIRE(T < (1ll << 31) - 64, "ghost_persample_dot_bf16: T too large");
-  GB_REQUIRE(ws_bytes >= ghost_persample_workspace_bytes(n_val, m_cols, n_cols, v_is_f32),
+  GB_REQUIRE(ws_bytes >= ghost_persample_workspace_bytes(n_train, n_val, m_cols, n_cols, v_is_f32),
              "ghost_persample_dot_bf16: workspace too small");
+  GB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0, "ghost_persample_dot_bf16: workspace must be 256-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const long long ld_acc = round_up(n_cols, 4);
-  const long long acc_bytes = round_up(static_cast<long long>(m_cols) * ld_acc * 4, 256);
+  const int esize = v_is_f32 ? 4 : 2;
   XtyParams p = {};
+  p.mode = kEpiStoreTiles;
   p.m_cols = m_cols;
   p.n_cols = n_cols;
   p.m_tiles = ceil_div(m_cols, XtyCfg::BM);
@@ -480,36 +446,37 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   p.T = T;
   p.k_splits = 1;
   p.kb_per_split = ceil_div(T, XtyCfg::BK);
-  p.vgrad = static_cast<uint8_t*>(ws) + acc_bytes;
-  p.ld_v = round_up(n_cols, 8);
   p.v_is_f32 = v_is_f32;
-  p.n_val = n_val;
-  p.n_train = n_train;
-  p.dot_scale = dot_scale;
-  p.M = M_out;
   p.err = ds->err_word;
+  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  const int group = persample_group(n_train, n_val, tiles, esize, kPersampleBudget);
+  float* sum = static_cast<float*>(ws);
+  uint8_t* vws = static_cast<uint8_t*>(ws) + tiles * kTileElems * 4;
+  uint8_t* wws = vws + static_cast<long long>(n_val) * tiles * kTileElems * esize;
   CUtensorMap tx, ty;
   int rc;
   const long long N = static_cast<long long>(n_train) + n_val;
   if ((rc = make_tmap_bf16_3d(&tx, X, N, T, m_cols, ldx, XtyCfg::BK)) != GHOST_OK) return rc;
   if ((rc = make_tmap_bf16_3d(&ty, Y, N, T, n_cols, ldy, XtyCfg::BK)) != GHOST_OK) return rc;
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
-  // pass 1: validation gradients
-  p.mode = kEpiStore;
+  // validation tiles
   p.samples = n_val;
   p.sample0 = n_train;
+  p.vgrad = vws;
   if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
-  // pass 2: train samples, dots (+ train gradient)
-  p.mode = kEpiDot;
-  p.samples = n_train;
-  p.sample0 = 0;
-  if (grad_out) {
-    p.acc_ws = static_cast<float*>(ws);
-    p.ld_acc = ld_acc;
-    GB_CUDA_OK(cudaMemsetAsync(ws, 0, static_cast<size_t>(m_cols) * ld_acc * 4, st));
+  // train samples, one group at a time: tiles, then dots (+ running train-gradient sum)
+  for (int b0 = 0; b0 < n_train; b0 += group) {
+    const int g = (n_train - b0 < group) ? n_train - b0 : group;
+    p.samples = g;
+    p.sample0 = b0;
+    p.vgrad = wws;
+    if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+    if ((rc = launch_tile_dot(vws, wws, v_is_f32, tiles, n_val, g, b0, n_train, dot_scale, M_out,
+                              grad_out ? sum : nullptr, b0 == 0 ? 1 : 0, ds, st)) != GHOST_OK)
+      return rc;
   }
-  if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
   if (grad_out)
-    return finalize_xty(p.acc_ws, ld_acc, grad_out, grad_is_f32, m_cols, n_cols, grad_scale, grad_accumulate, st);
+    return launch_tile_sum_finalize(sum, p.n_tiles, grad_out, grad_is_f32, m_cols, n_cols, grad_scale,
+                                    grad_accumulate, ds, st);
   return GHOST_OK;
 }

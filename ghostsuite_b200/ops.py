@@ -270,9 +270,6 @@ def wgrad(X: torch.Tensor, Y: torch.Tensor, scale: float, out_dtype: torch.dtype
     return out
 
 
-MAX_VAL_PER_CALL = 32
-
-
 def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float = 1.0,
                   want_grad: bool = False, grad_scale: float = 1.0,
                   grad_dtype: Optional[torch.dtype] = None
@@ -298,32 +295,19 @@ def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float
     grad = None
     if want_grad:
         grad = torch.empty((m, n), dtype=grad_dtype or X.dtype, device=X.device)
-    for v0 in range(0, n_val, MAX_VAL_PER_CALL):
-        v1 = min(n_val, v0 + MAX_VAL_PER_CALL)
-        nv = v1 - v0
-        if v0 == 0 and v1 == n_val:
-            Xc, Yc = X, Y
-        else:
-            Xc = torch.cat((X[:n_train], X[n_train + v0:n_train + v1]))
-            Yc = torch.cat((Y[:n_train], Y[n_train + v0:n_train + v1]))
-        arena = _Arena(X.device)
-        mat, split = _xty_operands(lib, arena, Xc, Yc, n_train + nv, T)
-        v_f32 = 1 if split else 0
-        ws_bytes = int(lib.ghost_persample_workspace_bytes(nv, m, n, v_f32))
-        off_ws = arena.plan(ws_bytes)
-        base = arena.commit()
-        do_grad = want_grad and v0 == 0
-        Mc = M if (v0 == 0 and v1 == n_val) else torch.empty((nv, n_train), dtype=_F32, device=X.device)
-        with _Timed("xty_gemm_kernel[persample]", "tensor",
-                    2.0 * (n_train + nv) * T * m * n + 2.0 * nv * n_train * m * n,
-                    2.0 * (n_train + nv) * T * (m + n)):
-            xp, yp, ldx, ldy, T_eff = mat(base)
-            _lib.check(lib.ghost_persample_dot_bf16(
-                xp, yp, n_train, nv, T_eff, m, n, ldx, ldy, float(dot_scale), Mc.data_ptr(), v_f32,
-                grad.data_ptr() if do_grad else None, _dt_flag(grad) if do_grad else 0,
-                float(grad_scale), 0, base + off_ws, ws_bytes, _stream_ptr()))
-        if Mc is not M:
-            M[v0:v1].copy_(Mc)
+    arena = _Arena(X.device)
+    mat, split = _xty_operands(lib, arena, X, Y, N, T)
+    v_f32 = 1 if split else 0
+    ws_bytes = int(lib.ghost_persample_workspace_bytes(n_train, n_val, m, n, v_f32))
+    off_ws = arena.plan(ws_bytes)
+    base = arena.commit()
+    with _Timed("xty_gemm_kernel+tile_dot_kernel[persample]", "tensor",
+                2.0 * N * T * m * n + 2.0 * n_val * n_train * m * n, 2.0 * N * T * (m + n)):
+        xp, yp, ldx, ldy, T_eff = mat(base)
+        _lib.check(lib.ghost_persample_dot_bf16(
+            xp, yp, n_train, n_val, T_eff, m, n, ldx, ldy, float(dot_scale), M.data_ptr(), v_f32,
+            grad.data_ptr() if want_grad else None, _dt_flag(grad) if want_grad else 0,
+            float(grad_scale), 0, base + off_ws, ws_bytes, _stream_ptr()))
     return M, grad
 
 
@@ -388,9 +372,14 @@ def layernorm_persample(A: torch.Tensor, G: torch.Tensor, eps: float
         raise ValueError("LayerNorm input and out-grad shapes differ")
     gw = torch.empty((N, F), dtype=_F32, device=A.device)
     gb = torch.empty((N, F), dtype=_F32, device=A.device)
+    arena = _Arena(A.device)
+    ws_bytes = int(lib.ghost_layernorm_workspace_bytes(N, T, F))
+    off = arena.plan(ws_bytes)
+    base = arena.commit()
     with _Timed("layernorm_persample_kernel", "hbm", 0.0, 2.0 * N * T * F * A.element_size() + 8.0 * N * F):
         _lib.check(lib.ghost_layernorm_persample(A.data_ptr(), G.data_ptr(), _dt_flag(A), N, T, F,
-                                                 float(eps), gw.data_ptr(), gb.data_ptr(), _stream_ptr()))
+                                                 float(eps), gw.data_ptr(), gb.data_ptr(), base + off,
+                                                 ws_bytes, _stream_ptr()))
     return gw, gb
 
 

@@ -87,13 +87,14 @@ int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, int m_cols,
 
 /* ---- Linear / Conv1D weight dot product, per-sample-gradient path ---------------------------- */
 /* X, Y: [n_train + n_val, T, cols] bf16.  M[v,b] = dot_scale * <X_v^T Y_v, X_b^T Y_b>.  Per-sample
- * weight gradients are formed tile by tile in TMEM and dotted against the stored validation
- * gradients in the epilogue; if grad_out != NULL the same pass also produces the train gradient
- * grad_scale * sum_b X_b^T Y_b (so ghost_wgrad_bf16 is not needed for that layer).
- * v_is_f32 selects the storage type of the validation gradients in the workspace.
+ * weight-gradient tiles are formed in TMEM by a tcgen05 GEMM over each sample's tokens and written
+ * tile-major to the workspace (bf16, or fp32 when v_is_f32); a streaming kernel then contracts the
+ * validation tiles with the train tiles into M and, if grad_out != NULL, sums the train tiles into
+ * the train gradient grad_scale * sum_b X_b^T Y_b in the same pass (so ghost_wgrad_bf16 is not
+ * needed for that layer).  Train samples are processed in groups sized to the workspace.
  * Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:131-135 and :443-447, per
  * validation sample (the reference's version sums the validation batch first). */
-long long ghost_persample_workspace_bytes(int n_val, int m_cols, int n_cols, int v_is_f32);
+long long ghost_persample_workspace_bytes(int n_train, int n_val, int m_cols, int n_cols, int v_is_f32);
 int ghost_persample_dot_bf16(const void* X, const void* Y, int n_train, int n_val, long long T,
                              int m_cols, int n_cols, long long ldx, long long ldy, float dot_scale,
                              float* M_out, int v_is_f32, void* grad_out, int grad_is_f32,
@@ -109,9 +110,13 @@ int ghost_colsum(const void* G, int is_f32, int N, long long T, int cols, long l
 /* Per-sample LayerNorm parameter gradients in one pass over A and G:
  * gw[n,f] = sum_t G[n,t,f] * xhat[n,t,f], gb[n,f] = sum_t G[n,t,f], xhat = layer norm of A over the
  * last dim without affine.  Replaces
- * ghostEngines/supported_layers_grad_samplers_dotprod.py:262-300 and :347-363. */
+ * ghostEngines/supported_layers_grad_samplers_dotprod.py:262-300 and :347-363.
+ * ws: scratch of ghost_layernorm_workspace_bytes() for the per-CTA partial sums, which are then
+ * added in a fixed order (the result is run-to-run deterministic). */
+long long ghost_layernorm_workspace_bytes(int N, long long T, int F);
 int ghost_layernorm_persample(const void* A, const void* G, int is_f32, int N, long long T, int F,
-                              float eps, float* gw, float* gb, void* stream);
+                              float eps, float* gw, float* gb, void* ws, long long ws_bytes,
+                              void* stream);
 /* M[v,b] = scale * <X[n_train + v, :], X[b, :]> for per-sample vectors X[N, F] fp32.  Replaces the
  * einsum('p,bp->b') / einsum('bf,f->b') contractions of the bias and LayerNorm paths. */
 int ghost_small_gram_f32(const float* X, int n_train, int n_val, int F, float scale, float* M_out,
