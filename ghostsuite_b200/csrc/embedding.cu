@@ -28,6 +28,33 @@ template <> __device__ __forceinline__ float ld_f32<__nv_bfloat16>(const __nv_bf
 template <typename T> __device__ __forceinline__ float round_to(float x);
 template <> __device__ __forceinline__ float round_to<float>(float x) { return x; }
 template <> __device__ __forceinline__ float round_to<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ void load8(const float* p, float (&x)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&x)[8]) {
+  const uint4 w = *reinterpret_cast<const uint4*>(p);
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    x[2 * e] = __uint_as_float(ww[e] << 16);
+    x[2 * e + 1] = __uint_as_float(ww[e] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void store8(float* p, const float (&x)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&x)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+    w[e] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
 template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
@@ -182,18 +209,32 @@ emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restri
       }
     }
   }
-  for (int f0 = 0; f0 < d; f0 += 32 * 4) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    if (cnt > 0 && cnt <= 32) {
-      for (int i = 0; i < cnt; ++i) {
-        const int j = __shfl_sync(0xffffffffu, mine, i);
-        const T* row = G + static_cast<long long>(j) * d;
+  // each lane owns 8 consecutive features per step (16-byte loads and stores when d % 8 == 0)
+  const bool vec = (d % 8 == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
+  auto add_row = [&](int j, int f, float (&acc)[8]) {
+    const T* row = G + static_cast<long long>(j) * d + f;
+    float x[8];
+    if (vec) {
+      if (f < d) {
+        load8(row, x);
+      } else {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int f = f0 + q * 32 + lane;
-          if (f < d) acc[q] = __fadd_rn(acc[q], round_to<T>(__fmul_rn(ld_f32<T>(row + f), pre_scale)));  // no fma contraction: two roundings, as the reference
-        }
+        for (int e = 0; e < 8; ++e) x[e] = 0.f;
       }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = (f + e < d) ? ld_f32<T>(row + e) : 0.f;
+    }
+    // no fma contraction: product and sum are rounded separately, as the reference does
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = __fadd_rn(acc[e], round_to<T>(__fmul_rn(x[e], pre_scale)));
+  };
+  for (int fbase = 0; fbase < d; fbase += 256) {      // warp-uniform trip count (shuffles inside)
+    const int f = fbase + lane * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (cnt > 0 && cnt <= 32) {
+      for (int i = 0; i < cnt; ++i) add_row(__shfl_sync(0xffffffffu, mine, i), f, acc);
     } else if (cnt > 32) {
       // selection in ascending token order: next = min{perm[i] : perm[i] > last}
       int last = -1;
@@ -206,24 +247,22 @@ emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restri
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
         last = best;
-        const T* row = G + static_cast<long long>(best) * d;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int f = f0 + q * 32 + lane;
-          if (f < d) acc[q] = __fadd_rn(acc[q], round_to<T>(__fmul_rn(ld_f32<T>(row + f), pre_scale)));  // no fma contraction: two roundings, as the reference
-        }
+        add_row(best, f, acc);
       }
     }
+    T* dst = out + static_cast<long long>(k) * d + f;
+    float o[8];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int f = f0 + q * 32 + lane;
-      if (f < d) {
-        float o = round_to<T>(acc[q]);
-        o = round_to<T>(__fdiv_rn(o, divisor));
-        T* dst = out + static_cast<long long>(k) * d + f;
-        if (accumulate) o = round_to<T>(__fadd_rn(ld_f32<T>(dst), o));
-        *dst = from_f32<T>(o);
-      }
+    for (int e = 0; e < 8; ++e) {
+      o[e] = round_to<T>(__fdiv_rn(round_to<T>(acc[e]), divisor));
+      if (accumulate && f + e < d) o[e] = round_to<T>(__fadd_rn(ld_f32<T>(dst + e), o[e]));
+    }
+    if (vec) {
+      if (f < d) store8(dst, o);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (f + e < d) dst[e] = from_f32<T>(o[e]);
     }
   }
 }
@@ -308,3 +347,4 @@ extern "C" int ghost_embedding_wgrad(const long long* ids, const void* G, int is
   count_launch(4);
   return post_launch("ghost_embedding_wgrad");
 }
+

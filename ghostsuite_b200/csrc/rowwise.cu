@@ -147,7 +147,7 @@ __global__ void colsum_kernel(const T* __restrict__ G, long long Tn, int cols, l
 //   gw[n, f] += sum_t G[n,t,f] * xhat[n,t,f],   gb[n, f] += sum_t G[n,t,f]
 // ------------------------------------------------------------------------------------------
 template <typename T, int NCHUNK>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, NCHUNK <= 3 ? 2 : 1)
 layernorm_persample_kernel(const T* __restrict__ A, const T* __restrict__ G, long long Tn, int F,
                            float eps, float* __restrict__ gw, float* __restrict__ gb,
                            float* __restrict__ part, int t_splits) {
@@ -386,7 +386,7 @@ extern "C" int ghost_colsum(const void* G, int is_f32, int N, long long T, int c
 }
 
 static int ln_splits(long long Tn, int N, int sm_count) {
-  long long want = (2ll * sm_count + N - 1) / N;
+  long long want = (2ll * sm_count) / N;   // at most two resident CTAs per SM: one wave
   const long long maxs = (Tn + 63) / 64;
   if (want > maxs) want = maxs;
   if (want < 1) want = 1;

@@ -13,10 +13,13 @@
 
 namespace gb {
 
-template <typename T> struct Ld8;
-template <> struct Ld8<__nv_bfloat16> {
-  static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&x)[8]) {
-    const uint4 w = __ldg(reinterpret_cast<const uint4*>(p));
+// 8 consecutive stored elements, kept packed in registers until they are used
+template <typename T> struct Pack8;
+template <> struct Pack8<__nv_bfloat16> {
+  uint4 w;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { w = __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void zero() { w = make_uint4(0u, 0u, 0u, 0u); }
+  __device__ __forceinline__ void unpack(float (&x)[8]) const {
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -25,10 +28,14 @@ template <> struct Ld8<__nv_bfloat16> {
     }
   }
 };
-template <> struct Ld8<float> {
-  static __device__ __forceinline__ void ld(const float* p, float (&x)[8]) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+template <> struct Pack8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = __ldg(reinterpret_cast<const float4*>(p));
+    b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  }
+  __device__ __forceinline__ void zero() { a = make_float4(0.f, 0.f, 0.f, 0.f); b = a; }
+  __device__ __forceinline__ void unpack(float (&x)[8]) const {
     x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
     x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
   }
@@ -55,7 +62,7 @@ constexpr int kChunksPerTile = kTileElems / kChunk;  // 1024
 // picks 4 of the 32 train samples of the block.  A thread accumulates an 8 (validation) x 4
 // (train) block of dot products over its vectors.
 template <typename T>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, sizeof(T) == 2 ? 2 : 1)
 tile_dot_kernel(const TileDotParams p) {
   const int lane = threadIdx.x & 31;
   const int kg = lane & 3;
@@ -80,33 +87,40 @@ tile_dot_kernel(const TileDotParams p) {
       for (long long c = c_begin; c < c_end; ++c) {
         const long long tile = c / kChunksPerTile;
         const int e = static_cast<int>(c % kChunksPerTile) * kChunk + kg * 8;
+        // phase 1: every load of the chunk is issued before any arithmetic (12 independent
+        // 16-byte requests per thread in flight)
+        Pack8<T> pw[4], pv[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int b = j0 + bg * 4 + q;
+          if (b < p.n_grp) pw[q].load(W + (tile * p.n_grp + b) * kTileElems + e);
+          else pw[q].zero();
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int v = v0 + i;
+          if (v < p.n_val) pv[i].load(V + (tile * p.n_val + v) * kTileElems + e);
+          else pv[i].zero();
+        }
+        // phase 2: unpack and accumulate
         float w[4][8];
         float s[8];
 #pragma unroll
         for (int x = 0; x < 8; ++x) s[x] = 0.f;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int b = j0 + bg * 4 + q;
-          if (b < p.n_grp) {
-            Ld8<T>::ld(W + (tile * p.n_grp + b) * kTileElems + e, w[q]);
-          } else {
-#pragma unroll
-            for (int x = 0; x < 8; ++x) w[q][x] = 0.f;
-          }
+          pw[q].unpack(w[q]);
 #pragma unroll
           for (int x = 0; x < 8; ++x) s[x] += w[q][x];
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const int v = v0 + i;
-          if (v < p.n_val) {
-            float vv[8];
-            Ld8<T>::ld(V + (tile * p.n_val + v) * kTileElems + e, vv);
+          float vv[8];
+          pv[i].unpack(vv);
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
+          for (int q = 0; q < 4; ++q)
 #pragma unroll
-              for (int x = 0; x < 8; ++x) acc[i][q] = fmaf(vv[x], w[q][x], acc[i][q]);
-          }
+            for (int x = 0; x < 8; ++x) acc[i][q] = fmaf(vv[x], w[q][x], acc[i][q]);
         }
         if (do_sum) {
           // sum over the eight 4-sample groups of the warp, then one 32-byte update per kg lane
