@@ -41,6 +41,7 @@ PROTOTYPES = {
     "ghost_rows_sum": (_i, [_vp, _i, _i, _f, _vp, _i, _i, _vp]),
     "ghost_embedding_dot_workspace_bytes": (_ll, [_i, _ll, _i]),
     "ghost_embedding_dot": (_i, [_vp, _vp, _i, _i, _i, _ll, _i, _i, _f, _vp, _vp, _ll, _vp]),
+    "ghost_embedding_dot_noalloc": (_i, [_vp, _vp, _i, _i, _i, _ll, _i, _i, _f, _vp, _vp]),
     "ghost_embedding_wgrad_workspace_bytes": (_ll, [_i, _ll, _i]),
     "ghost_embedding_wgrad": (_i, [_vp, _vp, _i, _i, _ll, _i, _i, _f, _f, _i, _vp, _vp, _ll, _vp]),
     "ghost_gradproj_dense_bf16": (_i, [_vp, _vp, _i, _ll, _i, _i, _ll, _ll, _vp, _vp, _i, _i, _ll, _ll, _f, _vp, _ll, _vp]),

@@ -13,6 +13,8 @@
 //   the order of the CPU index_add_, so the result is bit-identical to it.
 #include <limits.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace gb {
@@ -348,3 +350,70 @@ extern "C" int ghost_embedding_wgrad(const long long* ids, const void* G, int is
   return post_launch("ghost_embedding_wgrad");
 }
 
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of ghost_embedding_dot.
+//
+// Who needs it: callers that are not allowed to obtain device memory when the hook fires.  Two real
+// cases: a process whose device memory is owned up front by a fixed-size pool (an inference or
+// data-valuation service with a hard memory budget, where a late cudaMalloc can fail or stall every
+// stream while the driver synchronises), and code that runs inside another component's critical
+// section (an allocator callback, a communication progress thread) where calling back into any
+// allocator, torch's included, would deadlock.  Such callers can still hand over their inputs and
+// the output matrix, but they have nowhere to get the id-chain tables from.
+//
+// The tables therefore live in the library image itself: one file-scope __device__ array per GPU
+// that loads the library (kEmbStaticBytes, held until the process exits).  Limits follow from its
+// size: vocab <= 131072 and n_val * T <= 131072.  Larger problems are rejected; use
+// ghost_embedding_dot with a caller-provided workspace for those.
+//
+// The array's name is a host-side handle, not a device address, so the device address is looked up
+// with cudaGetSymbolAddress the first time the entry point runs on a device (with that device
+// current) and cached.  That first call should happen before any stream capture begins.  The
+// tables keep whatever the previous call left: every call re-initialises the head table and
+// rewrites the whole next-table range it uses before reading it.  All calls on one GPU share the
+// one array, so two calls whose kernels can overlap (different streams, no ordering) race; keep
+// calls to this entry point on one stream or order them with events.
+// ------------------------------------------------------------------------------------------------
+namespace gb {
+constexpr int kEmbStaticMaxVocab = 131072;
+constexpr long long kEmbStaticMaxValTokens = 131072;
+constexpr long long kEmbStaticBytes = 4ll * kEmbStaticMaxVocab + 4ll * kEmbStaticMaxValTokens;   // 1 MiB
+static __device__ __align__(256) unsigned char g_emb_static_scratch[kEmbStaticBytes];
+
+static int emb_static_scratch(void** out) {
+  static std::mutex mu;
+  static void* ptrs[64] = {};
+  int dev = -1;
+  GB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(GHOST_ERR_INVALID, "unsupported device ordinal %d", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    // set-up, once per device, with that device current
+    GB_CUDA_OK(cudaGetSymbolAddress(&p, g_emb_static_scratch));
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return GHOST_OK;
+}
+}  // namespace gb
+
+extern "C" int ghost_embedding_dot_noalloc(const long long* ids, const void* G, int is_f32, int n_train,
+                                           int n_val, long long T, int d, int vocab, float scale,
+                                           float* M_out, void* stream) {
+  if (!device_state()) return GHOST_ERR_DEVICE;
+  GB_REQUIRE(vocab > 0 && vocab <= kEmbStaticMaxVocab,
+             "ghost_embedding_dot_noalloc: vocab %d exceeds the built-in scratch (max %d); use "
+             "ghost_embedding_dot with a caller workspace", vocab, kEmbStaticMaxVocab);
+  GB_REQUIRE(n_val > 0 && T > 0 && static_cast<long long>(n_val) * T <= kEmbStaticMaxValTokens,
+             "ghost_embedding_dot_noalloc: n_val * T = %lld exceeds the built-in scratch (max %lld); use "
+             "ghost_embedding_dot with a caller workspace", static_cast<long long>(n_val) * T,
+             kEmbStaticMaxValTokens);
+  void* scratch = nullptr;
+  int rc = emb_static_scratch(&scratch);
+  if (rc != GHOST_OK) return rc;
+  // same kernels as ghost_embedding_dot; the head table is cleared and the used part of the next
+  // table rewritten on every call, so stale contents of the shared array are never read
+  return ghost_embedding_dot(ids, G, is_f32, n_train, n_val, T, d, vocab, scale, M_out, scratch,
+                             kEmbStaticBytes, stream);
+}

@@ -133,6 +133,18 @@ long long ghost_embedding_dot_workspace_bytes(int n_val, long long T, int vocab)
 int ghost_embedding_dot(const long long* ids, const void* G, int is_f32, int n_train, int n_val,
                         long long T, int d, int vocab, float scale, float* M_out, void* ws,
                         long long ws_bytes, void* stream);
+/* Same result as ghost_embedding_dot for callers that cannot supply a workspace because they are not
+ * allowed to allocate device memory at that point (a process whose device memory belongs to a
+ * fixed pool, or code running inside another component's critical section where re-entering any
+ * allocator would deadlock).  The id-chain tables live in a 1 MiB __device__ array inside the
+ * library (one copy per GPU that loads it, kept until exit), hence the limits vocab <= 131072 and
+ * n_val * T <= 131072; anything larger returns GHOST_ERR_INVALID.  The call allocates nothing.  Its
+ * first use on a device looks up the array's device address (cudaGetSymbolAddress) and should
+ * come before any stream capture.  All calls on a GPU share the one array: calls that can overlap
+ * on the device race, so keep them on one stream or order them.  No counterpart in the reference:
+ * the reference allocates a [vocab, d] table on every call. */
+int ghost_embedding_dot_noalloc(const long long* ids, const void* G, int is_f32, int n_train, int n_val,
+                                long long T, int d, int vocab, float scale, float* M_out, void* stream);
 /* out[vocab, d] (= or +=) round(sum over train tokens with that id of round(G * pre_scale)) / divisor
  * in the table dtype, accumulated in fp32 in ascending token order (bit-identical to the CPU
  * index_add_).  Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:214-235. */
