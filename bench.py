@@ -275,7 +275,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "parallelism": f"train batch sharded over {world} GPU(s), val replicated",
                    "l2": "working set per step (activations + out-grads, > 10 GB) exceeds the 126 MB L2",
-                   "optimizer": "AdamW (fused)", "path_rule": "cost"},
+                   "optimizer": "AdamW (fused)", "path_rule": "cost",
+                   "vocab_table_rows": "50257 ids; embedding / LM-head table padded to 50304 rows (padded logits masked out of the loss)"},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
         "gpu_launches": int(launches),
         "clocks": clocks,

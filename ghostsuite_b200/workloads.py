@@ -41,6 +41,16 @@ class GPT2Config:
     n_layer: int = 12
     n_head: int = 12
     tie_weights: bool = True
+    #: rows of the token-embedding / LM-head table are padded to a multiple of this (GPT-2's 50257
+    #: becomes 50304, as nanoGPT-style trainers and the reference's own model factory do): an odd
+    #: vocabulary size makes every cuBLAS GEMM on the logits fall back to unaligned legacy kernels.
+    #: Token ids stay below vocab_size and the padded logits never enter the loss.
+    pad_vocab_to: int = 64
+
+    @property
+    def padded_vocab(self) -> int:
+        m = max(1, self.pad_vocab_to)
+        return (self.vocab_size + m - 1) // m * m
 
 
 class _Attention(nn.Module):
@@ -90,11 +100,11 @@ class GPT2Like(nn.Module):
     def __init__(self, cfg: GPT2Config):
         super().__init__()
         self.cfg = cfg
-        self.wte = nn.Embedding(cfg.vocab_size, cfg.n_embd)
+        self.wte = nn.Embedding(cfg.padded_vocab, cfg.n_embd)
         self.wpe = nn.Embedding(cfg.n_positions, cfg.n_embd)
         self.h = nn.ModuleList(_Block(cfg) for _ in range(cfg.n_layer))
         self.ln_f = nn.LayerNorm(cfg.n_embd)
-        self.lm_head = nn.Linear(cfg.n_embd, cfg.vocab_size, bias=False)
+        self.lm_head = nn.Linear(cfg.n_embd, cfg.padded_vocab, bias=False)
         self.apply(self._init)
         for name, p in self.named_parameters():
             if name.endswith("c_proj.weight"):
@@ -127,8 +137,14 @@ class GPT2Like(nn.Module):
         logits = self.lm_head(self.ln_f(x))
         loss = None
         if labels is not None:
-            loss = F.cross_entropy(logits[:, :-1].reshape(-1, logits.size(-1)).float(),
-                                   labels[:, 1:].reshape(-1))
+            # next-token loss in fp32 without copying the logits for the shift: the targets are
+            # shifted instead and the last position of every sequence is ignored
+            V = self.cfg.vocab_size
+            target = torch.cat((labels[:, 1:], labels.new_full((B, 1), -100)), dim=1).reshape(-1)
+            flat = logits.reshape(-1, logits.size(-1)).float()
+            if flat.size(-1) != V:
+                flat[:, V:] = float("-inf")        # padded classes take no probability mass
+            loss = F.cross_entropy(flat, target, ignore_index=-100)
         return loss, logits
 
 
