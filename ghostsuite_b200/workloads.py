@@ -141,7 +141,9 @@ class GPT2Like(nn.Module):
             # shifted instead and the last position of every sequence is ignored
             V = self.cfg.vocab_size
             target = torch.cat((labels[:, 1:], labels.new_full((B, 1), -100)), dim=1).reshape(-1)
-            flat = logits.reshape(-1, logits.size(-1)).float()
+            flat = logits.reshape(-1, logits.size(-1))
+            # an fp32 copy that is safe to edit in place (for an fp32 model .float() is a no-op view)
+            flat = flat.float() if flat.dtype != torch.float32 else flat.clone()
             if flat.size(-1) != V:
                 flat[:, V:] = float("-inf")        # padded classes take no probability mass
             loss = F.cross_entropy(flat, target, ignore_index=-100)
