@@ -406,6 +406,107 @@ def run_kernels(args):
                                                     "source": peaks["source"]}, "results": results}), flush=True)
 
 
+def run_crossover(args):
+    """Single Linear layer d_in=4096, d_out=11008 (bf16, N(0,1)/sqrt(d) inputs): Gram path against
+    per-sample-gradient path over T.  Batch sizes shrink with T so that the Gram path stays within
+    seconds; times are reported per (train sample x validation sample) pair and per train token."""
+    from ghostsuite_b200 import ops, _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    d, p = 4096, 11008
+    rows = []
+    for T, n_t, n_v in ((128, 256, 32), (512, 256, 32), (2048, 64, 8), (8192, 16, 2)):
+        N = n_t + n_v
+        A = (torch.randn(N, T, d, generator=g, device=dev) * d ** -0.5).bfloat16()
+        G = (torch.randn(N, T, p, generator=g, device=dev) * p ** -0.5).bfloat16()
+        rec = {"T": T, "n_train": n_t, "n_val": n_v}
+        for name, fn in (("gram", lambda: ops.gram_dot(A, G, n_v)),
+                         ("persample", lambda: ops.persample_dot(G, A, n_v, want_grad=True, grad_scale=1.0,
+                                                                 grad_dtype=torch.bfloat16))):
+            fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            rec[name + "_ms"] = ms
+            rec[name + "_train_tokens_per_s"] = n_t * T / (ms * 1e-3)
+        rec["gram_flops"] = 2.0 * n_t * T * n_v * T * (d + p)
+        rec["persample_flops"] = 2.0 * N * T * d * p + 2.0 * n_v * n_t * d * p
+        rec["faster"] = "gram" if rec["gram_ms"] < rec["persample_ms"] else "persample"
+        rec["persample_includes_train_gradient"] = True
+        rows.append(rec)
+        del A, G
+        torch.cuda.empty_cache()
+    _lib.poll_kernel_error()
+    print(json.dumps({"mode": "crossover", "layer": {"d_in": d, "d_out": p, "dtype": "bf16"}, "rows": rows}), flush=True)
+
+
+def run_gradproj_model(args):
+    """GradProjLoRA on a Pythia-410M-shaped decoder (24 layers, d=1024, 16 heads, MLP 4096, vocab 50304,
+    random init, bf16), sequence 2048, batch 16, k_i = k_o = 32 on every attention / MLP Linear,
+    projections streamed to pinned host memory and written to disk by the engine's writer thread."""
+    import contextlib
+    import io
+    import shutil
+    from transformers import GPTNeoXConfig, GPTNeoXForCausalLM
+    from ghostsuite_b200 import _lib
+    from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoraEngine
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    cfg = GPTNeoXConfig(hidden_size=1024, num_hidden_layers=24, num_attention_heads=16, intermediate_size=4096,
+                        vocab_size=50304, max_position_embeddings=2048, use_cache=False)
+    model = GPTNeoXForCausalLM(cfg).to(torch.bfloat16).to(dev)
+    out_dir = tempfile.mkdtemp(prefix="gradproj_bench_")
+    with contextlib.redirect_stdout(io.StringIO()):
+        eng = GradProjLoraEngine(model, proj_layers="attention,mlp", proj_rank_total=1024, proj_rank_min=4,
+                                 proj_seed=42, proj_dtype="float32", proj_dir=out_dir, proj_save_interval=1,
+                                 proj_dims_override=(32, 32))
+        eng.attach()
+    B, T = 16, 2048
+    g = torch.Generator().manual_seed(1)
+    batches = [torch.randint(0, 50304, (B, T), generator=g).pin_memory() for _ in range(4)]
+
+    def step(i):
+        x = batches[i % 4].to(dev, non_blocking=True)
+        model.zero_grad(set_to_none=True)
+        loss = model(input_ids=x, labels=x).loss
+        loss.backward()
+        eng.collect_batch(batch_indices=list(range(i * B, (i + 1) * B)))
+        eng.clear_gradients()
+
+    for i in range(args.warmup):
+        step(i)
+    eng.flush()
+    torch.cuda.synchronize()
+    l0 = _lib.launch_count()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    eng.flush()
+    wall = time.perf_counter() - t0
+    ms = e0.elapsed_time(e1) / args.steps
+    _lib.poll_kernel_error()
+    n_files = len([f for f in os.listdir(out_dir) if f.startswith("proj_iter_")])
+    print(json.dumps({"mode": "gradproj_model", "workload": run_gradproj_model.__doc__.split("\n")[0],
+                      "layers": len(eng.matched_layers), "total_proj_dim": eng.total_proj_dim,
+                      "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
+                      "wall_ms_per_step_including_disk_flush": wall * 1e3 / args.steps,
+                      "d2h_bytes_per_step": B * eng.total_proj_dim * 4, "files_written": n_files,
+                      "gpu_launches": int(_lib.launch_count() - l0)}), flush=True)
+    eng.cleanup()
+    shutil.rmtree(out_dir, ignore_errors=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -413,8 +514,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--mode", default="step", choices=["step", "kernels"],
-                    help="step: the driver's benchmark line; kernels: per-kernel microbenchmarks")
+    ap.add_argument("--mode", default="step", choices=["step", "kernels", "crossover", "gradproj_model"],
+                    help="step: the driver's benchmark line; kernels: per-kernel microbenchmarks; crossover: "
+                         "Gram vs per-sample path over T on one Linear layer; gradproj_model: GradProj on a "
+                         "Pythia-410M-shaped model")
     ap.add_argument("--only", default="", help="kernels mode: comma-separated case names")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -423,6 +526,12 @@ def main():
 
     if args.mode == "kernels":
         run_kernels(args)
+        return
+    if args.mode == "crossover":
+        run_crossover(args)
+        return
+    if args.mode == "gradproj_model":
+        run_gradproj_model(args)
         return
     if args.impl == "reference":
         line = run_reference_arm(args, rank)

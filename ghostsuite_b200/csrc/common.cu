@@ -114,6 +114,51 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
   return GHOST_OK;
 }
 
+int make_tmap_plain_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                       uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld * elem_bytes) % 16 != 0)
+    return fail(GHOST_ERR_INVALID, "TMA operand %p / pitch %llu is not 16-byte aligned", base,
+                (unsigned long long)ld);
+  if (rows == 0 || cols == 0 || box_cols > 256 || box_rows > 256)
+    return fail(GHOST_ERR_INVALID, "bad plain TMA map (rows=%llu cols=%llu box=%ux%u)",
+                (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols);
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                  2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled(plain) failed with CUresult %d", (int)r);
+  return GHOST_OK;
+}
+
+int make_tmap_plain_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t planes, uint64_t rows,
+                       uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * elem_bytes) % 16 != 0)
+    return fail(GHOST_ERR_INVALID, "TMA operand %p / row of %llu elements is not 16-byte aligned", base,
+                (unsigned long long)cols);
+  if (planes == 0 || rows == 0 || cols == 0 || box_cols > 256 || box_rows > 256)
+    return fail(GHOST_ERR_INVALID, "bad plain 3-D TMA map");
+  cuuint64_t dims[3] = {cols, rows, planes};
+  cuuint64_t strides[2] = {cols * elem_bytes, rows * cols * elem_bytes};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                  3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled(plain 3d) failed with CUresult %d", (int)r);
+  return GHOST_OK;
+}
+
 int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t samples, uint64_t rows,
                       uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn fn = encode_fn();

@@ -55,6 +55,13 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t samples, uint64_t rows,
                       uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols = 64);
 
+// Plain (unswizzled) 2-D map of a row-major matrix of 2- or 4-byte elements; box = [box_rows, box_cols].
+int make_tmap_plain_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                       uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+// Plain 3-D map of a dense [planes, rows, cols] array; box = [1, box_rows, box_cols].
+int make_tmap_plain_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t planes, uint64_t rows,
+                       uint64_t cols, uint32_t box_rows, uint32_t box_cols);
+
 inline int ceil_div(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
 
 }  // namespace gb

@@ -1,158 +1,180 @@
 // tile_dot: second half of the per-sample-gradient path.
 //
 // xty_gemm (kEpiStoreTiles) leaves the per-sample weight-gradient tiles of the validation samples
-// (V) and of a group of train samples (W) in a workspace, tile-major.  This kernel streams both
-// once and produces
+// (V) and of a group of train samples (W) in a workspace, tile-major: [tile][sample][32768].  V and W
+// may be one buffer holding all samples (train first) or two buffers; either way they are described
+// by 3-D tensor maps [tiles, samples, 32768] plus a first-validation-sample offset.  This kernel streams both once and produces
 //     M[v, b]  += scale * sum_k V[v][k] * W[b][k]        (Frobenius products, reference :135)
 //     sum[k]   (+)= sum_b W[b][k]                        (the train gradient, reference :168)
-// Each warp owns a contiguous range of 64-element chunks of the flattened tile space, so the
-// train-gradient sum is a plain read-modify-write (no atomics, deterministic); the 8 x 32 block of
-// dot products a warp accumulates is reduced with shuffles and added to M once per warp.
-// Bandwidth-bound: every workspace byte is read once per (8 validation x 32 train) block.
+//
+// HBM-bound by design, so it is built as a copy pipeline: one producer thread feeds a ring of
+// shared-memory stages with TMA (one box of 8 validation rows and one of 32 train rows, 256
+// elements wide, per stage); eight compute warps consume them.  Warp w owns train samples
+// 4w..4w+3 of the block, lane l owns elements 8l..8l+7 of the stage, so every shared-memory read is
+// a conflict-free 16-byte access and a thread accumulates an 8 x 4 block of dot products.  Each
+// CTA owns a contiguous range of stages: the train-gradient sum is a plain read-modify-write
+// (deterministic, no atomics); the dot products are reduced with shuffles and added to M once per
+// CTA and block.
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace gb {
 
-// 8 consecutive stored elements, kept packed in registers until they are used
-template <typename T> struct Pack8;
-template <> struct Pack8<__nv_bfloat16> {
-  uint4 w;
-  __device__ __forceinline__ void load(const __nv_bfloat16* p) { w = __ldg(reinterpret_cast<const uint4*>(p)); }
-  __device__ __forceinline__ void zero() { w = make_uint4(0u, 0u, 0u, 0u); }
-  __device__ __forceinline__ void unpack(float (&x)[8]) const {
-    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      x[2 * e] = __uint_as_float(ww[e] << 16);
-      x[2 * e + 1] = __uint_as_float(ww[e] & 0xffff0000u);
-    }
-  }
-};
-template <> struct Pack8<float> {
-  float4 a, b;
-  __device__ __forceinline__ void load(const float* p) {
-    a = __ldg(reinterpret_cast<const float4*>(p));
-    b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-  }
-  __device__ __forceinline__ void zero() { a = make_float4(0.f, 0.f, 0.f, 0.f); b = a; }
-  __device__ __forceinline__ void unpack(float (&x)[8]) const {
-    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
-    x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-  }
-};
+constexpr int kTileElems = 128 * 256;
+constexpr int kTdCols = 256;            // elements per stage row
+constexpr int kTdValRows = 8;
+constexpr int kTdTrainRows = 32;
 
 struct TileDotParams {
-  const void* V;          // [tiles][n_val][32768]
-  const void* W;          // [tiles][n_grp][32768]
-  long long chunks;       // tiles * 1024 (32-element chunks)
-  long long chunks_per_warp;
-  int n_val, n_grp;       // validation samples, train samples in this group
-  int b0, n_train;        // first train sample of the group, total train samples (M row pitch)
+  long long stages;           // tiles * (32768 / 256)
+  long long stages_per_cta;
+  int n_val, n_grp;           // validation samples, train samples in this group
+  int v_off;                  // index of the first validation sample inside V's sample dimension
+  int b0, n_train;            // first train sample of the group, total train samples (M row pitch)
   float scale;
-  float* M;               // [n_val, n_train]
-  float* sum;             // [tiles * 32768] fp32 or null
-  int sum_init;           // 1: this group overwrites sum, 0: it accumulates
+  float* M;                   // [n_val, n_train]
+  float* sum;                 // [tiles * 32768] fp32 or null
+  int sum_init;               // 1: this group overwrites sum, 0: it accumulates
+  int* err;
 };
 
-constexpr int kTileElems = 128 * 256;
-constexpr int kChunk = 32;                           // elements per warp step (4 lanes x 8)
-constexpr int kChunksPerTile = kTileElems / kChunk;  // 1024
-
-// Lane layout: kg = lane & 3 picks one 8-element vector of the 32-element chunk, bg = lane >> 2
-// picks 4 of the 32 train samples of the block.  A thread accumulates an 8 (validation) x 4
-// (train) block of dot products over its vectors.
 template <typename T>
-__global__ void __launch_bounds__(256, sizeof(T) == 2 ? 2 : 1)
-tile_dot_kernel(const TileDotParams p) {
-  const int lane = threadIdx.x & 31;
-  const int kg = lane & 3;
-  const int bg = lane >> 2;
-  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const long long c_begin = warp * p.chunks_per_warp;
-  long long c_end = c_begin + p.chunks_per_warp;
-  if (c_end > p.chunks) c_end = p.chunks;
-  if (c_begin >= c_end) return;
-  const T* V = static_cast<const T*>(p.V);
-  const T* W = static_cast<const T*>(p.W);
+struct TdCfg {
+  static constexpr int kRowBytes = kTdCols * sizeof(T);
+  static constexpr int kStageBytes = (kTdValRows + kTdTrainRows) * kRowBytes;    // 20 KB / 40 KB
+  static constexpr int kStages = sizeof(T) == 2 ? 8 : 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 8 * kTdCols * 4 + 1024 + 256;
+};
 
-  for (int j0 = 0; j0 < p.n_grp; j0 += 32) {          // 32-train-sample blocks
-    for (int v0 = 0; v0 < p.n_val; v0 += 8) {          // 8-validation-sample blocks
+__device__ __forceinline__ void td_load8(const __nv_bfloat16* p, float (&x)[8]) {
+  const uint4 w = *reinterpret_cast<const uint4*>(p);
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    x[2 * e] = __uint_as_float(ww[e] << 16);
+    x[2 * e + 1] = __uint_as_float(ww[e] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void td_load8(const float* p, float (&x)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+  x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(288, 1)
+tile_dot_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
+                const TileDotParams p) {
+  using Cfg = TdCfg<T>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* s_part = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);     // [8 warps][256]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + 8 * kTdCols * 4);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long s_begin = static_cast<long long>(blockIdx.x) * p.stages_per_cta;
+  const long long s_end = (s_begin + p.stages_per_cta < p.stages) ? s_begin + p.stages_per_cta : p.stages;
+  constexpr int kStagesPerTile = kTileElems / kTdCols;   // 128
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 8); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 8 && lane == 0) { tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_w); }
+  __syncthreads();
+
+  if (warp == 8) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int j0 = 0; j0 < p.n_grp && ok; j0 += kTdTrainRows)
+        for (int v0 = 0; v0 < p.n_val && ok; v0 += kTdValRows)
+          for (long long s = s_begin; s < s_end; ++s) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 431)) { ok = false; break; }
+            uint8_t* st = smem + stage * Cfg::kStageBytes;
+            const int tile = static_cast<int>(s / kStagesPerTile);
+            const int col = static_cast<int>(s % kStagesPerTile) * kTdCols;
+            mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+            tma_load_3d(st, &tm_v, &full_bar[stage], col, p.v_off + v0, tile);
+            tma_load_3d(st + kTdValRows * Cfg::kRowBytes, &tm_w, &full_bar[stage], col, j0, tile);
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ compute warps 0-7
+  int stage = 0; uint32_t phase = 0;
+  bool alive = true;
+  for (int j0 = 0; j0 < p.n_grp && alive; j0 += kTdTrainRows) {
+    for (int v0 = 0; v0 < p.n_val && alive; v0 += kTdValRows) {
       float acc[8][4];
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int q = 0; q < 4; ++q) acc[i][q] = 0.f;
       const bool do_sum = (v0 == 0) && (p.sum != nullptr);
+      bool bvalid[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) bvalid[q] = (j0 + warp * 4 + q) < p.n_grp;
 #pragma unroll 1
-      for (long long c = c_begin; c < c_end; ++c) {
-        const long long tile = c / kChunksPerTile;
-        const int e = static_cast<int>(c % kChunksPerTile) * kChunk + kg * 8;
-        // phase 1: every load of the chunk is issued before any arithmetic (12 independent
-        // 16-byte requests per thread in flight)
-        Pack8<T> pw[4], pv[8];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int b = j0 + bg * 4 + q;
-          if (b < p.n_grp) pw[q].load(W + (tile * p.n_grp + b) * kTileElems + e);
-          else pw[q].zero();
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int v = v0 + i;
-          if (v < p.n_val) pv[i].load(V + (tile * p.n_val + v) * kTileElems + e);
-          else pv[i].zero();
-        }
-        // phase 2: unpack and accumulate
+      for (long long s = s_begin; s < s_end; ++s) {
+        const bool ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 132);
+        if (!named_bar_and(1, 256, ok)) { alive = false; break; }
+        const T* vbuf = reinterpret_cast<const T*>(smem + stage * Cfg::kStageBytes);
+        const T* wbuf = vbuf + kTdValRows * kTdCols;
         float w[4][8];
-        float s[8];
+        float ssum[8];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) s[x] = 0.f;
+        for (int x = 0; x < 8; ++x) ssum[x] = 0.f;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          pw[q].unpack(w[q]);
+          td_load8(wbuf + (warp * 4 + q) * kTdCols + lane * 8, w[q]);
 #pragma unroll
-          for (int x = 0; x < 8; ++x) s[x] += w[q][x];
+          for (int x = 0; x < 8; ++x) ssum[x] += bvalid[q] ? w[q][x] : 0.f;
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           float vv[8];
-          pv[i].unpack(vv);
+          td_load8(vbuf + i * kTdCols + lane * 8, vv);
 #pragma unroll
           for (int q = 0; q < 4; ++q)
 #pragma unroll
             for (int x = 0; x < 8; ++x) acc[i][q] = fmaf(vv[x], w[q][x], acc[i][q]);
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);     // this warp is done with the stage
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
         if (do_sum) {
-          // sum over the eight 4-sample groups of the warp, then one 32-byte update per kg lane
+          float4* mine = reinterpret_cast<float4*>(s_part + warp * kTdCols + lane * 8);
+          mine[0] = make_float4(ssum[0], ssum[1], ssum[2], ssum[3]);
+          mine[1] = make_float4(ssum[4], ssum[5], ssum[6], ssum[7]);
+          asm volatile("bar.sync 2, 256;" ::: "memory");
+          float t = 0.f;
 #pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            s[x] += __shfl_xor_sync(0xffffffffu, s[x], 4);
-            s[x] += __shfl_xor_sync(0xffffffffu, s[x], 8);
-            s[x] += __shfl_xor_sync(0xffffffffu, s[x], 16);
-          }
-          if (bg == 0) {
-            float4* dst = reinterpret_cast<float4*>(p.sum + c * kChunk + kg * 8);
-            float4 a = make_float4(s[0], s[1], s[2], s[3]), b = make_float4(s[4], s[5], s[6], s[7]);
-            if (!(p.sum_init && j0 == 0)) {
-              const float4 oa = dst[0], ob = dst[1];
-              a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
-              b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
-            }
-            dst[0] = a;
-            dst[1] = b;
-          }
+          for (int ww = 0; ww < 8; ++ww) t += s_part[ww * kTdCols + threadIdx.x];
+          float* dst = p.sum + s * kTdCols + threadIdx.x;
+          if (!(p.sum_init && j0 == 0)) t += *dst;
+          *dst = t;
         }
       }
-      // reduce the 8 x 4 block over the four kg lanes, then one atomic per (v, b)
+      if (!alive) break;
+      // reduce the 8 x 4 block over the 32 lanes, one atomic per (v, b) and CTA
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           float a = acc[i][q];
-          a += __shfl_xor_sync(0xffffffffu, a, 1);
-          a += __shfl_xor_sync(0xffffffffu, a, 2);
-          const int v = v0 + i, b = j0 + bg * 4 + q;
-          if (kg == 0 && v < p.n_val && b < p.n_grp && a != 0.f)
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+          const int v = v0 + i, b = j0 + warp * 4 + q;
+          if (lane == 0 && v < p.n_val && b < p.n_grp && a != 0.f)
             atomicAdd(&p.M[static_cast<long long>(v) * p.n_train + p.b0 + b], a * p.scale);
         }
     }
@@ -174,23 +196,44 @@ __global__ void tile_sum_finalize_kernel(const float* __restrict__ sum, int n_ti
   }
 }
 
-int launch_tile_dot(const void* V, const void* W, int is_f32, long long tiles, int n_val, int n_grp, int b0,
-                    int n_train, float scale, float* M, float* sum, int sum_init, const DeviceState* ds,
-                    cudaStream_t st) {
-  TileDotParams p;
-  p.V = V; p.W = W;
-  p.chunks = tiles * kChunksPerTile;
-  p.n_val = n_val; p.n_grp = n_grp; p.b0 = b0; p.n_train = n_train;
-  p.scale = scale; p.M = M; p.sum = sum; p.sum_init = sum_init;
-  long long warps = static_cast<long long>(ds->sm_count) * 16;      // two 256-thread CTAs per SM
-  if (warps > p.chunks) warps = p.chunks;
-  p.chunks_per_warp = (p.chunks + warps - 1) / warps;
-  warps = (p.chunks + p.chunks_per_warp - 1) / p.chunks_per_warp;
-  const int blocks = static_cast<int>((warps + 7) / 8);
-  if (is_f32) tile_dot_kernel<float><<<blocks, 256, 0, st>>>(p);
-  else tile_dot_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(p);
+template <typename T>
+static int launch_tile_dot_t(const void* V, int v_samples, const void* W, int w_samples, long long tiles,
+                             TileDotParams& p, const DeviceState* ds, cudaStream_t st) {
+  using Cfg = TdCfg<T>;
+  CUtensorMap tv, tw;
+  int rc;
+  if ((rc = make_tmap_plain_3d(&tv, V, sizeof(T), tiles, v_samples, kTileElems, kTdValRows, kTdCols)) != GHOST_OK)
+    return rc;
+  if ((rc = make_tmap_plain_3d(&tw, W, sizeof(T), tiles, w_samples, kTileElems, kTdTrainRows, kTdCols)) != GHOST_OK)
+    return rc;
+  static bool attr_set[64] = {};
+  if (!attr_set[ds->device]) {
+    GB_CUDA_OK(cudaFuncSetAttribute(tile_dot_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set[ds->device] = true;
+  }
+  long long ctas = ds->sm_count;
+  if (ctas > p.stages) ctas = p.stages;
+  p.stages_per_cta = (p.stages + ctas - 1) / ctas;
+  ctas = (p.stages + p.stages_per_cta - 1) / p.stages_per_cta;
+  tile_dot_kernel<T><<<static_cast<int>(ctas), 288, Cfg::kSmemBytes, st>>>(tv, tw, p);
   count_launch();
   return post_launch("tile_dot_kernel");
+}
+
+// V: [tiles][v_samples][32768] with the validation samples at index v_off..v_off+n_val-1;
+// W: [tiles][w_samples][32768] with the group's train samples at index 0..n_grp-1.
+int launch_tile_dot(const void* V, int v_samples, int v_off, const void* W, int w_samples, int is_f32,
+                    long long tiles, int n_val, int n_grp, int b0, int n_train, float scale, float* M,
+                    float* sum, int sum_init, const DeviceState* ds, cudaStream_t st) {
+  TileDotParams p;
+  p.v_off = v_off;
+  p.stages = tiles * (kTileElems / kTdCols);
+  p.stages_per_cta = 0;
+  p.n_val = n_val; p.n_grp = n_grp; p.b0 = b0; p.n_train = n_train;
+  p.scale = scale; p.M = M; p.sum = sum; p.sum_init = sum_init;
+  p.err = ds->err_word;
+  if (is_f32) return launch_tile_dot_t<float>(V, v_samples, W, w_samples, tiles, p, ds, st);
+  return launch_tile_dot_t<__nv_bfloat16>(V, v_samples, W, w_samples, tiles, p, ds, st);
 }
 
 int launch_tile_sum_finalize(const float* sum, int n_tiles_n, void* out, int out_is_f32, int rows, int cols,

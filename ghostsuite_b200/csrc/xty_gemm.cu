@@ -391,9 +391,9 @@ extern "C" int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, 
 }
 
 namespace gb {
-int launch_tile_dot(const void* V, const void* W, int is_f32, long long tiles, int n_val, int n_grp, int b0,
-                    int n_train, float scale, float* M, float* sum, int sum_init, const DeviceState* ds,
-                    cudaStream_t st);
+int launch_tile_dot(const void* V, int v_samples, int v_off, const void* W, int w_samples, int is_f32,
+                    long long tiles, int n_val, int n_grp, int b0, int n_train, float scale, float* M,
+                    float* sum, int sum_init, const DeviceState* ds, cudaStream_t st);
 int launch_tile_sum_finalize(const float* sum, int n_tiles_n, void* out, int out_is_f32, int rows, int cols,
                              float scale, int accumulate, const DeviceState* ds, cudaStream_t st);
 }
@@ -409,7 +409,13 @@ static int persample_group(int n_train, int n_val, long long tiles, int esize, l
   if (g > n_train) g = n_train;
   return static_cast<int>(g);
 }
-static const long long kPersampleBudget = 6ll << 30;
+static long long kPersampleBudget = 6ll << 30;
+
+extern "C" int ghost_set_persample_budget_bytes(long long bytes) {
+  GB_REQUIRE(bytes >= (1ll << 20), "ghost_set_persample_budget_bytes: at least 1 MiB");
+  kPersampleBudget = bytes;
+  return GHOST_OK;
+}
 
 extern "C" long long ghost_persample_workspace_bytes(int n_train, int n_val, int m_cols, int n_cols, int v_is_f32) {
   const long long tiles = static_cast<long long>(ceil_div(m_cols, XtyCfg::BM)) * ceil_div(n_cols, XtyCfg::BN);
@@ -459,21 +465,33 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   if ((rc = make_tmap_bf16_3d(&tx, X, N, T, m_cols, ldx, XtyCfg::BK)) != GHOST_OK) return rc;
   if ((rc = make_tmap_bf16_3d(&ty, Y, N, T, n_cols, ldy, XtyCfg::BK)) != GHOST_OK) return rc;
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
-  // validation tiles
-  p.samples = n_val;
-  p.sample0 = n_train;
-  p.vgrad = vws;
-  if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
-  // train samples, one group at a time: tiles, then dots (+ running train-gradient sum)
-  for (int b0 = 0; b0 < n_train; b0 += group) {
-    const int g = (n_train - b0 < group) ? n_train - b0 : group;
-    p.samples = g;
-    p.sample0 = b0;
-    p.vgrad = wws;
+  if (group == n_train) {
+    // everything fits: one GEMM pass over all samples (train first, validation last) into one
+    // [tile][N][32768] buffer, one streaming pass over it
+    p.samples = static_cast<int>(N);
+    p.sample0 = 0;
+    p.vgrad = vws;
     if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
-    if ((rc = launch_tile_dot(vws, wws, v_is_f32, tiles, n_val, g, b0, n_train, dot_scale, M_out,
-                              grad_out ? sum : nullptr, b0 == 0 ? 1 : 0, ds, st)) != GHOST_OK)
+    if ((rc = launch_tile_dot(vws, static_cast<int>(N), n_train, vws, static_cast<int>(N), v_is_f32, tiles,
+                              n_val, n_train, 0, n_train, dot_scale, M_out, grad_out ? sum : nullptr, 1,
+                              ds, st)) != GHOST_OK)
       return rc;
+  } else {
+    // validation tiles once, then the train samples one group at a time
+    p.samples = n_val;
+    p.sample0 = n_train;
+    p.vgrad = vws;
+    if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+    for (int b0 = 0; b0 < n_train; b0 += group) {
+      const int g = (n_train - b0 < group) ? n_train - b0 : group;
+      p.samples = g;
+      p.sample0 = b0;
+      p.vgrad = wws;
+      if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+      if ((rc = launch_tile_dot(vws, n_val, 0, wws, g, v_is_f32, tiles, n_val, g, b0, n_train, dot_scale,
+                                M_out, grad_out ? sum : nullptr, b0 == 0 ? 1 : 0, ds, st)) != GHOST_OK)
+        return rc;
+    }
   }
   if (grad_out)
     return launch_tile_sum_finalize(sum, p.n_tiles, grad_out, grad_is_f32, m_cols, n_cols, grad_scale,

@@ -95,6 +95,9 @@ int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, int m_cols,
  * Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:131-135 and :443-447, per
  * validation sample (the reference's version sums the validation batch first). */
 long long ghost_persample_workspace_bytes(int n_train, int n_val, int m_cols, int n_cols, int v_is_f32);
+/* Upper bound on that workspace (default 6 GiB); smaller values make the train samples go through
+ * in more, smaller groups.  Process-wide; set it before sizing workspaces. */
+int ghost_set_persample_budget_bytes(long long bytes);
 int ghost_persample_dot_bf16(const void* X, const void* Y, int n_train, int n_val, long long T,
                              int m_cols, int n_cols, long long ldx, long long ldy, float dot_scale,
                              float* M_out, int v_is_f32, void* grad_out, int grad_is_f32,

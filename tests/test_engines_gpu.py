@@ -343,6 +343,46 @@ def test_gradproj_naive_equality_and_non_interference(tmp_path):
         assert np.allclose(a, b, rtol=1e-5, atol=1e-6)
 
 
+def test_gradproj_engine_on_gpt2_like_bf16(tmp_path):
+    """Conv1D + Linear layers with sequence inputs in bf16 (the reference raises here because its
+    fp32 projection matrices meet bf16 activations): every layer's slice of the collected
+    [B, total_proj_dim] buffer equals the oracle evaluated on the (A, B) pair that layer's hook saw."""
+    from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoRAEngine
+    from ghostsuite_b200.workloads import GPT2Like, GPT2Config
+    torch.manual_seed(4)
+    cfg = GPT2Config(vocab_size=300, n_positions=64, n_embd=64, n_layer=2, n_head=4, tie_weights=False)
+    model = GPT2Like(cfg).bfloat16().cuda()
+    with contextlib.redirect_stdout(io.StringIO()):
+        eng = GradProjLoRAEngine(model, proj_layers="attn,mlp,lm_head", proj_rank_total=64, proj_rank_min=4,
+                                 proj_seed=7, proj_dtype="float32", proj_dir=str(tmp_path / "p"),
+                                 proj_save_interval=1, proj_dims_override={"lm_head": (8, 8)})
+        eng.attach()
+    assert len(eng.matched_layers) == 2 * 4 + 1
+    assert eng.projection_dims["lm_head"] == (8, 8)
+    cap = {}
+    for name, layer in eng.matched_layers.items():
+        layer.register_forward_hook(lambda l, i, o, n=name: cap.setdefault(n, {}).__setitem__("A", i[0].detach().cpu()))
+        layer.register_full_backward_hook(lambda l, gi, go, n=name: cap[n].__setitem__("B", go[0].detach().cpu()))
+    ids = torch.randint(0, 300, (5, 48)).cuda()
+    loss, _ = model(ids, labels=ids)
+    loss.backward()
+    proj = eng.collect_batch(batch_indices=list(range(5)))
+    eng.flush()
+    assert proj.shape == (5, eng.total_proj_dim) and proj.dtype == torch.float32
+    for name in sorted(eng.matched_layers):
+        P_i, P_o = eng.projection_matrices[name]
+        lo, hi = eng.slice_ranges[name]
+        conv1d = eng.matched_layers[name].__class__.__name__ == "Conv1D"
+        ref = O.gradproj_dense(cap[name]["A"], cap[name]["B"], P_i.cpu(), P_o.cpu(), conv1d=conv1d,
+                               compute_dtype=torch.float64)
+        assert O.rel_fro(proj[:, lo:hi].reshape(ref.shape), ref) < 2e-2, name
+    saved = torch.load(tmp_path / "p" / "proj_iter_000000.pt")
+    assert torch.equal(saved["proj"], proj.cpu()) and saved["batch_idx"] == list(range(5))
+    meta = eng.get_projection_metadata()
+    assert meta["total_proj_dim"] == eng.total_proj_dim and len(meta["layers"]) == 9
+    eng.cleanup()
+
+
 def test_manager_facade(tmp_path):
     from ghostsuite_b200.ghostEngines import GhostEngineManager
     from ghostsuite_b200.workloads import GPT2Like, GPT2Config

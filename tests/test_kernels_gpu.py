@@ -123,6 +123,27 @@ def test_persample_dot(case, dtype):
     assert O.rel_fro(M, M2.cpu()) < TOL[dtype]
 
 
+def test_persample_dot_in_groups():
+    """A small workspace budget forces the train samples through in several groups (and several
+    validation / train blocks of the streaming kernel): same numbers as the single-pass run."""
+    from ghostsuite_b200 import _lib
+    lib = _lib.load()
+    n_t, n_v, T, d, p = 37, 11, 70, 136, 264
+    A, G = make(n_t + n_v, T, d, p, torch.bfloat16, seed=11)
+    ref = O.linear_dot_exact(A, G, n_v)
+    gref = torch.einsum("btp,btd->pd", G[:n_t].double(), A[:n_t].double())
+    try:
+        for budget in (6 << 30, 2 << 20):
+            _lib.check(lib.ghost_set_persample_budget_bytes(budget))
+            M, grad = ops().persample_dot(G.cuda(), A.cuda(), n_v, want_grad=True, grad_scale=1.0,
+                                          grad_dtype=torch.float32)
+            after()
+            assert O.rel_fro(M, ref) < 2e-2
+            assert O.rel_fro(grad, gref) < 1e-2
+    finally:
+        _lib.check(lib.ghost_set_persample_budget_bytes(6 << 30))
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("shape", [(8, 6, 24), (12, 1, 10), (5, 300, 520), (3, 1024, 768)])
 def test_colsum_and_bias(shape, dtype):
