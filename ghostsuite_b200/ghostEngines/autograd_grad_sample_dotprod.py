@@ -116,7 +116,7 @@ def _apply_train_grad(layer: nn.Module, val_batch_size: int, loss_reduction: str
                 _create_or_accumulate_train_grad(bias, grad_bias)
     finally:
         for attr in ("activations", "backprops", "_ghost_backprop_scale", "_ghost_colsums",
-                     "_ghost_cached_train_grad", "_ghost_ln_cache"):
+                     "_ghost_cached_train_grad", "_ghost_ln_cache", "_ghost_conv_tokens"):
             layer.__dict__.pop(attr, None)
 
 
@@ -128,6 +128,8 @@ def _train_grad_bias_from_layer(layer: nn.Module, val_batch_size: int, loss_redu
         raise ValueError("No training samples to compute gradients, check batch sizes.")
     colsums = layer.__dict__.get("_ghost_colsums")
     if colsums is None:
+        if isinstance(layer, nn.Conv2d):      # features are dim 1 there: [N, p, H, W] -> [N, H*W, p]
+            B = B.reshape(B.size(0), B.size(1), -1).transpose(1, 2).contiguous()
         colsums = ops.colsum(B)
     scale = float(getattr(layer, "_ghost_backprop_scale", 1.0))
     if loss_reduction == "mean":

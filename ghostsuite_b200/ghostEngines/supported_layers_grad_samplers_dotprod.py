@@ -23,6 +23,7 @@ computed once and cached; pre-setting it overrides the choice) selects the Gram 
 from __future__ import annotations
 
 import torch
+import torch.nn.functional as F
 from torch import nn
 
 try:  # HF Conv1D is optional at import time; it is a registry key when transformers is present
@@ -37,8 +38,13 @@ from .. import ops
 #: 'gram' / 'persample' -- force one kernel (benchmarks and tests)
 PATH_RULE = "cost"
 
-# relative cost of the per-sample path's epilogue (validation-gradient dots) per tensor flop
-_PERSAMPLE_OVERHEAD = 1.25
+# Measured throughputs behind the 'cost' rule (B200): Gram kernel ~1.2e15 flop/s; per-sample GEMM
+# pass ~0.8e15 flop/s; the streaming dot kernel ~6e12 (validation x train x weight-element) products
+# per second on CUDA cores and ~5e12 bytes/s for writing and re-reading the bf16 tiles.
+_GRAM_FLOPS = 1.2e15
+_PERSAMPLE_FLOPS = 0.8e15
+_DOT_PRODUCTS_PER_S = 6.0e12
+_TILE_BYTES_PER_S = 5.0e12
 
 
 def _token_count(A: torch.Tensor) -> int:
@@ -57,7 +63,8 @@ def _should_use_ghost_computation(layer: nn.Module, A: torch.Tensor, B: torch.Te
 
     With ``PATH_RULE == 'reference'`` (or when the batch split is unknown) this is the reference's
     test ``2*T^2 <= weight.numel()``.  With ``'cost'`` the two kernels' tensor work for the full
-    matrix is compared: Gram ``2*n_t*n_v*T^2*(d+p)`` against per-sample ``2*(n_t+n_v)*T*d*p``.
+    matrix is compared: Gram ``2*n_t*n_v*T^2*(d+p)`` flops against the per-sample path's
+    ``2*(n_t+n_v)*T*d*p`` flops plus its ``n_v*n_t*d*p`` dot-kernel products and tile traffic.
     """
     if hasattr(layer, "use_ghost_computation"):
         return
@@ -73,8 +80,9 @@ def _should_use_ghost_computation(layer: nn.Module, A: torch.Tensor, B: torch.Te
         return
     n_v = int(val_batch_size)
     n_t = int(A.shape[0]) - n_v
-    gram = 2.0 * n_t * n_v * T * T * (d + p)
-    per = 2.0 * (n_t + n_v) * T * d * p * _PERSAMPLE_OVERHEAD
+    gram = 2.0 * n_t * n_v * T * T * (d + p) / _GRAM_FLOPS
+    per = (2.0 * (n_t + n_v) * T * d * p / _PERSAMPLE_FLOPS + float(n_v) * n_t * d * p / _DOT_PRODUCTS_PER_S
+           + 4.0 * (n_t + n_v) * d * p / _TILE_BYTES_PER_S)
     layer.use_ghost_computation = bool(gram <= per)
 
 
@@ -256,10 +264,64 @@ def _compute_layernorm_train_grad(layer: nn.LayerNorm, A: torch.Tensor, B: torch
     return None
 
 
+# --------------------------------------------------------------------------------------------
+# Conv2d: every output position is a token of the unfolded (im2col) input
+# --------------------------------------------------------------------------------------------
+def _conv2d_tokens(layer: nn.Conv2d, A: torch.Tensor, B: torch.Tensor):
+    """``(A_tok [N, L, C*kh*kw], B_tok [N, L, out_channels])`` for a Conv2d with groups == 1.  The
+    unfold is PyTorch's; the contractions over tokens run in the same kernels as nn.Linear."""
+    if layer.groups != 1:
+        raise ValueError("Conv2d with groups != 1 is not supported")
+    key = (A.data_ptr(), B.data_ptr(), A.size(0))
+    cached = layer.__dict__.get("_ghost_conv_tokens")
+    if cached is not None and cached[0] == key:
+        return cached[1], cached[2]
+    A_u = F.unfold(A.detach(), kernel_size=layer.kernel_size, dilation=layer.dilation,
+                   padding=layer.padding, stride=layer.stride)               # [N, D, L]
+    B_r = B.detach().reshape(B.size(0), B.size(1), -1)                        # [N, p, L]
+    A_tok = A_u.transpose(1, 2).contiguous()
+    B_tok = B_r.transpose(1, 2).contiguous()
+    layer._ghost_conv_tokens = (key, A_tok, B_tok)
+    return A_tok, B_tok
+
+
+def _compute_conv2d_dot_product(layer: nn.Conv2d, A: torch.Tensor, B: torch.Tensor,
+                                val_batch_size: int) -> None:
+    """nn.Conv2d weight and bias dot products (reference :513-563).  The reference's ghost branch
+    for this layer type contracts over output positions instead of features and fails unless
+    C*kh*kw == out_channels; both kernels here compute the per-sample-gradient products."""
+    if A.size(0) - val_batch_size <= 0:
+        raise ValueError("No training samples to compute dot product")
+    A_tok, B_tok = _conv2d_tokens(layer, A, B)
+    if not hasattr(layer, "use_ghost_computation"):
+        _should_use_ghost_computation(layer, A_tok.transpose(1, 2), B_tok.transpose(1, 2), conv=True,
+                                      val_batch_size=val_batch_size)
+    _dense_dot_product(layer, A_tok, B_tok, val_batch_size, weight_is_in_by_out=False)
+    cached = layer.__dict__.get("_ghost_cached_train_grad")
+    if cached is not None:       # re-key the cached train gradient to the tensors the hook passes
+        layer._ghost_cached_train_grad = (A.data_ptr(), B.data_ptr(), A.size(0), cached[3])
+
+
+def _compute_conv2d_train_grad(layer: nn.Conv2d, A: torch.Tensor, B: torch.Tensor, val_batch_size: int):
+    """nn.Conv2d averaged train gradient in the weight's shape (reference :566-592)."""
+    n_train = A.size(0) - val_batch_size
+    if n_train <= 0:
+        return None
+    cached = layer.__dict__.pop("_ghost_cached_train_grad", None)
+    if cached is not None and cached[0] == A.data_ptr() and cached[1] == B.data_ptr() and cached[2] == A.size(0):
+        grad = cached[3]
+    else:
+        A_tok, B_tok = _conv2d_tokens(layer, A, B)
+        grad = ops.wgrad(B_tok[:n_train], A_tok[:n_train], _backprop_scale(layer) / n_train, A.dtype)
+    layer.__dict__.pop("_ghost_conv_tokens", None)
+    return grad.view_as(layer.weight)
+
+
 _supported_layers_dotprod = {
     nn.Linear: (_compute_linear_dot_product, _compute_linear_train_grad),
     nn.Embedding: (_compute_embedding_dot_product, _compute_embedding_train_grad),
     nn.LayerNorm: (_compute_layernorm_dot_product, _compute_layernorm_train_grad),
+    nn.Conv2d: (_compute_conv2d_dot_product, _compute_conv2d_train_grad),
 }
 if _HFConv1D is not None:
     _supported_layers_dotprod[_HFConv1D] = (_compute_Conv1D_dot_product, _compute_Conv1D_train_grad)

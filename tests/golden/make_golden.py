@@ -141,6 +141,30 @@ def main():
         out[f"ln_{tag}_train_grad_b"] = f32(ln.bias.train_grad)
     out["ln_eps"] = np.array([nn.LayerNorm(Fdim).eps])
 
+    # ---------------- Conv2d ----------------
+    Ac = torch.randn(N, 3, 7, 6)
+    conv = nn.Conv2d(3, 5, kernel_size=(3, 2), stride=(2, 1), padding=(1, 0), dilation=(1, 2))
+    out[f"conv_A"] = f32(Ac)
+    Gc = torch.randn_like(conv(Ac)) / 5.0
+    out["conv_G"] = f32(Gc)
+    # The reference's ghost branch for Conv2d multiplies a [b, D, D] by a [b, p, p] tensor (it
+    # contracts over the output positions instead of the features, :550-554) and raises unless
+    # C*kh*kw == out_channels, so only the materialised branch can be recorded.
+    try:
+        c = nn.Conv2d(3, 5, kernel_size=(3, 2), stride=(2, 1), padding=(1, 0), dilation=(1, 2))
+        c.use_ghost_computation = True
+        ref._compute_conv2d_dot_product(c, Ac, Gc, 1)
+        out["conv_ghost_branch_runs"] = np.array([1])
+    except RuntimeError:
+        out["conv_ghost_branch_runs"] = np.array([0])
+    for nv in (1, n_v):
+        c = nn.Conv2d(3, 5, kernel_size=(3, 2), stride=(2, 1), padding=(1, 0), dilation=(1, 2))
+        c.use_ghost_computation = False
+        ref._compute_conv2d_dot_product(c, Ac, Gc, nv)
+        out[f"conv_nv{nv}_ghost0_w"] = f32(c.weight.grad_dot_prod)
+        out[f"conv_nv{nv}_ghost0_b"] = f32(c.bias.grad_dot_prod)
+    out["conv_train_grad"] = f32(ref._compute_conv2d_train_grad(conv, Ac, Gc * N, n_v))
+
     # ---------------- GradProj dense ----------------
     k_i, k_o = 4, 6
     P_i = pu.init_projection_matrix_gaussian(k_i, d, seed=42)

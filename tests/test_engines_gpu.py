@@ -219,6 +219,59 @@ def test_gpt2_like_per_module_parity(dtype, path_rule):
         L.PATH_RULE = old_rule
 
 
+@pytest.mark.parametrize("path_rule", ["gram", "persample"])
+def test_conv2d_network(path_rule, golden):
+    """A small CNN (Conv2d -> ReLU -> Conv2d -> pool -> Linear) in fp32: Conv2d dot products against
+    the float64 oracle on the captured tensors, train gradients against autograd."""
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as L
+    torch.manual_seed(5)
+
+    def build():
+        return nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.ReLU(), nn.Conv2d(8, 6, (3, 2), stride=(2, 1)),
+                             nn.ReLU(), nn.AdaptiveAvgPool2d(2), nn.Flatten(), nn.Linear(24, 5))
+
+    model = build().cuda()
+    ref_model = build()
+    ref_model.load_state_dict({k: v.cpu() for k, v in model.state_dict().items()})
+    n_t, n_v = 6, 3
+    X = torch.randn(n_t + n_v, 3, 10, 9)
+    Y = torch.randint(0, 5, (n_t + n_v,))
+    old = L.PATH_RULE
+    L.PATH_RULE = path_rule
+    try:
+        eng = GradDotProdEngine(model, val_batch_size=n_v)
+        eng.attach(torch.optim.SGD(model.parameters(), lr=0.1))
+        cap = {}
+        for name, m in model.named_modules():
+            if isinstance(m, nn.Conv2d):
+                m.register_forward_hook(lambda l, i, o, n=name: cap.setdefault(n, {}).__setitem__("A", i[0].detach().cpu()))
+                m.register_full_backward_hook(lambda l, gi, go, n=name: cap[n].__setitem__("B", go[0].detach().cpu()))
+        nn.functional.cross_entropy(model(X.cuda()), Y.cuda()).backward()
+        for name, m in model.named_modules():
+            if isinstance(m, nn.Conv2d):
+                Mw, Mb = O.conv2d_dot_exact(cap[name]["A"], cap[name]["B"], n_v, m.kernel_size, m.dilation,
+                                            m.padding, m.stride)
+                assert O.rel_fro(m.weight.grad_dot_prod_matrix, Mw) < 1e-4, name
+                assert O.rel_fro(m.bias.grad_dot_prod_matrix, Mb) < 1e-4, name
+        nn.functional.cross_entropy(ref_model(X[:n_t]), Y[:n_t]).backward()
+        for (name, p), (_, r) in zip(model.named_parameters(), ref_model.named_parameters()):
+            assert p.train_grad.shape == r.grad.shape
+            assert O.rel_fro(p.train_grad, r.grad) < 1e-4, name
+        eng.detach()
+    finally:
+        L.PATH_RULE = old
+    # the reference's materialised branch at one validation sample (golden) through the layer functions
+    A = torch.from_numpy(golden["conv_A"]).cuda()
+    G = torch.from_numpy(golden["conv_G"]).cuda()
+    conv = nn.Conv2d(3, 5, kernel_size=(3, 2), stride=(2, 1), padding=(1, 0), dilation=(1, 2)).cuda()
+    L._compute_conv2d_dot_product(conv, A, G, 1)
+    assert O.rel_fro(conv.weight.grad_dot_prod, torch.from_numpy(golden["conv_nv1_ghost0_w"])) < 2e-2
+    assert O.rel_fro(conv.bias.grad_dot_prod, torch.from_numpy(golden["conv_nv1_ghost0_b"])) < 2e-2
+    tg = L._compute_conv2d_train_grad(conv, A, G * 8, 3)
+    assert O.rel_fro(tg, torch.from_numpy(golden["conv_train_grad"])) < 1e-4
+
+
 def test_double_attach_and_error_types():
     from ghostsuite_b200.ghostEngines import GradDotProdEngine
     from ghostsuite_b200.ghostEngines import autograd_grad_sample_dotprod as H

@@ -138,3 +138,20 @@ def test_gradproj_dense(golden):
     grads = torch.einsum("btp,btd->bpd", G.double(), A.double()) * A.shape[0]
     naive = torch.from_numpy(golden["gp_P_o"]).double() @ grads @ torch.from_numpy(golden["gp_P_i"]).double().t()
     close(torch.from_numpy(golden["gp_linear"]), naive, rtol=1e-4, atol=1e-5)
+
+
+def test_conv2d(golden):
+    """Materialised branch of the reference (its ghost branch for Conv2d raises on shape grounds)."""
+    assert int(golden["conv_ghost_branch_runs"][0]) == 0
+    A = torch.from_numpy(golden["conv_A"])
+    G = torch.from_numpy(golden["conv_G"])
+    kw = dict(kernel_size=(3, 2), dilation=(1, 2), padding=(1, 0), stride=(2, 1))
+    for nv in (1, N_V):
+        w, b = O.conv2d_dot_reference(A, G, nv, use_ghost=False, **kw)
+        close(w.float(), golden[f"conv_nv{nv}_ghost0_w"], rtol=1e-3, atol=1e-3)
+        close(b.float(), golden[f"conv_nv{nv}_ghost0_b"], rtol=1e-3, atol=1e-3)
+    Mw, Mb = O.conv2d_dot_exact(A, G, 1, **kw)
+    assert O.rel_fro(torch.from_numpy(golden["conv_nv1_ghost0_w"]), Mw[0]) < 2e-2
+    assert O.rel_fro(torch.from_numpy(golden["conv_nv1_ghost0_b"]), Mb[0]) < 2e-2
+    tg = O.conv2d_train_grad(A, G * N, N_V, (5, 3, 3, 2), **kw)
+    close(tg, golden["conv_train_grad"], rtol=1e-5, atol=1e-6)
