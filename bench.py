@@ -314,6 +314,9 @@ KERNEL_CASES = {
     "gram_T128": ("gram", dict(n_t=256, n_v=32, T=128, d=4096, p=11008)),       # single-layer config, T = 128
     "gram_T512": ("gram", dict(n_t=256, n_v=32, T=512, d=4096, p=11008)),
     "gram_small": ("gram", dict(n_t=64, n_v=8, T=256, d=2048, p=4096)),          # sized for an ncu capture
+    "gram_pair_T128": ("gram_pair", dict(n_t=256, n_v=32, T=128, d=4096, p=11008)),   # cta_group::2 variant
+    "gram_pair_T512": ("gram_pair", dict(n_t=256, n_v=32, T=512, d=4096, p=11008)),
+    "gram_pair_small": ("gram_pair", dict(n_t=64, n_v=8, T=256, d=2048, p=4096)),
     "persample_cfc": ("persample", dict(n_t=32, n_v=8, T=1024, d=768, p=3072)),  # GPT-2 mlp.c_fc
     "persample_T512": ("persample", dict(n_t=256, n_v=32, T=512, d=4096, p=11008)),
     "persample_T2048": ("persample", dict(n_t=64, n_v=32, T=2048, d=4096, p=11008)),
@@ -350,6 +353,9 @@ def run_kernels(args):
         def rnd(*shape, scale=1.0, dtype=torch.bfloat16):
             return (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
 
+        _lib.check(_lib.load().ghost_set_gram_pair_mode(1 if kind == "gram_pair" else 0))
+        if kind == "gram_pair":
+            kind = "gram"
         if kind in ("gram", "persample", "wgrad"):
             N = c["n_t"] + c["n_v"]
             A = rnd(N, c["T"], c["d"], scale=c["d"] ** -0.5)
@@ -402,6 +408,7 @@ def run_kernels(args):
         results[name] = entry
         del fn
         torch.cuda.empty_cache()
+    _lib.check(_lib.load().ghost_set_gram_pair_mode(0))
     print(json.dumps({"mode": "kernels", "peaks": {"tensor_burst_tflops": burst, "hbm_gbs": peaks["hbm"],
                                                     "source": peaks["source"]}, "results": results}), flush=True)
 

@@ -291,7 +291,20 @@ static int launch_gram(const void* a_t, const void* a_v, const void* g_t, const 
   return post_launch("ghost_gram_kernel");
 }
 
+int launch_gram_pair(const void* a_t, const void* a_v, const void* g_t, const void* g_v, int n_train, int n_val,
+                     long long T, int ka, int kg, long long ld_at, long long ld_av, long long ld_gt,
+                     long long ld_gv, int round_mode, float scale, float* M, const DeviceState* ds,
+                     cudaStream_t stream);
+
+// 0: single-CTA kernels only; 1: CTA-pair kernel for problems with at least 512 x 256 tokens
+static int g_gram_pair_mode = 0;
+
 }  // namespace gb
+
+extern "C" int ghost_set_gram_pair_mode(int mode) {
+  gb::g_gram_pair_mode = mode ? 1 : 0;
+  return GHOST_OK;
+}
 
 extern "C" int ghost_gram_dot_bf16(const void* a_train, const void* a_val, const void* g_train,
                                    const void* g_val, int n_train, int n_val, long long T, int ka,
@@ -311,6 +324,9 @@ extern "C" int ghost_gram_dot_bf16(const void* a_train, const void* a_val, const
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
   const long long rows_v = static_cast<long long>(n_val) * T;
+  if (g_gram_pair_mode && rows_v >= 256 && static_cast<long long>(n_train) * T >= 512)
+    return launch_gram_pair(a_train, a_val, g_train, g_val, n_train, n_val, T, ka, kg, ld_at, ld_av, ld_gt,
+                            ld_gv, round_mode, scale, M_out, ds, st);
   if (rows_v <= 128)
     return launch_gram<128>(a_train, a_val, g_train, g_val, n_train, n_val, T, ka, kg, ld_at, ld_av,
                             ld_gt, ld_gv, round_mode, scale, M_out, ds, st);

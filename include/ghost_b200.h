@@ -73,6 +73,11 @@ int ghost_gram_dot_bf16(const void* a_train, const void* a_val, const void* g_tr
                         long long ld_at, long long ld_av, long long ld_gt, long long ld_gv,
                         int round_mode, float scale, float* M_out, void* stream);
 
+/* Selects the kernel behind ghost_gram_dot_bf16: 0 = one CTA per 128 x 256 tile, 1 = a CTA pair
+ * (tcgen05 cta_group::2) per 256 x 256 tile for problems of at least 512 train x 256 validation
+ * tokens.  Process-wide. */
+int ghost_set_gram_pair_mode(int mode);
+
 /* ---- train-gradient recovery ------------------------------------------------------------------- */
 /* out[m_cols, n_cols] (= or +=) scale * sum_{row < n_rows} X[row, :]^T Y[row, :].
  * nn.Linear weight [d_out, d_in]: X = out-grad, Y = activations; HF Conv1D weight [d_in, d_out]:

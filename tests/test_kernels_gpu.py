@@ -52,6 +52,30 @@ def test_gram_dot(case, dtype):
     assert O.rel_fro(M, ref) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", [(5, 3, 130, 72, 40), (4, 2, 256, 128, 64), (9, 2, 300, 200, 136),
+                                  (700, 300, 1, 64, 48), (3, 5, 513, 96, 256)])
+def test_gram_dot_cta_pair_kernel(case, dtype):
+    """The cta_group::2 variant (256 x 256 tile per CTA pair) against the oracle and the
+    single-CTA kernel, including ragged tiles and an odd number of tiles."""
+    from ghostsuite_b200 import _lib
+    lib = _lib.load()
+    n_t, n_v, T, d, p = case
+    A, G = make(n_t + n_v, T, d, p, dtype, seed=21)
+    ref = O.linear_dot_exact(A, G, n_v) if n_t * n_v < 5000 else None
+    try:
+        _lib.check(lib.ghost_set_gram_pair_mode(1))
+        M2 = ops().gram_dot(A.cuda(), G.cuda(), n_v)
+        after()
+    finally:
+        _lib.check(lib.ghost_set_gram_pair_mode(0))
+    M1 = ops().gram_dot(A.cuda(), G.cuda(), n_v)
+    after()
+    assert O.rel_fro(M2, M1.cpu()) < 1e-5
+    if ref is not None:
+        assert O.rel_fro(M2, ref) < TOL[dtype]
+
+
 def test_gram_dot_reference_rounding_mode():
     """round_mode=1 reproduces the reference's bf16-rounded Grams (vector = column sums)."""
     n_t, n_v, T, d, p = 5, 3, 6, 16, 24
