@@ -134,7 +134,8 @@ def _train_grad_bias_from_layer(layer: nn.Module, val_batch_size: int, loss_redu
     scale = float(getattr(layer, "_ghost_backprop_scale", 1.0))
     if loss_reduction == "mean":
         scale /= n_train
-    return ops.rows_sum(colsums, n_train, scale, layer.bias.dtype if B.dtype == layer.bias.dtype else B.dtype)
+    out_dtype = layer.bias.dtype if layer.bias.dtype in (torch.float32, torch.bfloat16) else torch.float32
+    return ops.rows_sum(colsums, n_train, scale, out_dtype)
 
 
 def _compute_train_grad_bias(B: torch.Tensor, val_batch_size: int, loss_reduction: str = "mean") -> torch.Tensor:
@@ -144,4 +145,5 @@ def _compute_train_grad_bias(B: torch.Tensor, val_batch_size: int, loss_reductio
     if n_train <= 0:
         raise ValueError("No training samples to compute gradients, check batch sizes.")
     colsums = ops.colsum(B)
-    return ops.rows_sum(colsums, n_train, 1.0 / n_train if loss_reduction == "mean" else 1.0, B.dtype)
+    out_dtype = B.dtype if B.dtype in (torch.float32, torch.bfloat16) else torch.float32
+    return ops.rows_sum(colsums, n_train, 1.0 / n_train if loss_reduction == "mean" else 1.0, out_dtype)

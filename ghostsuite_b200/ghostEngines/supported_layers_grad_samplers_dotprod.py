@@ -113,6 +113,15 @@ def _check_batch(A, B, val_batch_size: int) -> int:
     return n_train
 
 
+def _grad_dtype(param: torch.Tensor, A: torch.Tensor) -> torch.dtype:
+    """Train gradients are produced directly in the parameter's dtype when the kernels can write it
+    (float32 / bfloat16), so that ``param.grad = param.train_grad`` also works under autocast, where
+    activations are bf16 and parameters fp32 (the reference returns the activation dtype)."""
+    if param.dtype in (torch.float32, torch.bfloat16):
+        return param.dtype
+    return torch.float32 if A.dtype != torch.bfloat16 else torch.bfloat16
+
+
 def _backprop_scale(layer: nn.Module) -> float:
     """Factor that turns the stored out-grad into the reference's ``B * batch_size``.
 
@@ -149,7 +158,7 @@ def _dense_dot_product(layer: nn.Module, A: torch.Tensor, B: torch.Tensor, val_b
             want = bool(getattr(layer.weight, "initially_requires_grad", True))
             M, grad = ops.persample_dot(X, Y, val_batch_size, want_grad=want,
                                         grad_scale=_backprop_scale(layer) / n_train,
-                                        grad_dtype=A.dtype)
+                                        grad_dtype=_grad_dtype(layer.weight, A))
             if want:
                 layer._ghost_cached_train_grad = (A.data_ptr(), B.data_ptr(), N, grad)
         _set_dot(layer.weight, M)
@@ -169,7 +178,7 @@ def _dense_train_grad(layer: nn.Module, A: torch.Tensor, B: torch.Tensor, val_ba
     scale = _backprop_scale(layer) / n_train
     A_t, B_t = A[:n_train], B[:n_train]
     X, Y = (A_t, B_t) if weight_is_in_by_out else (B_t, A_t)
-    return ops.wgrad(X, Y, scale, A.dtype)
+    return ops.wgrad(X, Y, scale, _grad_dtype(layer.weight, A))
 
 
 def _compute_linear_dot_product(layer: nn.Linear, A: torch.Tensor, B: torch.Tensor,
@@ -312,7 +321,8 @@ def _compute_conv2d_train_grad(layer: nn.Conv2d, A: torch.Tensor, B: torch.Tenso
         grad = cached[3]
     else:
         A_tok, B_tok = _conv2d_tokens(layer, A, B)
-        grad = ops.wgrad(B_tok[:n_train], A_tok[:n_train], _backprop_scale(layer) / n_train, A.dtype)
+        grad = ops.wgrad(B_tok[:n_train], A_tok[:n_train], _backprop_scale(layer) / n_train,
+                         _grad_dtype(layer.weight, A))
     layer.__dict__.pop("_ghost_conv_tokens", None)
     return grad.view_as(layer.weight)
 

@@ -113,7 +113,10 @@ def _dt_flag(t: torch.Tensor) -> int:
 
 
 def _as3d(x: torch.Tensor) -> torch.Tensor:
-    """[N, d] -> [N, 1, d]; [N, ..., d] -> [N, T, d] (contiguous)."""
+    """[N, d] -> [N, 1, d]; [N, ..., d] -> [N, T, d] (contiguous).  float16 / float64 inputs are
+    widened / narrowed to float32 first (the kernels take float32 and bfloat16)."""
+    if x.dtype in (torch.float16, torch.float64):
+        x = x.float()
     if x.dim() <= 2:
         x = x.unsqueeze(1)
     else:

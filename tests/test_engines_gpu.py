@@ -272,6 +272,35 @@ def test_conv2d_network(path_rule, golden):
     assert O.rel_fro(tg, torch.from_numpy(golden["conv_train_grad"])) < 1e-4
 
 
+def test_autocast_and_fp16_inputs():
+    """fp32 parameters under bf16 autocast: train gradients come out in the parameter dtype and the
+    optimizer can consume them; fp16 tensors are accepted by the kernels' wrappers."""
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    from ghostsuite_b200 import ops
+    torch.manual_seed(2)
+    model = nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.LayerNorm(64), nn.Linear(64, 7)).cuda()
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    eng = GradDotProdEngine(model, val_batch_size=3)
+    eng.attach(opt)
+    X = torch.randn(9, 5, 32, device="cuda")
+    Y = torch.randint(0, 7, (9, 5), device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = nn.functional.cross_entropy(model(X).reshape(-1, 7).float(), Y.reshape(-1))
+    loss.backward()
+    for name, p in model.named_parameters():
+        assert p.train_grad.dtype == p.dtype == torch.float32, name
+        assert p.grad_dot_prod_matrix.shape == (3, 6)
+    eng.prepare_gradients()
+    opt.step()
+    eng.clear_gradients()
+    eng.detach()
+    A = torch.randn(6, 10, 24, device="cuda").half()
+    G = torch.randn(6, 10, 16, device="cuda").half()
+    M = ops.gram_dot(A, G, 2)
+    torch.cuda.synchronize()
+    assert O.rel_fro(M, O.linear_dot_exact(A.cpu(), G.cpu(), 2)) < 1e-4
+
+
 def test_double_attach_and_error_types():
     from ghostsuite_b200.ghostEngines import GradDotProdEngine
     from ghostsuite_b200.ghostEngines import autograd_grad_sample_dotprod as H
