@@ -551,6 +551,11 @@ def main():
             print(json.dumps(line), flush=True)
         return
 
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1; keep stdout for the one
+    # JSON line by pointing fd 1 at stderr until the result is ready.
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -558,6 +563,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
         line = run_ours(args, rank, world, local_rank)
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
         if line is not None:
             print(json.dumps(line), flush=True)
     finally:
