@@ -35,6 +35,11 @@ struct TileDotParams {
   float* M;                   // [n_val, n_train]
   float* sum;                 // [tiles * 32768] fp32 or null
   int sum_init;               // 1: this group overwrites sum, 0: it accumulates
+  // direct output of the train gradient (single-group case): out[r, c] (= or +=) out_scale * sum
+  void* out;                  // [m_cols, n_cols] row-major in the parameter dtype, or null
+  int out_is_f32, out_accumulate;
+  int m_cols, n_cols, n_tiles_n;
+  float out_scale;
   int* err;
 };
 
@@ -119,7 +124,7 @@ tile_dot_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant_
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int q = 0; q < 4; ++q) acc[i][q] = 0.f;
-      const bool do_sum = (v0 == 0) && (p.sum != nullptr);
+      const bool do_sum = (v0 == 0) && (p.sum != nullptr || p.out != nullptr);
       bool bvalid[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) bvalid[q] = (j0 + warp * 4 + q) < p.n_grp;
@@ -159,9 +164,29 @@ tile_dot_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant_
           float t = 0.f;
 #pragma unroll
           for (int ww = 0; ww < 8; ++ww) t += s_part[ww * kTdCols + threadIdx.x];
-          float* dst = p.sum + s * kTdCols + threadIdx.x;
-          if (!(p.sum_init && j0 == 0)) t += *dst;
-          *dst = t;
+          if (p.out != nullptr) {
+            // one stage is one 256-column row segment of one 128 x 256 tile
+            const long long tile = s / kStagesPerTile;
+            const int r = static_cast<int>(tile / p.n_tiles_n) * 128 + static_cast<int>(s % kStagesPerTile);
+            const int c = static_cast<int>(tile % p.n_tiles_n) * 256 + static_cast<int>(threadIdx.x);
+            if (r < p.m_cols && c < p.n_cols) {
+              const long long o = static_cast<long long>(r) * p.n_cols + c;
+              float val = t * p.out_scale;
+              if (p.out_is_f32) {
+                float* dst = static_cast<float*>(p.out) + o;
+                if (p.out_accumulate || j0 > 0) val += *dst;
+                *dst = val;
+              } else {
+                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + o;
+                if (p.out_accumulate || j0 > 0) val += __bfloat162float(*dst);
+                *dst = __float2bfloat16_rn(val);
+              }
+            }
+          } else {
+            float* dst = p.sum + s * kTdCols + threadIdx.x;
+            if (!(p.sum_init && j0 == 0)) t += *dst;
+            *dst = t;
+          }
         }
       }
       if (!alive) break;
@@ -224,9 +249,12 @@ static int launch_tile_dot_t(const void* V, int v_samples, const void* W, int w_
 // W: [tiles][w_samples][32768] with the group's train samples at index 0..n_grp-1.
 int launch_tile_dot(const void* V, int v_samples, int v_off, const void* W, int w_samples, int is_f32,
                     long long tiles, int n_val, int n_grp, int b0, int n_train, float scale, float* M,
-                    float* sum, int sum_init, const DeviceState* ds, cudaStream_t st) {
+                    float* sum, int sum_init, void* out, int out_is_f32, int out_accumulate, int m_cols,
+                    int n_cols, int n_tiles_n, float out_scale, const DeviceState* ds, cudaStream_t st) {
   TileDotParams p;
   p.v_off = v_off;
+  p.out = out; p.out_is_f32 = out_is_f32; p.out_accumulate = out_accumulate;
+  p.m_cols = m_cols; p.n_cols = n_cols; p.n_tiles_n = n_tiles_n; p.out_scale = out_scale;
   p.stages = tiles * (kTileElems / kTdCols);
   p.stages_per_cta = 0;
   p.n_val = n_val; p.n_grp = n_grp; p.b0 = b0; p.n_train = n_train;

@@ -393,7 +393,8 @@ extern "C" int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, 
 namespace gb {
 int launch_tile_dot(const void* V, int v_samples, int v_off, const void* W, int w_samples, int is_f32,
                     long long tiles, int n_val, int n_grp, int b0, int n_train, float scale, float* M,
-                    float* sum, int sum_init, const DeviceState* ds, cudaStream_t st);
+                    float* sum, int sum_init, void* out, int out_is_f32, int out_accumulate, int m_cols,
+                    int n_cols, int n_tiles_n, float out_scale, const DeviceState* ds, cudaStream_t st);
 int launch_tile_sum_finalize(const float* sum, int n_tiles_n, void* out, int out_is_f32, int rows, int cols,
                              float scale, int accumulate, const DeviceState* ds, cudaStream_t st);
 }
@@ -472,10 +473,17 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
     p.sample0 = 0;
     p.vgrad = vws;
     if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+    // With a single group the streaming kernel can write the train gradient itself (scaled, in the
+    // parameter dtype): no fp32 sum buffer, no finalize pass.  A bf16 output is only written
+    // directly when one 32-sample block covers the batch, so it is rounded once.
+    const bool direct = grad_out && (grad_is_f32 || n_train <= 32);
     if ((rc = launch_tile_dot(vws, static_cast<int>(N), n_train, vws, static_cast<int>(N), v_is_f32, tiles,
-                              n_val, n_train, 0, n_train, dot_scale, M_out, grad_out ? sum : nullptr, 1,
-                              ds, st)) != GHOST_OK)
+                              n_val, n_train, 0, n_train, dot_scale, M_out,
+                              (grad_out && !direct) ? sum : nullptr, 1, direct ? grad_out : nullptr,
+                              grad_is_f32, grad_accumulate, m_cols, n_cols, p.n_tiles, grad_scale, ds,
+                              st)) != GHOST_OK)
       return rc;
+    if (direct || !grad_out) return GHOST_OK;
   } else {
     // validation tiles once, then the train samples one group at a time
     p.samples = n_val;
@@ -489,7 +497,8 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
       p.vgrad = wws;
       if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
       if ((rc = launch_tile_dot(vws, n_val, 0, wws, g, v_is_f32, tiles, n_val, g, b0, n_train, dot_scale,
-                                M_out, grad_out ? sum : nullptr, b0 == 0 ? 1 : 0, ds, st)) != GHOST_OK)
+                                M_out, grad_out ? sum : nullptr, b0 == 0 ? 1 : 0, nullptr, 0, 0, m_cols,
+                                n_cols, p.n_tiles, 1.f, ds, st)) != GHOST_OK)
         return rc;
     }
   }
