@@ -41,6 +41,29 @@ METRIC = "train tokens/sec (ghost dot-prod + train grad, GPT-2 124M)"
 
 
 # ------------------------------------------------------------------------------------------------
+_SAVED_STDOUT = None
+
+
+def guard_stdout():
+    """Point file descriptor 1 at stderr so that library banners and engine log lines do not mix with
+    the JSON result; emit() restores it."""
+    global _SAVED_STDOUT
+    if _SAVED_STDOUT is None:
+        sys.stdout.flush()
+        _SAVED_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    global _SAVED_STDOUT
+    sys.stdout.flush()
+    if _SAVED_STDOUT is not None:
+        os.dup2(_SAVED_STDOUT, 1)
+        os.close(_SAVED_STDOUT)
+        _SAVED_STDOUT = None
+    print(json.dumps(obj), flush=True)
+
+
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -333,7 +356,7 @@ KERNEL_CASES = {
     "gradproj_llama_q": ("gradproj", dict(B=8, T=4096, n_i=4096, n_o=4096, k=64)),
     "gradproj_llama_gate": ("gradproj", dict(B=8, T=4096, n_i=4096, n_o=14336, k=64)),
     "gradproj_pythia_fc": ("gradproj", dict(B=16, T=2048, n_i=1024, n_o=4096, k=32)),
-    "gradproj_small": ("gradproj", dict(B=4, T=2048, n_i=2048, n_o=4096, k=64)),   # sized for an ncu capture
+    "gradproj_small": ("gradproj", dict(B=8, T=4096, n_i=1024, n_o=2048, k=64)),   # sized for an ncu capture
 }
 
 
@@ -414,8 +437,8 @@ def run_kernels(args):
         del fn
         torch.cuda.empty_cache()
     _lib.check(_lib.load().ghost_set_gram_pair_mode(0))
-    print(json.dumps({"mode": "kernels", "peaks": {"tensor_burst_tflops": burst, "hbm_gbs": peaks["hbm"],
-                                                    "source": peaks["source"]}, "results": results}), flush=True)
+    emit({"mode": "kernels", "peaks": {"tensor_burst_tflops": burst, "hbm_gbs": peaks["hbm"],
+                                                    "source": peaks["source"]}, "results": results})
 
 
 def run_crossover(args):
@@ -455,7 +478,7 @@ def run_crossover(args):
         del A, G
         torch.cuda.empty_cache()
     _lib.poll_kernel_error()
-    print(json.dumps({"mode": "crossover", "layer": {"d_in": d, "d_out": p, "dtype": "bf16"}, "rows": rows}), flush=True)
+    emit({"mode": "crossover", "layer": {"d_in": d, "d_out": p, "dtype": "bf16"}, "rows": rows})
 
 
 def run_gradproj_model(args):
@@ -509,12 +532,12 @@ def run_gradproj_model(args):
     ms = e0.elapsed_time(e1) / args.steps
     _lib.poll_kernel_error()
     n_files = len([f for f in os.listdir(out_dir) if f.startswith("proj_iter_")])
-    print(json.dumps({"mode": "gradproj_model", "workload": run_gradproj_model.__doc__.split("\n")[0],
+    emit({"mode": "gradproj_model", "workload": " ".join(run_gradproj_model.__doc__.split()),
                       "layers": len(eng.matched_layers), "total_proj_dim": eng.total_proj_dim,
                       "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
                       "wall_ms_per_step_including_disk_flush": wall * 1e3 / args.steps,
                       "d2h_bytes_per_step": B * eng.total_proj_dim * 4, "files_written": n_files,
-                      "gpu_launches": int(_lib.launch_count() - l0)}), flush=True)
+                      "gpu_launches": int(_lib.launch_count() - l0)})
     eng.cleanup()
     shutil.rmtree(out_dir, ignore_errors=True)
 
@@ -580,14 +603,14 @@ def run_gradproj_llama(args):
     rec = prof["ops"].get("gradproj_kernel", {"ms": 0.0, "calls": 1, "bytes": 0.0})
     peaks = _peaks()
     gbs = rec["bytes"] / (rec["ms"] * 1e-3) / 1e9 if rec["ms"] > 0 else 0.0
-    print(json.dumps({"mode": "gradproj_llama", "workload": " ".join(run_gradproj_llama.__doc__.split()),
+    emit({"mode": "gradproj_llama", "workload": " ".join(run_gradproj_llama.__doc__.split()),
                       "layers_projected": len(eng.matched_layers), "total_proj_dim": eng.total_proj_dim,
                       "batch": B, "seq_len": T, "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
                       "gradproj_kernel_ms_per_step": rec["ms"] / args.steps,
                       "gradproj_kernel_gbs": gbs, "gradproj_kernel_frac_of_measured_hbm": gbs / peaks["hbm"],
                       "d2h_bytes_per_step": B * eng.total_proj_dim * 4,
                       "max_memory_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
-                      "gpu_launches": int(_lib.launch_count() - l0)}), flush=True)
+                      "gpu_launches": int(_lib.launch_count() - l0)})
     eng.cleanup()
     shutil.rmtree(out_dir, ignore_errors=True)
 
@@ -612,6 +635,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    guard_stdout()
     if args.mode == "kernels":
         run_kernels(args)
         return
@@ -627,14 +651,9 @@ def main():
     if args.impl == "reference":
         line = run_reference_arm(args, rank)
         if line is not None:
-            print(json.dumps(line), flush=True)
+            emit(line)
         return
 
-    # Libraries (NCCL's version banner, for one) write to file descriptor 1; keep stdout for the one
-    # JSON line by pointing fd 1 at stderr until the result is ready.
-    sys.stdout.flush()
-    saved_stdout = os.dup(1)
-    os.dup2(2, 1)
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -642,10 +661,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
         line = run_ours(args, rank, world, local_rank)
-        sys.stdout.flush()
-        os.dup2(saved_stdout, 1)
         if line is not None:
-            print(json.dumps(line), flush=True)
+            emit(line)
     finally:
         if world > 1:
             import torch.distributed as dist
