@@ -26,7 +26,8 @@ struct GpParams {
   int kr_pad, kc_pad;      // MMA N extents (multiples of 16)
   int chunks_per_sample;
   long long units;         // B * chunks_per_sample
-  int units_per_cta;
+  int units_per_cta;       // base number of units per CTA
+  int units_extra;         // the first `units_extra` CTAs take one more
   float scale;
   float* out;              // sample b at out + b * out_stride, [k_r, k_c] row-major
   long long out_stride;
@@ -37,7 +38,7 @@ template <int KMAX>   // largest padded rank this instantiation handles (32, 64 
 struct GpCfg {
   static constexpr int BM = 128, BK = 64;
   static constexpr int kStageBytes = (BM + KMAX) * BK * 2;
-  static constexpr int kStages = (KMAX == 128) ? 3 : 4;   // 3 keeps KMAX = 128 inside 227 KB
+  static constexpr int kStages = (KMAX == 128) ? 3 : (KMAX == 64 ? 6 : 8);   // fills the 227 KB of shared memory
   static constexpr int kProjBytes = 2 * BM * KMAX * 4;     // fp32 staging of both projected blocks
   static constexpr int kSmemBytes = kStages * kStageBytes + kProjBytes + 1024 + 256;
   static constexpr int RT = KMAX / 16;   // output rows per thread (16 thread rows)
@@ -65,8 +66,9 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long u0 = static_cast<long long>(blockIdx.x) * p.units_per_cta;
-  long long u1 = u0 + p.units_per_cta;
+  const long long bx = blockIdx.x;
+  const long long u0 = bx * p.units_per_cta + (bx < p.units_extra ? bx : p.units_extra);
+  long long u1 = u0 + p.units_per_cta + (bx < p.units_extra ? 1 : 0);
   if (u1 > p.units) u1 = p.units;
   const int kb_r = (p.n_r + BK - 1) / BK;
   const int kb_total = kb_r + (p.n_c + BK - 1) / BK;
@@ -232,9 +234,9 @@ static int launch_gradproj(const CUtensorMap& tg, const CUtensorMap& tpr, const 
     GB_CUDA_OK(cudaFuncSetAttribute(gradproj_kernel<KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set[ds->device] = true;
   }
-  int grid = static_cast<int>(p.units < ds->sm_count ? p.units : ds->sm_count);
-  p.units_per_cta = static_cast<int>((p.units + grid - 1) / grid);
-  grid = static_cast<int>((p.units + p.units_per_cta - 1) / p.units_per_cta);
+  const int grid = static_cast<int>(p.units < ds->sm_count ? p.units : ds->sm_count);
+  p.units_per_cta = static_cast<int>(p.units / grid);
+  p.units_extra = static_cast<int>(p.units % grid);
   gradproj_kernel<KMAX><<<grid, 192, Cfg::kSmemBytes, st>>>(tg, tpr, ta, tpc, p);
   count_launch();
   return post_launch("gradproj_kernel");
