@@ -532,14 +532,15 @@ def run_gradproj_model(args):
     ms = e0.elapsed_time(e1) / args.steps
     _lib.poll_kernel_error()
     n_files = len([f for f in os.listdir(out_dir) if f.startswith("proj_iter_")])
-    emit({"mode": "gradproj_model", "workload": " ".join(run_gradproj_model.__doc__.split()),
-                      "layers": len(eng.matched_layers), "total_proj_dim": eng.total_proj_dim,
-                      "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
-                      "wall_ms_per_step_including_disk_flush": wall * 1e3 / args.steps,
-                      "d2h_bytes_per_step": B * eng.total_proj_dim * 4, "files_written": n_files,
-                      "gpu_launches": int(_lib.launch_count() - l0)})
+    total_proj_dim, n_layers = eng.total_proj_dim, len(eng.matched_layers)
     eng.cleanup()
     shutil.rmtree(out_dir, ignore_errors=True)
+    emit({"mode": "gradproj_model", "workload": " ".join(run_gradproj_model.__doc__.split()),
+                      "layers": n_layers, "total_proj_dim": total_proj_dim,
+                      "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
+                      "wall_ms_per_step_including_disk_flush": wall * 1e3 / args.steps,
+                      "d2h_bytes_per_step": B * total_proj_dim * 4, "files_written": n_files,
+                      "gpu_launches": int(_lib.launch_count() - l0)})
 
 
 def run_gradproj_llama(args):
@@ -603,16 +604,17 @@ def run_gradproj_llama(args):
     rec = prof["ops"].get("gradproj_kernel", {"ms": 0.0, "calls": 1, "bytes": 0.0})
     peaks = _peaks()
     gbs = rec["bytes"] / (rec["ms"] * 1e-3) / 1e9 if rec["ms"] > 0 else 0.0
+    total_proj_dim, n_layers = eng.total_proj_dim, len(eng.matched_layers)
+    eng.cleanup()
+    shutil.rmtree(out_dir, ignore_errors=True)
     emit({"mode": "gradproj_llama", "workload": " ".join(run_gradproj_llama.__doc__.split()),
-                      "layers_projected": len(eng.matched_layers), "total_proj_dim": eng.total_proj_dim,
+                      "layers_projected": n_layers, "total_proj_dim": total_proj_dim,
                       "batch": B, "seq_len": T, "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
                       "gradproj_kernel_ms_per_step": rec["ms"] / args.steps,
                       "gradproj_kernel_gbs": gbs, "gradproj_kernel_frac_of_measured_hbm": gbs / peaks["hbm"],
-                      "d2h_bytes_per_step": B * eng.total_proj_dim * 4,
+                      "d2h_bytes_per_step": B * total_proj_dim * 4,
                       "max_memory_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
                       "gpu_launches": int(_lib.launch_count() - l0)})
-    eng.cleanup()
-    shutil.rmtree(out_dir, ignore_errors=True)
 
 
 def main():

@@ -10,7 +10,9 @@
 // k_r x k_c contraction over the chunk's tokens is done in registers by the epilogue warps
 // (< 1 % of the flops).  Results go straight into the caller's [B, total_proj_dim] row slices with
 // fp32 atomics, so no [B, T, k] intermediate ever reaches HBM.  HBM-bound by design: arithmetic
-// intensity is about k flop per byte.
+// intensity is about k flop per byte.  What has to be kept small is the per-stage cost of the two
+// single threads that drive the pipeline (a barrier wait, an expect-tx, the TMA and MMA issues --
+// each on the order of 100 cycles), hence wide stages and one multi-lane TMA instruction per stage.
 //
 // CTA layout (192 threads): warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA issuer.
 #include "common.cuh"
@@ -36,14 +38,28 @@ struct GpParams {
 
 template <int KMAX>   // largest padded rank this instantiation handles (32, 64 or 128)
 struct GpCfg {
-  static constexpr int BM = 128, BK = 64;
-  static constexpr int kStageBytes = (BM + KMAX) * BK * 2;
-  static constexpr int kStages = (KMAX == 128) ? 3 : (KMAX == 64 ? 6 : 8);   // fills the 227 KB of shared memory
+  static constexpr int BM = 128, BK = 64;                  // BK: one 128-byte swizzle atom of bf16
+  // Columns per pipeline stage = ATOMS * 64.  The single threads that drive the pipeline pay a few
+  // hundred cycles per stage for the barrier round trip, so a stage carries two atoms when the
+  // shared memory allows it.
+  static constexpr int ATOMS = (KMAX == 128) ? 1 : 2;
+  static constexpr int kActAtomBytes = BM * BK * 2;
+  static constexpr int kProjAtomBytes = KMAX * BK * 2;
+  static constexpr int kStageBytes = ATOMS * (kActAtomBytes + kProjAtomBytes);
+  static constexpr int kStages = (KMAX == 32) ? 4 : 3;     // fills the 227 KB of shared memory
   static constexpr int kProjBytes = 2 * BM * KMAX * 4;     // fp32 staging of both projected blocks
   static constexpr int kSmemBytes = kStages * kStageBytes + kProjBytes + 1024 + 256;
   static constexpr int RT = KMAX / 16;   // output rows per thread (16 thread rows)
   static constexpr int CT = KMAX / 8;    // output cols per thread (8 thread cols)
+  static constexpr int NCH = KMAX / 4;   // float4 chunks per staged row
 };
+
+// Staged fp32 rows are stored with their float4 chunks XOR-permuted by the row index, so that the
+// 32 lanes of a warp (32 consecutive rows, same chunk) spread over all banks.
+template <int KMAX>
+__device__ __forceinline__ int gp_staged_index(int row, int elem) {
+  return row * KMAX + ((((elem >> 2) ^ row) & (KMAX / 4 - 1)) << 2) + (elem & 3);
+}
 
 template <int KMAX>
 __global__ void __launch_bounds__(192, 1)
@@ -52,6 +68,7 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
                 const GpParams p) {
   using Cfg = GpCfg<KMAX>;
   constexpr int BM = Cfg::BM, BK = Cfg::BK, kStages = Cfg::kStages, RT = Cfg::RT, CT = Cfg::CT;
+  constexpr int ATOMS = Cfg::ATOMS;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -70,8 +87,8 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
   const long long u0 = bx * p.units_per_cta + (bx < p.units_extra ? bx : p.units_extra);
   long long u1 = u0 + p.units_per_cta + (bx < p.units_extra ? 1 : 0);
   if (u1 > p.units) u1 = p.units;
-  const int kb_r = (p.n_r + BK - 1) / BK;
-  const int kb_total = kb_r + (p.n_c + BK - 1) / BK;
+  const int kb_r = (p.n_r + ATOMS * BK - 1) / (ATOMS * BK);            // pipeline stages over G's columns
+  const int kb_total = kb_r + (p.n_c + ATOMS * BK - 1) / (ATOMS * BK);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -89,24 +106,33 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 4) {
-    if (lane == 0) {
-      int stage = 0; uint32_t phase = 0; bool ok = true;
-      for (long long u = u0; u < u1 && ok; ++u) {
-        const int b = static_cast<int>(u / p.chunks_per_sample);
-        const int row0 = static_cast<int>(u % p.chunks_per_sample) * BM;
-        for (int kb = 0; kb < kb_total; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 421)) { ok = false; break; }
-          uint8_t* st = smem + stage * Cfg::kStageBytes;
-          const bool first = kb < kb_r;
-          const int kpad = first ? p.kr_pad : p.kc_pad;
-          mbar_arrive_expect_tx(&full_bar[stage], (BM + kpad) * BK * 2);
-          const int col = (first ? kb : kb - kb_r) * BK;
-          tma_load_3d(st, first ? &tm_g : &tm_a, &full_bar[stage], col, row0, b);
-          // projection tile: kpad rows x 64 cols, loaded as boxes of 16 rows
-          for (int r = 0; r < kpad; r += 16)
-            tma_load_2d(st + BM * BK * 2 + r * 128, first ? &tm_pr : &tm_pc, &full_bar[stage], col, r);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+    // Producer warp.  Lane 0 owns the barriers; lanes [0, ATOMS) each issue the TMA of one
+    // activation atom and lanes [ATOMS, 2*ATOMS) the TMA of one projection atom -- one warp
+    // instruction per stage instead of one thread issuing the boxes back to back.
+    const bool is_p = lane >= ATOMS;
+    const int atom = is_p ? lane - ATOMS : lane;
+    const uint32_t dst_off = is_p ? ATOMS * Cfg::kActAtomBytes + atom * Cfg::kProjAtomBytes
+                                  : atom * Cfg::kActAtomBytes;
+    int stage = 0; uint32_t phase = 0; bool ok = true;
+    for (long long u = u0; u < u1 && ok; ++u) {
+      const int b = static_cast<int>(u / p.chunks_per_sample);
+      const int row0 = static_cast<int>(u % p.chunks_per_sample) * BM;
+      for (int kb = 0; kb < kb_total; ++kb) {
+        int w = 1;
+        if (lane == 0) w = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 421) ? 1 : 0;
+        w = __shfl_sync(0xffffffffu, w, 0);
+        if (!w) { ok = false; break; }
+        const bool first = kb < kb_r;
+        if (lane == 0)
+          mbar_arrive_expect_tx(&full_bar[stage], ATOMS * (BM + (first ? p.kr_pad : p.kc_pad)) * BK * 2);
+        if (lane < 2 * ATOMS) {
+          // an atom past the last column starts out of range and is zero-filled
+          const int col = ((first ? kb : kb - kb_r) * ATOMS + atom) * BK;
+          const CUtensorMap* m = first ? (is_p ? &tm_pr : &tm_g) : (is_p ? &tm_pc : &tm_a);
+          tma_load_3d(smem + stage * Cfg::kStageBytes + dst_off, m, &full_bar[stage], col,
+                      is_p ? 0 : row0, is_p ? 0 : b);
         }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 5) {
@@ -123,14 +149,18 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 523)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(sa + BM * BK * 2, 16, 1024);
           const bool first = kb < kb_r;
           const bool fresh = (kb == 0) || (kb == kb_r);
+          const uint32_t d = first ? d_r : d_c;
+          const uint32_t idesc = first ? idesc_r : idesc_c;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_bf16(first ? d_r : d_c, adesc + 2 * k, bdesc + 2 * k, first ? idesc_r : idesc_c,
-                      (fresh && k == 0) ? 0u : 1u);
+          for (int at = 0; at < ATOMS; ++at) {
+            const uint64_t adesc = make_smem_desc_sw128(sa + at * Cfg::kActAtomBytes, 16, 1024);
+            const uint64_t bdesc = make_smem_desc_sw128(sa + ATOMS * Cfg::kActAtomBytes + at * Cfg::kProjAtomBytes, 16, 1024);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              umma_bf16(d, adesc + 2 * k, bdesc + 2 * k, idesc, (fresh && at == 0 && k == 0) ? 0u : 1u);
+          }
           umma_commit(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -165,6 +195,20 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
         }
       }
     };
+    // TMEM -> shared (fp32): row `tid` of one projected block
+    auto stage_block = [&](uint32_t taddr, int kpad, float* dst) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < kpad; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          if (c0 + j < KMAX)
+            *reinterpret_cast<float4*>(&dst[gp_staged_index<KMAX>(tid, c0 + j)]) =
+                make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      }
+    };
 
     bool alive = true;
     for (long long u = u0; u < u1; ++u) {
@@ -173,30 +217,8 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
       if (!named_bar_and(2, 128, mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.err, 124))) { alive = false; break; }
       tc_fence_after_sync();
       const uint32_t t_r = tmem_base + lane_base + acc * 256;
-      const uint32_t t_c = t_r + 128;
-      // TMEM -> shared (fp32).  Row `tid` of both projected blocks.
-#pragma unroll 1
-      for (int c0 = 0; c0 < p.kr_pad; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_r + c0, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          if (c0 + j < KMAX)
-            *reinterpret_cast<float4*>(&s_r[tid * KMAX + c0 + j]) =
-                make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-      }
-#pragma unroll 1
-      for (int c0 = 0; c0 < p.kc_pad; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_c + c0, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          if (c0 + j < KMAX)
-            *reinterpret_cast<float4*>(&s_c[tid * KMAX + c0 + j]) =
-                make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-      }
+      stage_block(t_r, p.kr_pad, s_r);
+      stage_block(t_r + 128, p.kc_pad, s_c);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -206,10 +228,16 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
 #pragma unroll 4
       for (int t = 0; t < BM; ++t) {
         float rr[RT], cc[CT];
+        if constexpr (RT >= 4) {
 #pragma unroll
-        for (int i = 0; i < RT; ++i) rr[i] = s_r[t * KMAX + ty * RT + i];
+          for (int i = 0; i < RT; i += 4)
+            *reinterpret_cast<float4*>(&rr[i]) = *reinterpret_cast<const float4*>(&s_r[gp_staged_index<KMAX>(t, ty * RT + i)]);
+        } else {
+          *reinterpret_cast<float2*>(&rr[0]) = *reinterpret_cast<const float2*>(&s_r[gp_staged_index<KMAX>(t, ty * RT)]);
+        }
 #pragma unroll
-        for (int j = 0; j < CT; ++j) cc[j] = s_c[t * KMAX + tx * CT + j];
+        for (int j = 0; j < CT; j += 4)
+          *reinterpret_cast<float4*>(&cc[j]) = *reinterpret_cast<const float4*>(&s_c[gp_staged_index<KMAX>(t, tx * CT + j)]);
 #pragma unroll
         for (int i = 0; i < RT; ++i)
 #pragma unroll
@@ -274,8 +302,9 @@ extern "C" int ghost_gradproj_dense_bf16(const void* G, const void* A, int B, lo
   int rc;
   if ((rc = make_tmap_bf16_3d(&tg, G, B, T, n_r, ldg, 128)) != GHOST_OK) return rc;
   if ((rc = make_tmap_bf16_3d(&ta, A, B, T, n_c, lda, 128)) != GHOST_OK) return rc;
-  if ((rc = make_tmap_bf16_2d(&tpr, P_r, k_r, n_r, ldpr, 16)) != GHOST_OK) return rc;
-  if ((rc = make_tmap_bf16_2d(&tpc, P_c, k_c, n_c, ldpc, 16)) != GHOST_OK) return rc;
+  // the projection matrices as one-sample 3-D operands, so that one TMA instruction form serves all four
+  if ((rc = make_tmap_bf16_3d(&tpr, P_r, 1, k_r, n_r, ldpr, p.kr_pad)) != GHOST_OK) return rc;
+  if ((rc = make_tmap_bf16_3d(&tpc, P_c, 1, k_c, n_c, ldpc, p.kc_pad)) != GHOST_OK) return rc;
   GB_CUDA_OK(cudaMemset2DAsync(out, out_stride * sizeof(float), 0, static_cast<size_t>(k_r) * k_c * sizeof(float), B, st));
   const int kmax = p.kr_pad > p.kc_pad ? p.kr_pad : p.kc_pad;
   if (kmax <= 32) return launch_gradproj<32>(tg, tpr, ta, tpc, p, ds, st);
