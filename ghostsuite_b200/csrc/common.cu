@@ -181,6 +181,33 @@ int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t samples, uint
   return GHOST_OK;
 }
 
+// [samples, rows, cols] bf16 seen as [samples, cols/64, rows, 64]: one box then covers `box_blocks`
+// adjacent 64-column blocks of `box_rows` rows, each block landing in shared memory as its own
+// 128-byte-swizzled [box_rows][64] panel.  cols must be a multiple of 64 (a partial last block
+// would read past the row instead of being zero-filled).
+int make_tmap_bf16_blocks(CUtensorMap* out, const void* base, uint64_t samples, uint64_t rows,
+                          uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_blocks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+    return fail(GHOST_ERR_INVALID, "TMA operand base %p is not 16-byte aligned", base);
+  if ((ld * 2) % 16 != 0)
+    return fail(GHOST_ERR_INVALID, "TMA operand row pitch %llu elements is not a multiple of 8",
+                (unsigned long long)ld);
+  if (rows == 0 || cols == 0 || samples == 0 || cols % 64 != 0)
+    return fail(GHOST_ERR_INVALID, "blocked TMA operand needs a column count that is a multiple of 64");
+  cuuint64_t dims[4] = {64, rows, cols / 64, samples};
+  cuuint64_t strides[3] = {ld * 2, 128, rows * ld * 2};
+  cuuint32_t box[4] = {64, box_rows, box_blocks, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled(blocked 4d) failed with CUresult %d", (int)r);
+  return GHOST_OK;
+}
+
 }  // namespace gb
 
 extern "C" {

@@ -55,6 +55,12 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t samples, uint64_t rows,
                       uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols = 64);
 
+// The same matrix seen as [samples, cols/64, rows, 64] (cols a multiple of 64): one box covers
+// `box_blocks` adjacent 64-column blocks of `box_rows` rows, each block landing in shared memory
+// as its own swizzled [box_rows][64] panel.  Coordinates: (0, row, block, sample).
+int make_tmap_bf16_blocks(CUtensorMap* out, const void* base, uint64_t samples, uint64_t rows,
+                          uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_blocks);
+
 // Plain (unswizzled) 2-D map of a row-major matrix of 2- or 4-byte elements; box = [box_rows, box_cols].
 int make_tmap_plain_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
                        uint64_t ld, uint32_t box_rows, uint32_t box_cols);

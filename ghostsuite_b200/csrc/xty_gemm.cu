@@ -44,6 +44,7 @@ struct XtyParams {
   void* vgrad;
   long long ld_v;
   int v_is_f32;
+  int blocked_x, blocked_y;  // operand map is the blocked 4-D form: one TMA per stage instead of one per 64 columns
   int* err;
 };
 
@@ -153,12 +154,22 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
           mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           const int row = kb * BK;
           const int z = p.sample0 + sample;
+          // Every TMA instruction costs the issuing thread on the order of 100 cycles whatever its
+          // size, and six of them per stage would take longer than the stage's MMAs.
+          if (p.blocked_x) {
+            tma_load_4d(st, &tm_x, &full_bar[stage], 0, row, m0 / 64, z);
+          } else {
 #pragma unroll
-          for (int j = 0; j < BM / 64; ++j)
-            tma_load_3d(st + j * (BK * 128), &tm_x, &full_bar[stage], m0 + j * 64, row, z);
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(st + j * (BK * 128), &tm_x, &full_bar[stage], m0 + j * 64, row, z);
+          }
+          if (p.blocked_y) {
+            tma_load_4d(st + BM * BK * 2, &tm_y, &full_bar[stage], 0, row, n0 / 64, z);
+          } else {
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_3d(st + BM * BK * 2 + j * (BK * 128), &tm_y, &full_bar[stage], n0 + j * 64, row, z);
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(st + BM * BK * 2 + j * (BK * 128), &tm_y, &full_bar[stage], n0 + j * 64, row, z);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -312,6 +323,20 @@ __global__ void xty_finalize_kernel(const float* __restrict__ ws, long long ld_w
   }
 }
 
+// Operand maps: the blocked form (one TMA instruction per operand and stage) when the column count
+// is a multiple of 64, else one box per 64 columns with the tail zero-filled by the bounds check.
+static int make_xty_maps(CUtensorMap* tx, CUtensorMap* ty, XtyParams& p, const void* X, const void* Y,
+                         long long samples, long long rows, long long ldx, long long ldy) {
+  int rc;
+  p.blocked_x = (p.m_cols % 64 == 0) ? 1 : 0;
+  p.blocked_y = (p.n_cols % 64 == 0) ? 1 : 0;
+  rc = p.blocked_x ? make_tmap_bf16_blocks(tx, X, samples, rows, p.m_cols, ldx, XtyCfg::BK, XtyCfg::BM / 64)
+                   : make_tmap_bf16_3d(tx, X, samples, rows, p.m_cols, ldx, XtyCfg::BK);
+  if (rc != GHOST_OK) return rc;
+  return p.blocked_y ? make_tmap_bf16_blocks(ty, Y, samples, rows, p.n_cols, ldy, XtyCfg::BK, XtyCfg::BN / 64)
+                     : make_tmap_bf16_3d(ty, Y, samples, rows, p.n_cols, ldy, XtyCfg::BK);
+}
+
 static int launch_xty(const CUtensorMap& tx, const CUtensorMap& ty, XtyParams p,
                       const DeviceState* ds, cudaStream_t st) {
   static bool attr_set[64] = {};
@@ -383,8 +408,7 @@ extern "C" int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, 
   p.err = ds->err_word;
   CUtensorMap tx, ty;
   int rc;
-  if ((rc = make_tmap_bf16_3d(&tx, X, 1, n_rows, m_cols, ldx, XtyCfg::BK)) != GHOST_OK) return rc;
-  if ((rc = make_tmap_bf16_3d(&ty, Y, 1, n_rows, n_cols, ldy, XtyCfg::BK)) != GHOST_OK) return rc;
+  if ((rc = make_xty_maps(&tx, &ty, p, X, Y, 1, n_rows, ldx, ldy)) != GHOST_OK) return rc;
   GB_CUDA_OK(cudaMemsetAsync(ws, 0, static_cast<size_t>(m_cols) * p.ld_acc * 4, st));
   if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
   return finalize_xty(p.acc_ws, p.ld_acc, out, out_is_f32, m_cols, n_cols, scale, accumulate, st);
@@ -463,8 +487,7 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   CUtensorMap tx, ty;
   int rc;
   const long long N = static_cast<long long>(n_train) + n_val;
-  if ((rc = make_tmap_bf16_3d(&tx, X, N, T, m_cols, ldx, XtyCfg::BK)) != GHOST_OK) return rc;
-  if ((rc = make_tmap_bf16_3d(&ty, Y, N, T, n_cols, ldy, XtyCfg::BK)) != GHOST_OK) return rc;
+  if ((rc = make_xty_maps(&tx, &ty, p, X, Y, N, T, ldx, ldy)) != GHOST_OK) return rc;
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
   if (group == n_train) {
     // everything fits: one GEMM pass over all samples (train first, validation last) into one
