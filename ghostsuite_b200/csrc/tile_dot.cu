@@ -8,13 +8,22 @@
 //     sum[k]   (+)= sum_b W[b][k]                        (the train gradient, reference :168)
 //
 // HBM-bound by design, so it is built as a copy pipeline: one producer thread feeds a ring of
-// shared-memory stages with TMA (one box of 8 validation rows and one of 32 train rows, 256
-// elements wide, per stage); eight compute warps consume them.  Warp w owns train samples
-// 4w..4w+3 of the block, lane l owns elements 8l..8l+7 of the stage, so every shared-memory read is
-// a conflict-free 16-byte access and a thread accumulates an 8 x 4 block of dot products.  Each
-// CTA owns a contiguous range of stages: the train-gradient sum is a plain read-modify-write
-// (deterministic, no atomics); the dot products are reduced with shuffles and added to M once per
-// CTA and block.
+// shared-memory stages with TMA (one box of validation rows and one of 32 train rows, 256 elements
+// wide, per stage); eight compute warps consume them.  Each CTA owns a contiguous range of stages:
+// the train-gradient sum is a plain read-modify-write (deterministic, no atomics); the dot
+// products are reduced inside the CTA and added to M once per CTA and block.
+//
+// bf16 tiles (tile_dot_mma_kernel): the stage is loaded as four 128-byte-swizzled 64-element
+// panels per operand, and both contractions run on the tensor cores through mma.sync
+// (m16n8k16, fp32 accumulate) fed by ldmatrix: the dot products as W[16 train x 16 k] x
+// V[16 k x 8 val], the train-gradient sum as mask[16 x 16 train] x W[16 train x 8 k] (a
+// transposed ldmatrix of the same rows).  Warp w owns elements 32w..32w+31 of the stage.  With the
+// arithmetic off the CUDA cores the kernel is bound by the stream, and up to 32 validation rows
+// share one pass over the train rows.
+//
+// fp32 tiles (tile_dot_kernel<float>): warp w owns train samples 4w..4w+3 of the block, lane l
+// elements 8l..8l+7 of the stage, every shared-memory read is a conflict-free 16-byte access and
+// a thread accumulates an 8 x 4 block of dot products on the CUDA cores (exact fp32 products).
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -206,6 +215,226 @@ tile_dot_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// bf16 tiles on mma.sync
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int NVT>   // 8-row validation blocks per stage (1, 2 or 4)
+struct TdMmaCfg {
+  static constexpr int kValRows = 8 * NVT;
+  static constexpr int kPanels = kTdCols / 64;                               // 64-element panels per stage row
+  static constexpr int kValBytes = kPanels * kValRows * 128;
+  static constexpr int kStageBytes = kValBytes + kPanels * kTdTrainRows * 128;   // 20 / 24 / 32 KB
+  static constexpr int kStages = NVT == 1 ? 8 : (NVT == 2 ? 6 : 5);
+  static constexpr int kRedBytes = 8 * kTdTrainRows * kValRows * 4;          // per-warp partial dot blocks
+  static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + kTdCols * 4 + 1024 + 256;
+};
+
+template <int NVT>
+__global__ void __launch_bounds__(288, 1)
+tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
+                    const TileDotParams p) {
+  using Cfg = TdMmaCfg<NVT>;
+  constexpr int kStages = Cfg::kStages, VR = Cfg::kValRows;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* s_red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);            // [8 warps][32][VR]
+  float* s_sum = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + Cfg::kRedBytes);   // [256]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kRedBytes + kTdCols * 4);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long s_begin = static_cast<long long>(blockIdx.x) * p.stages_per_cta;
+  const long long s_end = (s_begin + p.stages_per_cta < p.stages) ? s_begin + p.stages_per_cta : p.stages;
+  constexpr int kStagesPerTile = kTileElems / kTdCols;   // 128
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 8); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 8 && lane == 0) { tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_w); }
+  __syncthreads();
+
+  if (warp == 8) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int j0 = 0; j0 < p.n_grp && ok; j0 += kTdTrainRows)
+        for (int v0 = 0; v0 < p.n_val && ok; v0 += VR)
+          for (long long s = s_begin; s < s_end; ++s) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 431)) { ok = false; break; }
+            uint8_t* st = smem + stage * Cfg::kStageBytes;
+            const int tile = static_cast<int>(s / kStagesPerTile);
+            const int panel = static_cast<int>(s % kStagesPerTile) * Cfg::kPanels;
+            mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+            tma_load_4d(st, &tm_v, &full_bar[stage], 0, p.v_off + v0, panel, tile);
+            tma_load_4d(st + Cfg::kValBytes, &tm_w, &full_bar[stage], 0, j0, panel, tile);
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ compute warps 0-7
+  // This warp's slice of a stage: panel `pn`, 16-byte chunks c0..c0+3 (32 elements, two k-steps).
+  const int pn = warp >> 1, c0 = (warp & 1) * 4;
+  const int g = lane >> 2, q = lane & 3;
+  // ldmatrix lane addresses inside a stage (panel rows are 128 bytes, chunk index XOR (row & 7))
+  uint32_t a_off[2][2];      // W as the A operand: [m-tile][k-step]
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      const int row = mt * 16 + (lane & 15), chunk = c0 + 2 * ks + (lane >> 4);
+      a_off[mt][ks] = Cfg::kValBytes + pn * (kTdTrainRows * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
+    }
+  uint32_t b_off[NVT];       // V as the B operand: [n-tile], both k-steps in one x4
+#pragma unroll
+  for (int nt = 0; nt < NVT; ++nt) {
+    const int row = nt * 8 + (lane & 7), chunk = c0 + (lane >> 3);
+    b_off[nt] = pn * (VR * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
+  }
+  uint32_t t_off[4];         // W transposed, for the column sums: [8-element group], rows = lane
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    t_off[j] = Cfg::kValBytes + pn * (kTdTrainRows * 128) + lane * 128 + (((c0 + j) ^ (lane & 7)) << 4);
+
+  int stage = 0; uint32_t phase = 0;
+  bool alive = true;
+  for (int j0 = 0; j0 < p.n_grp && alive; j0 += kTdTrainRows) {
+    // A operand of the column-sum MMA: 1.0 where the train row (the k index) belongs to the group
+    uint32_t mask_a[2][4];
+#pragma unroll
+    for (int kr = 0; kr < 2; ++kr) {
+      const int k_lo = j0 + kr * 16 + q * 2, k_hi = k_lo + 8;
+      const uint32_t lo = (k_lo < p.n_grp ? 0x3F80u : 0u) | (k_lo + 1 < p.n_grp ? 0x3F800000u : 0u);
+      const uint32_t hi = (k_hi < p.n_grp ? 0x3F80u : 0u) | (k_hi + 1 < p.n_grp ? 0x3F800000u : 0u);
+      mask_a[kr][0] = lo; mask_a[kr][1] = lo; mask_a[kr][2] = hi; mask_a[kr][3] = hi;
+    }
+    for (int v0 = 0; v0 < p.n_val && alive; v0 += VR) {
+      float acc[2][NVT][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NVT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
+      const bool do_sum = (v0 == 0) && (p.sum != nullptr || p.out != nullptr);
+#pragma unroll 1
+      for (long long s = s_begin; s < s_end; ++s) {
+        const bool ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 132);
+        if (!named_bar_and(1, 256, ok)) { alive = false; break; }
+        const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
+        uint32_t a[2][2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) ldsm_x4(st + a_off[mt][ks], a[mt][ks]);
+#pragma unroll
+        for (int nt = 0; nt < NVT; ++nt) {
+          uint32_t b[4];
+          ldsm_x4(st + b_off[nt], b);
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            mma_bf16_16816(acc[mt][nt], a[mt][0], b[0], b[1]);
+            mma_bf16_16816(acc[mt][nt], a[mt][1], b[2], b[3]);
+          }
+        }
+        float csum[4][4];
+        if (do_sum) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t t[4];
+            ldsm_x4_trans(st + t_off[j], t);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) csum[j][e] = 0.f;
+            mma_bf16_16816(csum[j], mask_a[0], t[0], t[1]);
+            mma_bf16_16816(csum[j], mask_a[1], t[2], t[3]);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);     // this warp is done with the stage
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (do_sum) {
+          // every row of csum[j] holds the sums of elements 8j..8j+7 of this warp's slice
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (g == j) *reinterpret_cast<float2*>(&s_sum[warp * 32 + j * 8 + q * 2]) = make_float2(csum[j][0], csum[j][1]);
+          asm volatile("bar.sync 2, 256;" ::: "memory");
+          const float t = s_sum[threadIdx.x];
+          if (p.out != nullptr) {
+            // one stage is one 256-column row segment of one 128 x 256 tile
+            const long long tile = s / kStagesPerTile;
+            const int r = static_cast<int>(tile / p.n_tiles_n) * 128 + static_cast<int>(s % kStagesPerTile);
+            const int c = static_cast<int>(tile % p.n_tiles_n) * 256 + static_cast<int>(threadIdx.x);
+            if (r < p.m_cols && c < p.n_cols) {
+              const long long o = static_cast<long long>(r) * p.n_cols + c;
+              float val = t * p.out_scale;
+              if (p.out_is_f32) {
+                float* dst = static_cast<float*>(p.out) + o;
+                if (p.out_accumulate || j0 > 0) val += *dst;
+                *dst = val;
+              } else {
+                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + o;
+                if (p.out_accumulate || j0 > 0) val += __bfloat162float(*dst);
+                *dst = __float2bfloat16_rn(val);
+              }
+            }
+          } else {
+            float* dst = p.sum + s * kTdCols + threadIdx.x;
+            float val = t;
+            if (!(p.sum_init && j0 == 0)) val += *dst;
+            *dst = val;
+          }
+          // s_sum is rewritten only after the next stage's named barrier, which every thread
+          // reaches after this read
+        }
+      }
+      if (!alive) break;
+      // reduce the per-warp [32 train x VR val] partial blocks, one atomic per (v, b) and CTA
+      float* mine = s_red + warp * (kTdTrainRows * VR);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NVT; ++nt) {
+          const int b_lo = mt * 16 + g, v = nt * 8 + q * 2;
+          mine[b_lo * VR + v] = acc[mt][nt][0];
+          mine[b_lo * VR + v + 1] = acc[mt][nt][1];
+          mine[(b_lo + 8) * VR + v] = acc[mt][nt][2];
+          mine[(b_lo + 8) * VR + v + 1] = acc[mt][nt][3];
+        }
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      for (int idx = threadIdx.x; idx < kTdTrainRows * VR; idx += 256) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += s_red[w * (kTdTrainRows * VR) + idx];
+        const int b = j0 + idx / VR, v = v0 + idx % VR;
+        if (v < p.n_val && b < p.n_grp && t != 0.f)
+          atomicAdd(&p.M[static_cast<long long>(v) * p.n_train + p.b0 + b], t * p.scale);
+      }
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+    }
+  }
+}
+
 // out[r, c] (= or +=) scale * sum[tile(r, c)][r % 128][c % 256], cast to the parameter dtype
 template <typename OutT>
 __global__ void tile_sum_finalize_kernel(const float* __restrict__ sum, int n_tiles_n, OutT* __restrict__ out,
@@ -245,6 +474,31 @@ static int launch_tile_dot_t(const void* V, int v_samples, const void* W, int w_
   return post_launch("tile_dot_kernel");
 }
 
+template <int NVT>
+static int launch_tile_dot_mma(const void* V, int v_samples, const void* W, int w_samples, long long tiles,
+                               TileDotParams& p, const DeviceState* ds, cudaStream_t st) {
+  using Cfg = TdMmaCfg<NVT>;
+  CUtensorMap tv, tw;
+  int rc;
+  // [tiles][samples][32768] seen as [tiles][512 panels][samples][64]: one box = 4 panels of the stage
+  if ((rc = make_tmap_bf16_blocks(&tv, V, tiles, v_samples, kTileElems, kTileElems, Cfg::kValRows, Cfg::kPanels)) != GHOST_OK)
+    return rc;
+  if ((rc = make_tmap_bf16_blocks(&tw, W, tiles, w_samples, kTileElems, kTileElems, kTdTrainRows, Cfg::kPanels)) != GHOST_OK)
+    return rc;
+  static bool attr_set[64] = {};
+  if (!attr_set[ds->device]) {
+    GB_CUDA_OK(cudaFuncSetAttribute(tile_dot_mma_kernel<NVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set[ds->device] = true;
+  }
+  long long ctas = ds->sm_count;
+  if (ctas > p.stages) ctas = p.stages;
+  p.stages_per_cta = (p.stages + ctas - 1) / ctas;
+  ctas = (p.stages + p.stages_per_cta - 1) / p.stages_per_cta;
+  tile_dot_mma_kernel<NVT><<<static_cast<int>(ctas), 288, Cfg::kSmemBytes, st>>>(tv, tw, p);
+  count_launch();
+  return post_launch("tile_dot_mma_kernel");
+}
+
 // V: [tiles][v_samples][32768] with the validation samples at index v_off..v_off+n_val-1;
 // W: [tiles][w_samples][32768] with the group's train samples at index 0..n_grp-1.
 int launch_tile_dot(const void* V, int v_samples, int v_off, const void* W, int w_samples, int is_f32,
@@ -261,7 +515,9 @@ int launch_tile_dot(const void* V, int v_samples, int v_off, const void* W, int 
   p.scale = scale; p.M = M; p.sum = sum; p.sum_init = sum_init;
   p.err = ds->err_word;
   if (is_f32) return launch_tile_dot_t<float>(V, v_samples, W, w_samples, tiles, p, ds, st);
-  return launch_tile_dot_t<__nv_bfloat16>(V, v_samples, W, w_samples, tiles, p, ds, st);
+  if (n_val <= 8) return launch_tile_dot_mma<1>(V, v_samples, W, w_samples, tiles, p, ds, st);
+  if (n_val <= 16) return launch_tile_dot_mma<2>(V, v_samples, W, w_samples, tiles, p, ds, st);
+  return launch_tile_dot_mma<4>(V, v_samples, W, w_samples, tiles, p, ds, st);
 }
 
 int launch_tile_sum_finalize(const float* sum, int n_tiles_n, void* out, int out_is_f32, int rows, int cols,

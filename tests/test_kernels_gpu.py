@@ -37,6 +37,8 @@ LIN_CASES = [
     (2, 2, 300, 200, 136),    # validation rows straddle the 256-wide tile
     (4, 2, 128, 64, 64),      # exactly tile-aligned
     (2, 3, 37, 10, 50),       # feature sizes that are not multiples of 8
+    (33, 20, 9, 64, 264),     # 17..32 validation samples share one streaming pass; two train blocks
+    (40, 35, 20, 72, 136),    # more than 32 validation samples: two passes over the train tiles
 ]
 
 
