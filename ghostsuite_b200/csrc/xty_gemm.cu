@@ -44,6 +44,7 @@ struct XtyParams {
   void* vgrad;
   long long ld_v;
   int v_is_f32;
+  int sample_major;          // unit order (sample, tile), dealt round-robin to the CTAs; needs k_splits == 1
   int blocked_x, blocked_y;  // operand map is the blocked 4-D form: one TMA per stage instead of one per 64 columns
   int* err;
 };
@@ -95,12 +96,18 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tiles_mn = p.m_tiles * p.n_tiles;
-  // unit -> (tile, sample, split); sample is the fastest index so that consecutive units of a CTA
-  // neighbourhood reuse the same validation-gradient tiles from L2.
+  // unit -> (tile, sample, split).  Plain order: tile-major, samples and splits inside.  Tile-store
+  // mode walks (sample, outer tile index, inner tile index) instead, the inner index being the one
+  // with fewer tiles: neighbouring units share the tile of the wider operand.
   const long long units = static_cast<long long>(tiles_mn) * p.samples * p.k_splits;
   const int kb_sample = static_cast<int>((p.T + BK - 1) / BK);
-  const long long u_begin = static_cast<long long>(blockIdx.x) * p.units_per_cta;
-  const long long u_end = (u_begin + p.units_per_cta < units) ? u_begin + p.units_per_cta : units;
+  // plain order: a contiguous range per CTA; sample-major order: units dealt round-robin, so that
+  // at any time the CTAs work on neighbouring tiles of the same sample (their operand rows are
+  // adjacent in HBM and shared through L2)
+  const long long u_step = p.sample_major ? gridDim.x : 1;
+  const long long u_begin = p.sample_major ? blockIdx.x : static_cast<long long>(blockIdx.x) * p.units_per_cta;
+  const long long u_end = p.sample_major ? units
+                          : ((u_begin + p.units_per_cta < units) ? u_begin + p.units_per_cta : units);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -127,6 +134,17 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   auto decode = [&](long long u, int& tile, int& sample, int& kb0, int& kb1) {
+    if (p.sample_major) {
+      const bool n_inner = p.n_tiles <= p.m_tiles;
+      const int n_in = n_inner ? p.n_tiles : p.m_tiles;
+      sample = static_cast<int>(u / tiles_mn);
+      const int r = static_cast<int>(u % tiles_mn);
+      const int outer = r / n_in, in = r % n_in;
+      tile = n_inner ? outer * p.n_tiles + in : in * p.n_tiles + outer;
+      kb0 = 0;
+      kb1 = kb_sample;
+      return;
+    }
     const int inner = p.samples * p.k_splits;
     tile = static_cast<int>(u / inner);
     const int r = static_cast<int>(u % inner);
@@ -143,7 +161,7 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long u = u_begin; u < u_end && ok; ++u) {
+      for (long long u = u_begin; u < u_end && ok; u += u_step) {
         int tile, sample, kb0, kb1;
         decode(u, tile, sample, kb0, kb1);
         const int m0 = (tile / p.n_tiles) * BM;
@@ -182,7 +200,7 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (long long u = u_begin; u < u_end && ok; ++u) {
+      for (long long u = u_begin; u < u_end && ok; u += u_step) {
         int tile, sample, kb0, kb1;
         decode(u, tile, sample, kb0, kb1);
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.err, 512)) { ok = false; break; }
@@ -211,7 +229,7 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    for (long long u = u_begin; u < u_end; ++u) {
+    for (long long u = u_begin; u < u_end; u += u_step) {
       int tile, sample, kb0, kb1;
       decode(u, tile, sample, kb0, kb1);
       const int m0 = (tile / p.n_tiles) * BM;
@@ -348,7 +366,7 @@ static int launch_xty(const CUtensorMap& tx, const CUtensorMap& ty, XtyParams p,
   const long long units = static_cast<long long>(p.m_tiles) * p.n_tiles * p.samples * p.k_splits;
   int grid = static_cast<int>(units < ds->sm_count ? units : ds->sm_count);
   p.units_per_cta = static_cast<int>((units + grid - 1) / grid);
-  grid = static_cast<int>((units + p.units_per_cta - 1) / p.units_per_cta);
+  if (!p.sample_major) grid = static_cast<int>((units + p.units_per_cta - 1) / p.units_per_cta);
   xty_gemm_kernel<<<grid, 192, XtyCfg::kSmemBytes, st>>>(tx, ty, p);
   count_launch();
   return post_launch("xty_gemm_kernel");
@@ -476,6 +494,7 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   p.n_tiles = ceil_div(n_cols, XtyCfg::BN);
   p.T = T;
   p.k_splits = 1;
+  p.sample_major = 1;
   p.kb_per_split = ceil_div(T, XtyCfg::BK);
   p.v_is_f32 = v_is_f32;
   p.err = ds->err_word;
