@@ -254,7 +254,6 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* s_red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);            // [8 warps][32][VR]
-  float* s_sum = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + Cfg::kRedBytes);   // [256]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kRedBytes + kTdCols * 4);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
@@ -340,8 +339,11 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
       const bool do_sum = (v0 == 0) && (p.sum != nullptr || p.out != nullptr);
 #pragma unroll 1
       for (long long s = s_begin; s < s_end; ++s) {
-        const bool ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 132);
-        if (!named_bar_and(1, 256, ok)) { alive = false; break; }
+        // the warps run through the ring independently of one another; lane 0 waits for the warp
+        int ok = 1;
+        if (lane == 0) ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 132) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { alive = false; break; }
         const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
         uint32_t a[2][2][4];
 #pragma unroll
@@ -373,42 +375,58 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[stage]);     // this warp is done with the stage
         if (++stage == kStages) { stage = 0; phase ^= 1; }
-        if (do_sum) {
-          // every row of csum[j] holds the sums of elements 8j..8j+7 of this warp's slice
+        if (do_sum && g < 4) {
+          // every row of csum[j] holds the sums of elements 8j..8j+7 of this warp's slice; lane
+          // (g = j, q) writes elements 8j + 2q, 8j + 2q + 1: the warp covers 32 adjacent elements
+          float t0 = 0.f, t1 = 0.f;
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            if (g == j) *reinterpret_cast<float2*>(&s_sum[warp * 32 + j * 8 + q * 2]) = make_float2(csum[j][0], csum[j][1]);
-          asm volatile("bar.sync 2, 256;" ::: "memory");
-          const float t = s_sum[threadIdx.x];
+            if (g == j) { t0 = csum[j][0]; t1 = csum[j][1]; }
+          const int e0 = warp * 32 + g * 8 + q * 2;          // element inside the stage row
           if (p.out != nullptr) {
             // one stage is one 256-column row segment of one 128 x 256 tile
             const long long tile = s / kStagesPerTile;
             const int r = static_cast<int>(tile / p.n_tiles_n) * 128 + static_cast<int>(s % kStagesPerTile);
-            const int c = static_cast<int>(tile % p.n_tiles_n) * 256 + static_cast<int>(threadIdx.x);
+            const int c = static_cast<int>(tile % p.n_tiles_n) * 256 + e0;
             if (r < p.m_cols && c < p.n_cols) {
               const long long o = static_cast<long long>(r) * p.n_cols + c;
-              float val = t * p.out_scale;
+              const bool rmw = p.out_accumulate || j0 > 0;
+              const bool pair = (c + 1 < p.n_cols) && ((p.n_cols & 1) == 0);     // o is even then
+              t0 *= p.out_scale; t1 *= p.out_scale;
               if (p.out_is_f32) {
                 float* dst = static_cast<float*>(p.out) + o;
-                if (p.out_accumulate || j0 > 0) val += *dst;
-                *dst = val;
+                if (pair) {
+                  float2 v = make_float2(t0, t1);
+                  if (rmw) { const float2 old = *reinterpret_cast<const float2*>(dst); v.x += old.x; v.y += old.y; }
+                  *reinterpret_cast<float2*>(dst) = v;
+                } else {
+                  dst[0] = rmw ? dst[0] + t0 : t0;
+                  if (c + 1 < p.n_cols) dst[1] = rmw ? dst[1] + t1 : t1;
+                }
               } else {
                 __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + o;
-                if (p.out_accumulate || j0 > 0) val += __bfloat162float(*dst);
-                *dst = __float2bfloat16_rn(val);
+                if (pair) {
+                  if (rmw) {
+                    const __nv_bfloat162 old = *reinterpret_cast<const __nv_bfloat162*>(dst);
+                    t0 += __bfloat162float(old.x); t1 += __bfloat162float(old.y);
+                  }
+                  *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(t0, t1);
+                } else {
+                  dst[0] = __float2bfloat16_rn(rmw ? __bfloat162float(dst[0]) + t0 : t0);
+                  if (c + 1 < p.n_cols) dst[1] = __float2bfloat16_rn(rmw ? __bfloat162float(dst[1]) + t1 : t1);
+                }
               }
             }
           } else {
-            float* dst = p.sum + s * kTdCols + threadIdx.x;
-            float val = t;
-            if (!(p.sum_init && j0 == 0)) val += *dst;
-            *dst = val;
+            float2* dst = reinterpret_cast<float2*>(p.sum + s * kTdCols + e0);
+            float2 v = make_float2(t0, t1);
+            if (!(p.sum_init && j0 == 0)) { const float2 old = *dst; v.x += old.x; v.y += old.y; }
+            *dst = v;
           }
-          // s_sum is rewritten only after the next stage's named barrier, which every thread
-          // reaches after this read
         }
       }
-      if (!alive) break;
+      // the only CTA-wide agreement: every compute warp gets here once per block, aborted or not
+      if (!named_bar_and(1, 256, alive)) { alive = false; break; }
       // reduce the per-warp [32 train x VR val] partial blocks, one atomic per (v, b) and CTA
       float* mine = s_red + warp * (kTdTrainRows * VR);
 #pragma unroll
