@@ -39,10 +39,15 @@ from .. import ops
 PATH_RULE = "cost"
 
 # Measured throughputs behind the 'cost' rule (B200): Gram kernel ~1.2e15 flop/s; per-sample GEMM
-# pass ~0.8e15 flop/s; the streaming dot kernel ~6e12 (validation x train x weight-element) products
-# per second on CUDA cores and ~5e12 bytes/s for writing and re-reading the bf16 tiles.
+# pass ~1.1e15 flop/s plus ~3e12 bytes/s for storing the tiles (the term that matters when a sample
+# has few tokens); the streaming kernel reads bf16 tiles at ~4.5e12 bytes/s with its contraction on
+# the tensor cores (32 train rows and up to 32 validation rows per
+# pass); with fp32 tiles its contraction runs on CUDA cores at ~6e12 (validation x train x
+# weight-element) products per second and ~5e12 bytes/s.
 _GRAM_FLOPS = 1.2e15
-_PERSAMPLE_FLOPS = 0.8e15
+_PERSAMPLE_FLOPS = 1.1e15
+_STREAM_BYTES_PER_S = 4.5e12
+_TILE_WRITE_BYTES_PER_S = 3.0e12
 _DOT_PRODUCTS_PER_S = 6.0e12
 _TILE_BYTES_PER_S = 5.0e12
 
@@ -64,7 +69,7 @@ def _should_use_ghost_computation(layer: nn.Module, A: torch.Tensor, B: torch.Te
     With ``PATH_RULE == 'reference'`` (or when the batch split is unknown) this is the reference's
     test ``2*T^2 <= weight.numel()``.  With ``'cost'`` the two kernels' tensor work for the full
     matrix is compared: Gram ``2*n_t*n_v*T^2*(d+p)`` flops against the per-sample path's
-    ``2*(n_t+n_v)*T*d*p`` flops plus its ``n_v*n_t*d*p`` dot-kernel products and tile traffic.
+    ``2*(n_t+n_v)*T*d*p`` flops plus the streaming kernel's passes over the stored tiles.
     """
     if hasattr(layer, "use_ghost_computation"):
         return
@@ -81,8 +86,16 @@ def _should_use_ghost_computation(layer: nn.Module, A: torch.Tensor, B: torch.Te
     n_v = int(val_batch_size)
     n_t = int(A.shape[0]) - n_v
     gram = 2.0 * n_t * n_v * T * T * (d + p) / _GRAM_FLOPS
-    per = (2.0 * (n_t + n_v) * T * d * p / _PERSAMPLE_FLOPS + float(n_v) * n_t * d * p / _DOT_PRODUCTS_PER_S
-           + 4.0 * (n_t + n_v) * d * p / _TILE_BYTES_PER_S)
+    if A.dtype == torch.float32:
+        gram *= 3.0       # hi/lo split operands: three bf16 products per fp32 product, both paths
+        per = (6.0 * (n_t + n_v) * T * d * p / _PERSAMPLE_FLOPS + float(n_v) * n_t * d * p / _DOT_PRODUCTS_PER_S
+               + 8.0 * (n_t + n_v) * d * p / _TILE_BYTES_PER_S)
+    else:
+        vr = 8 if n_v <= 8 else (16 if n_v <= 16 else 32)
+        passes = -(-n_v // vr) * -(-n_t // 32)
+        per = (2.0 * (n_t + n_v) * T * d * p / _PERSAMPLE_FLOPS
+               + 2.0 * d * p * (n_t + n_v) / _TILE_WRITE_BYTES_PER_S
+               + 2.0 * d * p * (32 + vr) * passes / _STREAM_BYTES_PER_S)
     layer.use_ghost_computation = bool(gram <= per)
 
 
