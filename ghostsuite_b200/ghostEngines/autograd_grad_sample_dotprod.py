@@ -19,6 +19,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
+from . import supported_layers_grad_samplers_dotprod as _layers
 from .supported_layers_grad_samplers_dotprod import (
     _supported_layers_dotprod,
     _create_or_accumulate_train_grad,
@@ -58,6 +59,7 @@ def add_hooks(model: nn.Module, val_batch_size: int, loss_reduction: str = "mean
 
 def remove_hooks(model: nn.Module):
     """Remove everything ``add_hooks`` registered."""
+    _layers.finalize_pending_dots()
     if hasattr(model, "autograd_grad_sample_hooks"):
         for handle in model.autograd_grad_sample_hooks:
             handle.remove()
@@ -87,7 +89,17 @@ def _prepare_sample_grad_or_dotprod(layer: nn.Module, grad_output: Tuple[torch.T
 
     # 'mean' losses carry a 1/batch factor; the train-gradient kernels undo it in their epilogue
     layer._ghost_backprop_scale = float(backprops.shape[0]) if loss_reduction == "mean" else 1.0
-    dot_fn(layer, A, backprops, val_batch_size=val_batch_size)
+    # the per-parameter [n_train] vectors are reduced in one batched op when the backward pass ends
+    if _layers.begin_deferred_dots():
+        try:
+            torch.autograd.Variable._execution_engine.queue_callback(_layers.finalize_pending_dots)
+        except Exception:
+            _layers.finalize_pending_dots()      # not inside a backward pass: reduce immediately
+    try:
+        dot_fn(layer, A, backprops, val_batch_size=val_batch_size)
+    except BaseException:
+        _layers.finalize_pending_dots()          # a failed pass may never reach its callback
+        raise
     layer.backprops = backprops
 
 

@@ -17,6 +17,7 @@ from torch import nn
 
 from .. import _lib
 from . import autograd_grad_sample_dotprod
+from . import supported_layers_grad_samplers_dotprod as _layers
 from . import transformers_support
 
 
@@ -103,21 +104,30 @@ class GradDotProdEngine:
         self._aggregate_and_log_dot_products()
 
     def _aggregate_and_log_dot_products(self):
-        total = None
-        total_matrix = None
+        """Sum of the dot products over all parameters (reference :195-262), as one stacked
+        reduction instead of one in-place add per parameter."""
+        _layers.finalize_pending_dots()
+        vectors, matrices = [], []
         for _, param in self.module.named_parameters():
             if hasattr(param, "grad_dot_prod") and param.initially_requires_grad:
                 if param.grad_dot_prod.numel() > 0:
-                    if total is None:
-                        total = param.grad_dot_prod.clone()
-                    else:
-                        total += param.grad_dot_prod
                     m = getattr(param, "grad_dot_prod_matrix", None)
                     if m is not None:
-                        total_matrix = m.clone() if total_matrix is None else total_matrix.add_(m)
+                        matrices.append(m)
+                    else:
+                        vectors.append(param.grad_dot_prod)
                 delattr(param, "grad_dot_prod")
                 if hasattr(param, "grad_dot_prod_matrix"):
                     delattr(param, "grad_dot_prod_matrix")
+        total = None
+        total_matrix = None
+        if matrices:
+            total_matrix = torch.stack(matrices).sum(dim=0)
+            total = total_matrix.sum(dim=0)
+        if vectors:
+            extra = torch.stack(vectors).sum(dim=0)
+            total = extra if total is None else total + extra
+            total_matrix = None          # a parameter without a matrix makes the summed matrix partial
         if total is None:
             warnings.warn("No gradient dot products computed for this iteration.")
             return

@@ -22,6 +22,8 @@ computed once and cached; pre-setting it overrides the choice) selects the Gram 
 """
 from __future__ import annotations
 
+import threading
+
 import torch
 import torch.nn.functional as F
 from torch import nn
@@ -110,9 +112,58 @@ def _create_or_accumulate_train_grad(param: torch.Tensor, grad: torch.Tensor) ->
         param.train_grad = grad
 
 
+# While a backward hook runs, the [n_train] vectors are not reduced one launch per parameter: the
+# (parameter, matrix) pairs are collected here and ``finalize_pending_dots`` reduces them all in one
+# batched op when the backward pass ends.  Direct callers of the layer functions get the vector at
+# once.
+_PENDING_DOTS = None
+_PENDING_LOCK = threading.Lock()      # backward hooks of different devices run on different threads
+
+
+def begin_deferred_dots() -> bool:
+    """Start collecting; returns True when this call opened the list (its caller must arrange for
+    ``finalize_pending_dots`` to run)."""
+    global _PENDING_DOTS
+    with _PENDING_LOCK:
+        if _PENDING_DOTS is not None:
+            return False
+        _PENDING_DOTS = []
+        return True
+
+
+def finalize_pending_dots() -> None:
+    """Set ``param.grad_dot_prod = param.grad_dot_prod_matrix.sum(0)`` for every collected parameter
+    with one stack + one reduction per matrix shape.  A tied parameter keeps its last matrix, as it
+    does when every hook overwrites the attribute.  Safe to call when nothing is pending."""
+    global _PENDING_DOTS
+    with _PENDING_LOCK:
+        pending, _PENDING_DOTS = _PENDING_DOTS, None
+    if not pending:
+        return
+    last = {}
+    for param, M in pending:
+        last[id(param)] = (param, M)
+    groups = {}
+    for param, M in last.values():
+        groups.setdefault((tuple(M.shape), M.dtype, M.device), []).append((param, M))
+    for items in groups.values():
+        stacked = torch.stack([M for _, M in items])          # [P, n_val, n_train]
+        vectors = stacked.sum(dim=1)
+        for i, (param, M) in enumerate(items):
+            if getattr(param, "grad_dot_prod_matrix", None) is M:
+                param.grad_dot_prod = vectors[i]
+
+
 def _set_dot(param: torch.Tensor, M: torch.Tensor) -> None:
     param.grad_dot_prod_matrix = M
-    param.grad_dot_prod = M.sum(dim=0)
+    with _PENDING_LOCK:
+        deferred = _PENDING_DOTS is not None
+        if deferred:
+            _PENDING_DOTS.append((param, M))
+    if deferred:
+        param.grad_dot_prod = M          # placeholder until the backward pass ends
+    else:
+        param.grad_dot_prod = M.sum(dim=0)
 
 
 def _check_batch(A, B, val_batch_size: int) -> int:
