@@ -47,6 +47,8 @@ PROTOTYPES = {
     "ghost_embedding_wgrad_workspace_bytes": (_ll, [_i, _ll, _i]),
     "ghost_embedding_wgrad": (_i, [_vp, _vp, _i, _i, _ll, _i, _i, _f, _f, _i, _vp, _vp, _ll, _vp]),
     "ghost_gradproj_dense_bf16": (_i, [_vp, _vp, _i, _ll, _i, _i, _ll, _ll, _vp, _vp, _i, _i, _ll, _ll, _f, _vp, _ll, _vp]),
+    "ghost_workload_ce_forward": (_i, [_vp, _i, _ll, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp]),
+    "ghost_workload_ce_backward": (_i, [_vp, _i, _ll, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp]),
 }
 
 _lib = None

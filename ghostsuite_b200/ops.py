@@ -518,3 +518,48 @@ def gradproj_dense(G: torch.Tensor, A: torch.Tensor, P_r: torch.Tensor, P_c: tor
 
 def launch_count() -> int:
     return _lib.launch_count()
+
+
+# ------------------------------------------------------------------------------------------------
+# benchmark model helper: fused token cross-entropy (not part of the ghost hot path)
+# ------------------------------------------------------------------------------------------------
+def ce_supported(logits: torch.Tensor) -> bool:
+    """True when the fused loss kernels can take this [rows, cols] logit matrix as it is."""
+    if not logits.is_cuda or logits.dtype not in (_BF16, _F32) or logits.dim() != 2:
+        return False
+    vec = 8 if logits.dtype == _BF16 else 4
+    return logits.stride(1) == 1 and logits.stride(0) % vec == 0 and logits.data_ptr() % 16 == 0
+
+
+def ce_forward(logits: torch.Tensor, targets: torch.Tensor, valid_cols: int, ignore_index: int = -100
+               ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row log-sum-exp over the first ``valid_cols`` columns and per-row loss (0 for ignored
+    rows), both float32 ``[rows]``, in one pass over ``logits``."""
+    lib = _lib.load()
+    _require_cuda(logits, targets)
+    rows, cols = logits.shape
+    targets = targets.contiguous()
+    lse = torch.empty(rows, dtype=_F32, device=logits.device)
+    loss_rows = torch.empty(rows, dtype=_F32, device=logits.device)
+    with _Timed("ce_forward_kernel", "hbm", 0.0, float(rows) * valid_cols * logits.element_size()):
+        _lib.check(lib.ghost_workload_ce_forward(logits.data_ptr(), _dt_flag(logits), rows, cols, int(valid_cols),
+                                                 logits.stride(0), targets.data_ptr(), int(ignore_index),
+                                                 lse.data_ptr(), loss_rows.data_ptr(), _stream_ptr()))
+    return lse, loss_rows
+
+
+def ce_backward(logits: torch.Tensor, targets: torch.Tensor, valid_cols: int, lse: torch.Tensor,
+                scale: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """``scale * (softmax(logits[:, :valid_cols]) - onehot(targets))`` in the logits' dtype, zero in
+    padded columns and ignored rows; ``scale`` is a one-element float32 device tensor."""
+    lib = _lib.load()
+    _require_cuda(logits, targets, lse, scale)
+    rows, cols = logits.shape
+    targets = targets.contiguous()
+    out = torch.empty((rows, cols), dtype=logits.dtype, device=logits.device)
+    with _Timed("ce_backward_kernel", "hbm", 0.0, 2.0 * rows * cols * logits.element_size()):
+        _lib.check(lib.ghost_workload_ce_backward(logits.data_ptr(), _dt_flag(logits), rows, cols, int(valid_cols),
+                                                  logits.stride(0), targets.data_ptr(), int(ignore_index),
+                                                  lse.data_ptr(), scale.data_ptr(), out.data_ptr(), cols,
+                                                  _stream_ptr()))
+    return out

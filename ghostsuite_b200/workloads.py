@@ -33,6 +33,34 @@ except Exception:  # pragma: no cover - transformers is part of the supported en
             return torch.addmm(self.bias, x.view(-1, x.size(-1)), self.weight).view(size_out)
 
 
+class _FusedTokenLoss(torch.autograd.Function):
+    """Mean next-token cross-entropy over the first ``valid_cols`` logit columns from two streaming
+    kernels (``ops.ce_forward`` / ``ops.ce_backward``): the logits are read once in the forward,
+    once more in the backward, and the gradient is written once, in the logits' dtype.  The usual
+    fp32-copy + log-softmax formulation moves the tensor through HBM about ten times."""
+
+    @staticmethod
+    def forward(ctx, logits2d, target, valid_cols):
+        from . import ops
+        lse, loss_rows = ops.ce_forward(logits2d, target, valid_cols)
+        n_valid = (target != -100).sum().to(torch.float32)
+        ctx.save_for_backward(logits2d, target, lse, n_valid)
+        ctx.valid_cols = valid_cols
+        return loss_rows.sum() / n_valid
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import ops
+        logits2d, target, lse, n_valid = ctx.saved_tensors
+        scale = (grad_out.to(torch.float32) / n_valid).reshape(1).contiguous()
+        return ops.ce_backward(logits2d, target, ctx.valid_cols, lse, scale), None, None
+
+
+def _fused_loss_ok(flat: torch.Tensor) -> bool:
+    from . import ops
+    return ops.ce_supported(flat)
+
+
 @dataclass
 class GPT2Config:
     vocab_size: int = 50257
@@ -46,6 +74,8 @@ class GPT2Config:
     #: vocabulary size makes every cuBLAS GEMM on the logits fall back to unaligned legacy kernels.
     #: Token ids stay below vocab_size and the padded logits never enter the loss.
     pad_vocab_to: int = 64
+    #: on a GPU the loss comes from the library's fused cross-entropy kernels; False = torch ops
+    fused_loss: bool = True
 
     @property
     def padded_vocab(self) -> int:
@@ -142,11 +172,14 @@ class GPT2Like(nn.Module):
             V = self.cfg.vocab_size
             target = torch.cat((labels[:, 1:], labels.new_full((B, 1), -100)), dim=1).reshape(-1)
             flat = logits.reshape(-1, logits.size(-1))
-            # an fp32 copy that is safe to edit in place (for an fp32 model .float() is a no-op view)
-            flat = flat.float() if flat.dtype != torch.float32 else flat.clone()
-            if flat.size(-1) != V:
-                flat[:, V:] = float("-inf")        # padded classes take no probability mass
-            loss = F.cross_entropy(flat, target, ignore_index=-100)
+            if self.cfg.fused_loss and flat.is_cuda and _fused_loss_ok(flat):
+                loss = _FusedTokenLoss.apply(flat, target, V)
+            else:
+                # an fp32 copy that is safe to edit in place (for an fp32 model .float() is a no-op view)
+                flat = flat.float() if flat.dtype != torch.float32 else flat.clone()
+                if flat.size(-1) != V:
+                    flat[:, V:] = float("-inf")        # padded classes take no probability mass
+                loss = F.cross_entropy(flat, target, ignore_index=-100)
         return loss, logits
 
 

@@ -174,6 +174,22 @@ int ghost_gradproj_dense_bf16(const void* G, const void* A, int B, long long T, 
                               int k_c, long long ldpr, long long ldpc, float scale, float* out,
                               long long out_stride, void* stream);
 
+/* ---- benchmark model helper (not part of the ghost hot path) ------------------------------------ */
+/* Token cross-entropy of a [rows, cols] logit matrix whose last cols - cols_valid columns are padding
+ * (they take no probability mass and get zero gradient).  Forward: lse[r] = log-sum-exp over the
+ * valid columns, loss_rows[r] = lse[r] - logits[r, targets[r]] (0 where targets[r] == ignore_index);
+ * one pass over the logits.  Backward: dlogits[r, c] = scale[0] * (softmax - onehot), scale a
+ * device scalar (upstream gradient / number of counted rows); one read and one write.  Used by
+ * the loss of the synthetic GPT-2 model the benchmark trains.  No counterpart in the reference,
+ * whose models take their loss from torch ops. */
+int ghost_workload_ce_forward(const void* logits, int is_f32, long long rows, int cols, int cols_valid,
+                              long long ld, const long long* targets, long long ignore_index, float* lse,
+                              float* loss_rows, void* stream);
+int ghost_workload_ce_backward(const void* logits, int is_f32, long long rows, int cols, int cols_valid,
+                               long long ld, const long long* targets, long long ignore_index,
+                               const float* lse, const float* scale, void* dlogits, long long ld_out,
+                               void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -310,3 +310,32 @@ def test_error_codes_are_python_exceptions():
         o.small_gram(A.reshape(4, 24), 4)
     with pytest.raises(RuntimeError):
         o.colsum(A.cpu())
+
+
+# ------------------------------------------------------------------------------------------------
+# benchmark model helper: fused token cross-entropy against torch's own
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(37, 1000, 1000), (64, 50304, 50257), (5, 72, 61)])
+def test_fused_token_loss_matches_torch(shape, dtype):
+    from ghostsuite_b200.workloads import _FusedTokenLoss
+    rows, cols, valid = shape
+    g = torch.Generator().manual_seed(5)
+    logits = (torch.randn(rows, cols, generator=g) * 3).to(dtype).cuda().requires_grad_(True)
+    target = torch.randint(0, valid, (rows,), generator=g)
+    target[::7] = -100
+    target = target.cuda()
+    loss = _FusedTokenLoss.apply(logits, target, valid)
+    (loss * 1.7).backward()
+    ref_logits = logits.detach().float().clone().requires_grad_(True)
+    masked = ref_logits[:, :valid]
+    ref = torch.nn.functional.cross_entropy(masked, target, ignore_index=-100)
+    (ref * 1.7).backward()
+    assert abs(loss.item() - ref.item()) <= 2e-5 * max(1.0, abs(ref.item()))
+    got = logits.grad.float()
+    want = ref_logits.grad
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5       # relative Frobenius; bf16 = one rounding of the result
+    assert (got - want).norm() <= tol * want.norm()
+    assert torch.count_nonzero(got[:, valid:]) == 0
+    assert torch.count_nonzero(got[::7]) == 0
