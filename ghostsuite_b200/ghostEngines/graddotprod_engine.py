@@ -131,16 +131,21 @@ class GradDotProdEngine:
         if total is None:
             warnings.warn("No gradient dot products computed for this iteration.")
             return
+        # device -> host: all copies are queued first and waited for once (this is also the step's
+        # sync point); the train batch is copied once when inputs and labels are one tensor
+        x_cpu = _to_host_async(self.X_train)
+        y_cpu = x_cpu if self.Y_train is self.X_train else _to_host_async(self.Y_train)
         entry = {
-            "dot_product": to_device(total, "cpu"),      # device -> host: also the step's sync point
-            "X_train": to_device(self.X_train, "cpu") if self.X_train is not None else None,
-            "Y_train": to_device(self.Y_train, "cpu") if self.Y_train is not None else None,
+            "dot_product": _to_host_async(total),
+            "X_train": x_cpu,
+            "Y_train": y_cpu,
             "iter_num": self.iter_num,
             "batch_idx": self.batch_idx,
         }
         if total_matrix is not None:
-            entry["dot_product_matrix"] = to_device(total_matrix, "cpu")
+            entry["dot_product_matrix"] = _to_host_async(total_matrix)
         if total.is_cuda:
+            torch.cuda.current_stream(total.device).synchronize()
             _lib.poll_kernel_error()
         self.dot_product_log.append(entry)
 
@@ -162,6 +167,18 @@ class GradDotProdEngine:
         self.Y_train = Y_train
         self.iter_num = iter_num
         self.batch_idx = batch_idx
+
+
+def _to_host_async(data):
+    """Queue a device -> host copy (pinned destination) without waiting; the caller synchronises
+    the stream once after queueing all of them.  Host data is passed through."""
+    if data is None:
+        return None
+    if isinstance(data, dict):
+        return {k: _to_host_async(v) if hasattr(v, "to") else v for k, v in data.items()}
+    if hasattr(data, "is_cuda") and data.is_cuda:
+        return data.to("cpu", non_blocking=True)
+    return data
 
 
 def to_device(data, device):
