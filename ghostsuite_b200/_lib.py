@@ -39,6 +39,7 @@ PROTOTYPES = {
     "ghost_colsum": (_i, [_vp, _i, _i, _ll, _i, _ll, _vp, _vp]),
     "ghost_layernorm_workspace_bytes": (_ll, [_i, _ll, _i]),
     "ghost_layernorm_persample": (_i, [_vp, _vp, _i, _i, _ll, _i, _f, _vp, _vp, _vp, _ll, _vp]),
+    "ghost_rmsnorm_persample": (_i, [_vp, _vp, _i, _i, _ll, _i, _f, _vp, _vp, _vp, _ll, _vp]),
     "ghost_small_gram_f32": (_i, [_vp, _i, _i, _i, _f, _vp, _vp]),
     "ghost_rows_sum": (_i, [_vp, _i, _i, _f, _vp, _i, _i, _vp]),
     "ghost_embedding_dot_workspace_bytes": (_ll, [_i, _ll, _i]),

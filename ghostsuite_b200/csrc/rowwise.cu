@@ -150,7 +150,7 @@ template <typename T, int NCHUNK>
 __global__ void __launch_bounds__(256, NCHUNK <= 3 ? 2 : 1)
 layernorm_persample_kernel(const T* __restrict__ A, const T* __restrict__ G, long long Tn, int F,
                            float eps, float* __restrict__ gw, float* __restrict__ gb,
-                           float* __restrict__ part, int t_splits) {
+                           float* __restrict__ part, int t_splits, int rms) {
   extern __shared__ float sm[];   // [8 warps][2][F]
   const int n = blockIdx.y, split = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,7 +182,7 @@ layernorm_persample_kernel(const T* __restrict__ A, const T* __restrict__ G, lon
     for (int i = 0; i < NCHUNK; ++i)
 #pragma unroll
       for (int j = 0; j < 8; ++j) s += x[i][j];
-    const float mean = warp_sum(s) * invF;
+    const float mean = rms ? 0.f : warp_sum(s) * invF;     // RMS norm: no centring
     float q = 0.f;
 #pragma unroll
     for (int i = 0; i < NCHUNK; ++i) {
@@ -243,7 +243,8 @@ __global__ void layernorm_reduce_kernel(const float* __restrict__ part, int N, i
 template <typename T>
 __global__ void __launch_bounds__(256)
 layernorm_persample_generic_kernel(const T* __restrict__ A, const T* __restrict__ G, long long Tn, int F,
-                                   float eps, float* __restrict__ gw, float* __restrict__ gb, int t_splits) {
+                                   float eps, float* __restrict__ gw, float* __restrict__ gb, int t_splits,
+                                   int rms) {
   extern __shared__ float sm[];   // [2][F] + 32
   float* s_gw = sm;
   float* s_gb = sm + F;
@@ -266,7 +267,7 @@ layernorm_persample_generic_kernel(const T* __restrict__ A, const T* __restrict_
     __syncthreads();
     float tot = 0.f;
     for (int w = 0; w < 8; ++w) tot += s_red[w];
-    const float mean = tot * invF;
+    const float mean = rms ? 0.f : tot * invF;
     float q = 0.f;
     for (int f = threadIdx.x; f < F; f += blockDim.x) { const float dlt = to_f32<T>(a[f]) - mean; q += dlt * dlt; }
     q = warp_sum(q);
@@ -403,7 +404,7 @@ extern "C" long long ghost_layernorm_workspace_bytes(int N, long long T, int F) 
 
 template <typename T>
 static int launch_ln(const T* A, const T* G, int N, long long Tn, int F, float eps, float* gw, float* gb,
-                     float* ws, long long ws_bytes, const DeviceState* ds, cudaStream_t st) {
+                     float* ws, long long ws_bytes, const DeviceState* ds, cudaStream_t st, int rms) {
   const bool fast = (F % 8 == 0) && (F <= 1024) &&
                     ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0);
   if (fast) {
@@ -421,7 +422,7 @@ static int launch_ln(const T* A, const T* G, int N, long long Tn, int F, float e
       if (smem > 48 * 1024)                                                                           \
         GB_CUDA_OK(cudaFuncSetAttribute(layernorm_persample_kernel<T, NC>,                            \
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));     \
-      layernorm_persample_kernel<T, NC><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, ws, splits); \
+      layernorm_persample_kernel<T, NC><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, ws, splits, rms); \
     } while (0)
     switch (nchunk) {
       case 1: GB_LN_LAUNCH(1); break;
@@ -450,23 +451,34 @@ static int launch_ln(const T* A, const T* G, int N, long long Tn, int F, float e
   if (smem > 48 * 1024)
     GB_CUDA_OK(cudaFuncSetAttribute(layernorm_persample_generic_kernel<T>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  layernorm_persample_generic_kernel<T><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, splits);
+  layernorm_persample_generic_kernel<T><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, splits, rms);
   count_launch();
   return post_launch("layernorm_persample_generic_kernel");
+}
+
+static int norm_persample(const char* who, const void* A, const void* G, int is_f32, int N, long long T, int F,
+                          float eps, float* gw, float* gb, void* ws, long long ws_bytes, void* stream, int rms) {
+  const DeviceState* ds = device_state();
+  if (!ds) return GHOST_ERR_DEVICE;
+  GB_REQUIRE(A && G && gw && gb, "%s: null pointer", who);
+  GB_REQUIRE(N > 0 && T > 0 && F > 0 && N <= 65535, "%s: bad dimensions", who);
+  GB_REQUIRE(F <= 24 * 1024, "%s: normalized size above 24576 is not supported", who);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* w = static_cast<float*>(ws);
+  if (is_f32) return launch_ln<float>(static_cast<const float*>(A), static_cast<const float*>(G), N, T, F, eps, gw, gb, w, ws_bytes, ds, st, rms);
+  return launch_ln<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(G), N, T, F, eps, gw, gb, w, ws_bytes, ds, st, rms);
 }
 
 extern "C" int ghost_layernorm_persample(const void* A, const void* G, int is_f32, int N, long long T,
                                          int F, float eps, float* gw, float* gb, void* ws,
                                          long long ws_bytes, void* stream) {
-  const DeviceState* ds = device_state();
-  if (!ds) return GHOST_ERR_DEVICE;
-  GB_REQUIRE(A && G && gw && gb, "ghost_layernorm_persample: null pointer");
-  GB_REQUIRE(N > 0 && T > 0 && F > 0 && N <= 65535, "ghost_layernorm_persample: bad dimensions");
-  GB_REQUIRE(F <= 24 * 1024, "ghost_layernorm_persample: normalized size above 24576 is not supported");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  float* w = static_cast<float*>(ws);
-  if (is_f32) return launch_ln<float>(static_cast<const float*>(A), static_cast<const float*>(G), N, T, F, eps, gw, gb, w, ws_bytes, ds, st);
-  return launch_ln<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(G), N, T, F, eps, gw, gb, w, ws_bytes, ds, st);
+  return norm_persample("ghost_layernorm_persample", A, G, is_f32, N, T, F, eps, gw, gb, ws, ws_bytes, stream, 0);
+}
+
+extern "C" int ghost_rmsnorm_persample(const void* A, const void* G, int is_f32, int N, long long T,
+                                       int F, float eps, float* gw, float* gsum, void* ws,
+                                       long long ws_bytes, void* stream) {
+  return norm_persample("ghost_rmsnorm_persample", A, G, is_f32, N, T, F, eps, gw, gsum, ws, ws_bytes, stream, 1);
 }
 
 extern "C" int ghost_small_gram_f32(const float* X, int n_train, int n_val, int F, float scale,

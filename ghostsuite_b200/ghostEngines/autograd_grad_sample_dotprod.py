@@ -41,6 +41,9 @@ def add_hooks(model: nn.Module, val_batch_size: int, loss_reduction: str = "mean
 
     handles = []
     for name, layer in model.named_modules():
+        if type(layer) not in _supported_layers_dotprod and getattr(layer, "weight", None) is not None \
+                and layer.weight.dim() == 1:
+            _layers.maybe_register_rmsnorm(type(layer))
         if type(layer) in _supported_layers_dotprod and requires_grad(layer):
             layer.name = name
             handles.append(layer.register_forward_hook(_capture_activations))
@@ -111,7 +114,7 @@ def _apply_train_grad(layer: nn.Module, val_batch_size: int, loss_reduction: str
             f"Layer {layer.__class__.__name__} is not supported for training gradient computation. "
             "Ensure it is included in the _supported_layers_dotprod dictionary.")
     try:
-        if isinstance(layer, nn.LayerNorm):
+        if type(layer) in _layers._SELF_APPLYING or isinstance(layer, nn.LayerNorm):
             train_grad_fn(layer, layer.activations, layer.backprops, val_batch_size)
         else:
             weight = getattr(layer, "weight", None)

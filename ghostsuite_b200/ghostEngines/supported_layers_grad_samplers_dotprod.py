@@ -338,6 +338,62 @@ def _compute_layernorm_train_grad(layer: nn.LayerNorm, A: torch.Tensor, B: torch
 
 
 # --------------------------------------------------------------------------------------------
+# RMS norm (nn.RMSNorm, Llama-style *RMSNorm modules).  Not in the reference, whose hook
+# registration skips such layers with a warning (autograd_grad_sample_dotprod.py:76-79).
+# --------------------------------------------------------------------------------------------
+def _rmsnorm_eps(layer: nn.Module, A: torch.Tensor) -> float:
+    eps = getattr(layer, "variance_epsilon", None)
+    if eps is None:
+        eps = getattr(layer, "eps", None)
+    if eps is None:
+        eps = torch.finfo(A.dtype).eps          # nn.RMSNorm's default
+    return float(eps)
+
+
+def _rmsnorm_vectors(layer: nn.Module, A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    key = (A.data_ptr(), B.data_ptr(), A.size(0))
+    cached = layer.__dict__.get("_ghost_ln_cache")
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    gw, _ = ops.layernorm_persample(A.detach(), B.detach(), _rmsnorm_eps(layer, A), rms=True)
+    layer._ghost_ln_cache = (key, gw)
+    return gw
+
+
+def _compute_rmsnorm_dot_product(layer: nn.Module, A: torch.Tensor, B: torch.Tensor,
+                                 val_batch_size: int):
+    """RMS norm: weight dot products from one pass over A and B."""
+    if A.size(0) - val_batch_size <= 0:
+        return
+    _set_dot(layer.weight, ops.small_gram(_rmsnorm_vectors(layer, A, B), val_batch_size))
+
+
+def _compute_rmsnorm_train_grad(layer: nn.Module, A: torch.Tensor, B: torch.Tensor,
+                                val_batch_size: int) -> None:
+    """RMS norm: applies the averaged train gradient of the weight itself and returns None."""
+    n_train = A.size(0) - val_batch_size
+    if n_train <= 0:
+        raise ValueError("No training samples to compute gradients, check batch sizes.")
+    gw = _rmsnorm_vectors(layer, A, B)
+    layer.__dict__.pop("_ghost_ln_cache", None)
+    scale = _backprop_scale(layer) / n_train
+    _create_or_accumulate_train_grad(layer.weight, ops.rows_sum(gw, n_train, scale, layer.weight.dtype))
+    return None
+
+
+def maybe_register_rmsnorm(cls) -> bool:
+    """Register a module class as an RMS norm when it looks like one: the name ends in 'RMSNorm'
+    and instances carry a 1-D ``weight`` (nn.RMSNorm, transformers' LlamaRMSNorm and its copies)."""
+    if cls in _supported_layers_dotprod:
+        return cls in _SELF_APPLYING and cls is not nn.LayerNorm
+    if not cls.__name__.endswith("RMSNorm"):
+        return False
+    _supported_layers_dotprod[cls] = (_compute_rmsnorm_dot_product, _compute_rmsnorm_train_grad)
+    _SELF_APPLYING.add(cls)
+    return True
+
+
+# --------------------------------------------------------------------------------------------
 # Conv2d: every output position is a token of the unfolded (im2col) input
 # --------------------------------------------------------------------------------------------
 def _conv2d_tokens(layer: nn.Conv2d, A: torch.Tensor, B: torch.Tensor):
@@ -399,3 +455,7 @@ _supported_layers_dotprod = {
 }
 if _HFConv1D is not None:
     _supported_layers_dotprod[_HFConv1D] = (_compute_Conv1D_dot_product, _compute_Conv1D_train_grad)
+# layer types whose train-gradient function writes ``param.train_grad`` itself and returns None
+_SELF_APPLYING = {nn.LayerNorm}
+if hasattr(nn, "RMSNorm"):
+    maybe_register_rmsnorm(nn.RMSNorm)

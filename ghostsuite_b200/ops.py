@@ -361,9 +361,11 @@ def rows_sum(X: torch.Tensor, n_rows: int, scale: float, out_dtype: torch.dtype,
     return out
 
 
-def layernorm_persample(A: torch.Tensor, G: torch.Tensor, eps: float
+def layernorm_persample(A: torch.Tensor, G: torch.Tensor, eps: float, rms: bool = False
                         ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Per-sample LayerNorm gamma/beta gradients ``([N, F], [N, F])`` float32 in one pass."""
+    """Per-sample LayerNorm gamma/beta gradients ``([N, F], [N, F])`` float32 in one pass.  With
+    ``rms=True`` the normalisation is RMS norm's (no centring); the second result is then just the
+    token sum of the out-grad."""
     lib = _lib.load()
     _require_cuda(A, G)
     if A.dtype != G.dtype:
@@ -380,9 +382,9 @@ def layernorm_persample(A: torch.Tensor, G: torch.Tensor, eps: float
     off = arena.plan(ws_bytes)
     base = arena.commit()
     with _Timed("layernorm_persample_kernel", "hbm", 0.0, 2.0 * N * T * F * A.element_size() + 8.0 * N * F):
-        _lib.check(lib.ghost_layernorm_persample(A.data_ptr(), G.data_ptr(), _dt_flag(A), N, T, F,
-                                                 float(eps), gw.data_ptr(), gb.data_ptr(), base + off,
-                                                 ws_bytes, _stream_ptr()))
+        fn = lib.ghost_rmsnorm_persample if rms else lib.ghost_layernorm_persample
+        _lib.check(fn(A.data_ptr(), G.data_ptr(), _dt_flag(A), N, T, F, float(eps), gw.data_ptr(),
+                      gb.data_ptr(), base + off, ws_bytes, _stream_ptr()))
     return gw, gb
 
 

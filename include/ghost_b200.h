@@ -125,6 +125,14 @@ long long ghost_layernorm_workspace_bytes(int N, long long T, int F);
 int ghost_layernorm_persample(const void* A, const void* G, int is_f32, int N, long long T, int F,
                               float eps, float* gw, float* gb, void* ws, long long ws_bytes,
                               void* stream);
+/* The same pass for an RMS norm (y = weight * x / sqrt(mean(x^2) + eps), no centring, no bias):
+ * gw[n,f] = sum_t G[n,t,f] * x[n,t,f] / rms[n,t]; gsum[n,f] = sum_t G[n,t,f] is produced as well
+ * (callers that do not need it pass scratch).  Workspace as for ghost_layernorm_persample.  The
+ * reference has no RMS-norm support (ghostEngines/autograd_grad_sample_dotprod.py:76-79 skips such
+ * layers with a warning), so Llama-style models get no dot products for their norm weights there. */
+int ghost_rmsnorm_persample(const void* A, const void* G, int is_f32, int N, long long T, int F,
+                            float eps, float* gw, float* gsum, void* ws, long long ws_bytes,
+                            void* stream);
 /* M[v,b] = scale * <X[n_train + v, :], X[b, :]> for per-sample vectors X[N, F] fp32.  Replaces the
  * einsum('p,bp->b') / einsum('bf,f->b') contractions of the bias and LayerNorm paths. */
 int ghost_small_gram_f32(const float* X, int n_train, int n_val, int F, float scale, float* M_out,

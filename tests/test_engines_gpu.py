@@ -505,3 +505,71 @@ def test_manager_facade(tmp_path):
     with contextlib.redirect_stdout(io.StringIO()):
         mgr.cleanup()
     assert os.path.exists(tmp_path / "grad_dotprods" / "dot_prod_log_iter_-1.pt")
+
+
+@pytest.mark.parametrize("cls_name", ["torch", "llama_style"])
+def test_rmsnorm_network(cls_name):
+    """RMS norm layers (not supported by the reference): dot products against the float64 oracle on
+    the captured tensors, per-sample ground truth from batch-size-1 backward passes, train gradients
+    against autograd."""
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    torch.manual_seed(9)
+
+    class TinyRMSNorm(nn.Module):          # the shape of transformers' LlamaRMSNorm
+        def __init__(self, d, eps=1e-6):
+            super().__init__()
+            self.weight = nn.Parameter(torch.ones(d))
+            self.variance_epsilon = eps
+
+        def forward(self, x):
+            v = x.float().pow(2).mean(-1, keepdim=True)
+            return self.weight * (x.float() * torch.rsqrt(v + self.variance_epsilon)).to(x.dtype)
+
+    def norm(d):
+        return nn.RMSNorm(d, eps=1e-5) if cls_name == "torch" else TinyRMSNorm(d)
+
+    def build():
+        return nn.Sequential(nn.Linear(24, 40), norm(40), nn.ReLU(), nn.Linear(40, 40), norm(40), nn.Linear(40, 7))
+
+    model = build().cuda()
+    with torch.no_grad():
+        for m in model.modules():
+            if type(m).__name__.endswith("RMSNorm"):
+                m.weight.uniform_(0.5, 1.5)
+    ref_model = build()
+    ref_model.load_state_dict({k: v.cpu() for k, v in model.state_dict().items()})
+    n_t, n_v, T = 5, 3, 9
+    X = torch.randn(n_t + n_v, T, 24)
+    Y = torch.randint(0, 7, (n_t + n_v, T))
+    loss_fn = lambda out, y: nn.functional.cross_entropy(out.reshape(-1, 7), y.reshape(-1))
+    eng = GradDotProdEngine(model, val_batch_size=n_v)
+    eng.attach(torch.optim.SGD(model.parameters(), lr=0.1))
+    norms = [(n, m) for n, m in model.named_modules() if type(m).__name__.endswith("RMSNorm")]
+    assert len(norms) == 2
+    cap = {}
+    for name, m in norms:
+        m.register_forward_hook(lambda l, i, o, n=name: cap.setdefault(n, {}).__setitem__("A", i[0].detach().cpu()))
+        m.register_full_backward_hook(lambda l, gi, go, n=name: cap[n].__setitem__("B", go[0].detach().cpu()))
+    loss_fn(model(X.cuda()), Y.cuda()).backward()
+    for name, m in norms:
+        eps = getattr(m, "variance_epsilon", None) or m.eps
+        want = O.rmsnorm_dot_exact(cap[name]["A"], cap[name]["B"], n_v, eps)
+        assert O.rel_fro(m.weight.grad_dot_prod_matrix, want) < 1e-4, name
+        assert m.weight.grad_dot_prod.shape == (n_t,)
+    # ground truth: one backward pass per sample on the CPU copy, with the full-batch loss scale
+    N = n_t + n_v
+    per = {name: [] for name, _ in norms}
+    for i in range(N):
+        ref_model.zero_grad()
+        (loss_fn(ref_model(X[i:i + 1]), Y[i:i + 1]) / N).backward()
+        for (name, _), (_, r) in zip(norms, [(n, m) for n, m in ref_model.named_modules() if type(m).__name__.endswith("RMSNorm")]):
+            per[name].append(r.weight.grad.double().clone())
+    for name, m in norms:
+        g = torch.stack(per[name])
+        truth = g[n_t:] @ g[:n_t].t()
+        assert O.rel_fro(m.weight.grad_dot_prod_matrix, truth) < 1e-4, name
+    ref_model.zero_grad()
+    loss_fn(ref_model(X[:n_t]), Y[:n_t]).backward()
+    for (name, p), (_, r) in zip(model.named_parameters(), ref_model.named_parameters()):
+        assert O.rel_fro(p.train_grad, r.grad) < 1e-4, name
+    eng.detach()

@@ -339,3 +339,18 @@ def test_fused_token_loss_matches_torch(shape, dtype):
     assert (got - want).norm() <= tol * want.norm()
     assert torch.count_nonzero(got[:, valid:]) == 0
     assert torch.count_nonzero(got[::7]) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(6, 5, 64), (9, 33, 768), (3, 17, 4096), (4, 7, 30)])
+def test_rmsnorm_persample(shape, dtype):
+    N, T, F = shape
+    g = torch.Generator().manual_seed(21)
+    A = (torch.randn(N, T, F, generator=g) * 2 + 0.3).to(dtype)
+    G = torch.randn(N, T, F, generator=g).to(dtype)
+    gw, gsum = ops().layernorm_persample(A.cuda(), G.cuda(), 1e-6, rms=True)
+    want = O.rmsnorm_persample_exact(A, G, 1e-6)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert O.rel_fro(gw, want) < tol
+    assert O.rel_fro(gsum, G.double().sum(1)) < tol

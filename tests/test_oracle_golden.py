@@ -155,3 +155,27 @@ def test_conv2d(golden):
     assert O.rel_fro(torch.from_numpy(golden["conv_nv1_ghost0_b"]), Mb[0]) < 2e-2
     tg = O.conv2d_train_grad(A, G * N, N_V, (5, 3, 3, 2), **kw)
     close(tg, golden["conv_train_grad"], rtol=1e-5, atol=1e-6)
+
+
+def test_rmsnorm_oracle_matches_autograd():
+    """RMS norm has no reference counterpart: the float64 restatement is pinned against per-sample
+    autograd gradients of torch's own nn.RMSNorm."""
+    import torch
+    from oracle import ghost_oracle as O
+    torch.manual_seed(3)
+    N, T, F, eps = 4, 6, 10, 1e-5
+    norm = torch.nn.RMSNorm(F, eps=eps).double()
+    with torch.no_grad():
+        norm.weight.uniform_(0.5, 1.5)
+    A = torch.randn(N, T, F, dtype=torch.float64)
+    G = torch.randn(N, T, F, dtype=torch.float64)
+    per = []
+    for n in range(N):
+        norm.zero_grad()
+        (norm(A[n:n + 1]) * G[n:n + 1]).sum().backward()
+        per.append(norm.weight.grad.clone())
+    per = torch.stack(per)
+    got = O.rmsnorm_persample_exact(A, G, eps)
+    assert torch.allclose(got, per, rtol=1e-10, atol=1e-12)
+    M = O.rmsnorm_dot_exact(A, G, 1, eps)
+    assert torch.allclose(M, per[3:] @ per[:3].t(), rtol=1e-10, atol=1e-12)
