@@ -547,8 +547,9 @@ def run_gradproj_model(args):
 def run_gradproj_llama(args):
     """GradProjLoRA on a Llama-3-8B-shaped decoder (32 layers, d=4096, 32 heads / 8 KV heads, SwiGLU 14336,
     vocab 128256, random init, bf16), sequence 4096, k_i = k_o = 64 on all 224 attention / MLP Linears.
-    Batch 2 per GPU instead of the configuration's 8: without recomputation the saved activations of the
-    32-layer model are about 7.8 MB per token, so batch 8 x 4096 would need ~250 GB.  Weights have
+    Without recomputation the saved activations of the 32-layer model are about 7.8 MB per token, so
+    the configuration's batch of 8 x 4096 tokens would need ~250 GB: run it with --checkpoint --batch 8
+    (decoder layers recomputed in the backward pass), or at --batch 2 without.  Weights have
     requires_grad=False (only a one-element dummy bias on the embedding keeps the graph alive), so
     autograd computes activation gradients only."""
     import contextlib
@@ -569,6 +570,10 @@ def run_gradproj_llama(args):
     for prm in model.parameters():
         prm.requires_grad = False
     _add_dummy_bias(model.get_input_embeddings())
+    if args.checkpoint:
+        # recompute each decoder layer in the backward pass: only the layer-boundary activations stay
+        # resident, which is what lets the configuration's batch of 8 x 4096 tokens fit
+        model.gradient_checkpointing_enable(gradient_checkpointing_kwargs={"use_reentrant": True})
     out_dir = tempfile.mkdtemp(prefix="gradproj_llama_")
     with contextlib.redirect_stdout(io.StringIO()):
         eng = GradProjLoraEngine(model, proj_layers="self_attn,mlp", proj_rank_total=4096, proj_rank_min=4,
@@ -610,7 +615,8 @@ def run_gradproj_llama(args):
     shutil.rmtree(out_dir, ignore_errors=True)
     emit({"mode": "gradproj_llama", "workload": " ".join(run_gradproj_llama.__doc__.split()),
                       "layers_projected": n_layers, "total_proj_dim": total_proj_dim,
-                      "batch": B, "seq_len": T, "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
+                      "batch": B, "seq_len": T, "activation_checkpointing": bool(args.checkpoint),
+                      "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
                       "gradproj_kernel_ms_per_step": rec["ms"] / args.steps,
                       "gradproj_kernel_gbs": gbs, "gradproj_kernel_frac_of_measured_hbm": gbs / peaks["hbm"],
                       "d2h_bytes_per_step": B * total_proj_dim * 4,
@@ -627,6 +633,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=2, help="gradproj_llama mode: sequences per step")
     ap.add_argument("--layers", type=int, default=32, help="gradproj_llama mode: decoder layers")
+    ap.add_argument("--checkpoint", action="store_true",
+                    help="gradproj_llama mode: recompute decoder layers in the backward pass (needed for --batch 8)")
     ap.add_argument("--mode", default="step",
                     choices=["step", "kernels", "crossover", "gradproj_model", "gradproj_llama"],
                     help="step: the driver's benchmark line; kernels: per-kernel microbenchmarks; crossover: "

@@ -56,6 +56,11 @@ class GradProjHooks:
     # -- hooks -----------------------------------------------------------------------------------
     def forward_hook_store_inputs(self, module: nn.Module, inputs: Tuple[torch.Tensor, ...],
                                   output: torch.Tensor) -> None:
+        # Under activation checkpointing (re-entrant form) the first forward runs without autograd
+        # and the layer is run again inside the backward pass: only that second run is followed by
+        # the backward hook, so only it keeps the input alive.
+        if not torch.is_grad_enabled():
+            return
         module._ghost_A_raw = inputs[0].detach()
 
     def backward_hook_compute_proj(self, module: nn.Module, grad_input, grad_output) -> None:
