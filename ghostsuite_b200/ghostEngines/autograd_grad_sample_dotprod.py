@@ -70,7 +70,11 @@ def remove_hooks(model: nn.Module):
 
 
 def _capture_activations(layer: nn.Module, inputs: Tuple, outputs: Tuple):
-    """Forward hook: keep the layer input for the backward hook."""
+    """Forward hook: keep the layer input for the backward hook.  A forward without autograd
+    (evaluation, or the first pass of re-entrant activation checkpointing) is followed by no
+    backward hook and keeps nothing alive."""
+    if not torch.is_grad_enabled():
+        return
     layer.activations = inputs[0].detach()
 
 

@@ -573,3 +573,44 @@ def test_rmsnorm_network(cls_name):
     for (name, p), (_, r) in zip(model.named_parameters(), ref_model.named_parameters()):
         assert O.rel_fro(p.train_grad, r.grad) < 1e-4, name
     eng.detach()
+
+
+def test_gradproj_under_activation_checkpointing(tmp_path):
+    """Blocks recomputed in the backward pass (re-entrant checkpointing): the projections equal those
+    of the plain run, and the no-grad first forward leaves no cached input behind."""
+    from torch.utils.checkpoint import checkpoint
+    from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoraEngine
+
+    class Net(nn.Module):
+        def __init__(self, use_ckpt):
+            super().__init__()
+            torch.manual_seed(4)
+            self.inp = nn.Linear(12, 16)
+            self.blocks = nn.ModuleList(nn.Sequential(nn.Linear(16, 32), nn.GELU(), nn.Linear(32, 16)) for _ in range(3))
+            self.out = nn.Linear(16, 6)
+            self.use_ckpt = use_ckpt
+
+        def forward(self, x):
+            x = self.inp(x)
+            for blk in self.blocks:
+                x = x + (checkpoint(blk, x, use_reentrant=True) if self.use_ckpt else blk(x))
+            return self.out(x)
+
+    X = torch.randn(5, 7, 12, device="cuda")
+    Y = torch.randint(0, 6, (5, 7), device="cuda")
+    outs = []
+    for use_ckpt in (False, True):
+        model = Net(use_ckpt).cuda()
+        with contextlib.redirect_stdout(io.StringIO()):
+            eng = GradProjLoraEngine(model, "blocks", 16, 2, 42, "float32", str(tmp_path / f"c{int(use_ckpt)}"),
+                                     proj_save_interval=10 ** 9)
+            eng.attach()
+        eng.iteration = 1
+        out = model(X)
+        if use_ckpt:      # nothing cached by the no-grad forward inside the checkpointed blocks
+            assert not any(hasattr(m, "_ghost_A_raw") for m in model.blocks.modules())
+        nn.functional.cross_entropy(out.reshape(-1, 6), Y.reshape(-1)).backward()
+        outs.append(eng.collect_batch().cpu())
+        eng.detach()
+    assert outs[0].shape == outs[1].shape and outs[0].abs().sum() > 0
+    assert torch.allclose(outs[0], outs[1], rtol=1e-5, atol=1e-6)
