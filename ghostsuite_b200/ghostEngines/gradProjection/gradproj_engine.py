@@ -68,8 +68,11 @@ class _HostStreamer:
             slot_idx, event, rows, save_dict, path = job
             try:
                 event.synchronize()
-                save_dict["proj"] = self._slots[slot_idx][:rows].clone()
-                torch.save(save_dict, path)
+                if callable(path):                      # raw format: the engine appends the rows itself
+                    path(self._slots[slot_idx][:rows], save_dict)
+                else:
+                    save_dict["proj"] = self._slots[slot_idx][:rows].clone()
+                    torch.save(save_dict, path)
             except BaseException as exc:   # surfaced on the next submit()/flush()
                 self._error = exc
             finally:
@@ -139,6 +142,16 @@ class GradProjLoraEngine:
         self.include_conv2d = include_conv2d
         self.proj_dims_override = kwargs.get("proj_dims_override")
         self.async_save = bool(kwargs.get("async_save", True))
+        # 'pt': one torch.save file per saved iteration, as the reference writes them.
+        # 'bin': rows appended to one flat file (proj.bin, row-major [rows, total_proj_dim] in
+        # proj_dtype) plus index.json, which a reader memory-maps (load_projection_bin): no pickling
+        # on the writer thread, so one host thread keeps up with several GPUs.
+        self.proj_format = str(kwargs.get("proj_format", "pt"))
+        if self.proj_format not in ("pt", "bin"):
+            raise ValueError(f"proj_format must be 'pt' or 'bin', got {self.proj_format}")
+        self._bin_file = None
+        self._bin_rows = 0
+        self._bin_index: List[dict] = []
 
         self.matched_layers = OrderedDict()
         self.projection_matrices = {}
@@ -298,6 +311,12 @@ class GradProjLoraEngine:
         save_dict = {"iter": self.iteration, "batch_size": projection.shape[0]}
         if batch_indices is not None:
             save_dict["batch_idx"] = batch_indices
+        if self.proj_format == "bin":
+            if projection.is_cuda and self.async_save:
+                self._streamer.submit(projection, save_dict, self._append_bin)
+            else:
+                self._append_bin(projection.cpu(), save_dict)
+            return
         path = self.proj_dir / f"proj_iter_{self.iteration:06d}.pt"
         if projection.is_cuda and self.async_save:
             self._streamer.submit(projection, save_dict, path)
@@ -305,9 +324,33 @@ class GradProjLoraEngine:
             save_dict = {"proj": projection.cpu(), **save_dict}
             torch.save(save_dict, path)
 
+    def _append_bin(self, rows_host: torch.Tensor, info: dict) -> None:
+        """Append one batch of rows to proj.bin (called in submission order, by the writer thread
+        when saving is asynchronous)."""
+        if self._bin_file is None:
+            self._bin_file = open(self.proj_dir / "proj.bin", "wb")
+        data = rows_host.contiguous()
+        if data.dtype == torch.bfloat16:
+            data = data.view(torch.int16)
+        self._bin_file.write(data.numpy().tobytes())
+        entry = {"iter": info["iter"], "row0": self._bin_rows, "rows": int(rows_host.shape[0])}
+        if "batch_idx" in info:
+            entry["batch_idx"] = [int(i) for i in info["batch_idx"]]
+        self._bin_index.append(entry)
+        self._bin_rows += int(rows_host.shape[0])
+
+    def _write_bin_index(self) -> None:
+        if self.proj_format != "bin" or self._bin_file is None:
+            return
+        self._bin_file.flush()
+        with open(self.proj_dir / "index.json", "w") as f:
+            json.dump({"dtype": str(self.proj_dtype).split(".")[-1], "total_proj_dim": self.total_proj_dim,
+                       "rows": self._bin_rows, "batches": self._bin_index}, f)
+
     def flush(self):
         """Wait until every queued projection has been written to disk."""
         self._streamer.flush()
+        self._write_bin_index()
 
     def get_projection_metadata(self) -> dict:
         return self.metadata.copy()
@@ -349,6 +392,10 @@ class GradProjLoraEngine:
     def cleanup(self):
         self.detach()
         self._streamer.flush()
+        self._write_bin_index()
+        if self._bin_file is not None:
+            self._bin_file.close()
+            self._bin_file = None
         self._streamer.close()
         self.projection_matrices.clear()
 
@@ -362,6 +409,19 @@ class GradProjLoraEngine:
 
 #: spelling used in some descriptions of the engine
 GradProjLoRAEngine = GradProjLoraEngine
+
+
+def load_projection_bin(proj_dir: str):
+    """Reader for ``proj_format='bin'``: ``(rows, index)`` with ``rows`` a read-only numpy memory map
+    of shape ``[n_rows, total_proj_dim]`` (bfloat16 data is exposed as int16 bit patterns) and
+    ``index`` the parsed index.json (per saved batch: iter, row0, rows, batch_idx)."""
+    import numpy as np
+    with open(Path(proj_dir) / "index.json") as f:
+        index = json.load(f)
+    np_dtype = {"float32": np.float32, "float16": np.float16, "bfloat16": np.int16}[index["dtype"]]
+    rows = np.memmap(Path(proj_dir) / "proj.bin", dtype=np_dtype, mode="r",
+                     shape=(index["rows"], index["total_proj_dim"]))
+    return rows, index
 
 
 def create_gradproj_engine(model: nn.Module, config: dict) -> GradProjLoraEngine:

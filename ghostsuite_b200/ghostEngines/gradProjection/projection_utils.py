@@ -110,3 +110,22 @@ def compute_projection_metadata(layer_name: str, layer: nn.Module, k_i: int, k_o
         meta["n_i"] = layer.num_embeddings
         meta["n_o"] = layer.embedding_dim
     return meta
+
+
+def projection_similarity(proj_a: torch.Tensor, proj_b: torch.Tensor) -> torch.Tensor:
+    """Gradient-similarity scores ``proj_a @ proj_b.T`` between two sets of projected per-sample
+    gradients (``[Na, D]``, ``[Nb, D]`` -> ``[Na, Nb]`` float32): the downstream step of the
+    reference's examples (Examples/ghost_gradproj_lm.py:190-196), done while the projections are
+    still on the device.  A plain dense GEMM, so it is the library's (cuBLAS through torch), in
+    full fp32 so that scores do not depend on the TF32 setting."""
+    if proj_a.shape[-1] != proj_b.shape[-1]:
+        raise ValueError("projection sets have different dimensions")
+    a, b = proj_a.float(), proj_b.float()
+    if a.is_cuda:
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            return a @ b.t()
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+    return a @ b.t()

@@ -614,3 +614,29 @@ def test_gradproj_under_activation_checkpointing(tmp_path):
         eng.detach()
     assert outs[0].shape == outs[1].shape and outs[0].abs().sum() > 0
     assert torch.allclose(outs[0], outs[1], rtol=1e-5, atol=1e-6)
+
+
+def test_gradproj_bin_format(tmp_path):
+    """proj_format='bin': rows appended to one flat file in submission order; the memory-mapped
+    reader returns exactly what collect_batch returned."""
+    from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoraEngine, load_projection_bin
+    torch.manual_seed(6)
+    model = nn.Sequential(nn.Linear(10, 24), nn.ReLU(), nn.Linear(24, 5)).cuda()
+    with contextlib.redirect_stdout(io.StringIO()):
+        eng = GradProjLoraEngine(model, "0,2", 16, 2, 42, "float32", str(tmp_path / "b"), proj_format="bin")
+        eng.attach()
+    got = []
+    for it, bs in enumerate((4, 3, 4)):
+        X = torch.randn(bs, 10, device="cuda")
+        Y = torch.randint(0, 5, (bs,), device="cuda")
+        model.zero_grad()
+        nn.functional.cross_entropy(model(X), Y).backward()
+        got.append(eng.collect_batch(batch_indices=list(range(10 * it, 10 * it + bs))).cpu())
+    eng.flush()
+    rows, index = load_projection_bin(str(tmp_path / "b"))
+    assert rows.shape == (11, eng.total_proj_dim) and index["rows"] == 11
+    assert [b["rows"] for b in index["batches"]] == [4, 3, 4]
+    assert index["batches"][1]["batch_idx"] == [10, 11, 12] and index["batches"][1]["row0"] == 4
+    assert np.array_equal(np.asarray(rows), torch.cat(got).numpy())
+    eng.cleanup()
+    assert (tmp_path / "b" / "metadata.json").exists()
