@@ -116,7 +116,20 @@ __global__ void colsum_kernel(const T* __restrict__ G, long long Tn, int cols, l
                       ((reinterpret_cast<uintptr_t>(G + static_cast<long long>(n) * Tn * ld + c0) & 15u) == 0);
   if (c0 < cols) {
     const T* base = G + static_cast<long long>(n) * Tn * ld + c0;
-    for (long long t = t0 + ry; t < t1; t += 8) {
+    long long t = t0 + ry;
+    if (vec_ok) {
+      // four independent 16-byte loads in flight per thread
+      for (; t + 24 < t1; t += 32) {
+        float x0[8], x1[8], x2[8], x3[8];
+        Vec8<T>::load(base + t * ld, x0);
+        Vec8<T>::load(base + (t + 8) * ld, x1);
+        Vec8<T>::load(base + (t + 16) * ld, x2);
+        Vec8<T>::load(base + (t + 24) * ld, x3);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += (x0[j] + x1[j]) + (x2[j] + x3[j]);
+      }
+    }
+    for (; t < t1; t += 8) {
       float x[8];
       if (vec_ok) {
         Vec8<T>::load(base + t * ld, x);
@@ -146,14 +159,31 @@ __global__ void colsum_kernel(const T* __restrict__ G, long long Tn, int cols, l
 // LayerNorm per-sample gradients, one warp per token row, F <= 256 * NCHUNK, F % 8 == 0.
 //   gw[n, f] += sum_t G[n,t,f] * xhat[n,t,f],   gb[n, f] += sum_t G[n,t,f]
 // ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Each warp streams its token rows through a private three-slot ring in shared memory filled with
+// cp.async: the loads of the next two rows are in flight while the current row goes through its two
+// dependent shuffle reductions.  A lane reads back exactly the 16-byte pieces it copied itself, so
+// the ring needs no synchronisation beyond cp.async.wait_group.
+constexpr int kLnSlots = 3;
+
 template <typename T, int NCHUNK>
 __global__ void __launch_bounds__(256, NCHUNK <= 3 ? 2 : 1)
 layernorm_persample_kernel(const T* __restrict__ A, const T* __restrict__ G, long long Tn, int F,
                            float eps, float* __restrict__ gw, float* __restrict__ gb,
                            float* __restrict__ part, int t_splits, int rms) {
-  extern __shared__ float sm[];   // [8 warps][2][F]
+  extern __shared__ __align__(16) unsigned char sm_raw[];   // rings [8 warps][3][2][F] of T, then [8][2][F] floats
+  float* sm = reinterpret_cast<float*>(sm_raw);
   const int n = blockIdx.y, split = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  T* ring = reinterpret_cast<T*>(sm_raw) + static_cast<size_t>(warp) * kLnSlots * 2 * F;
   const long long per = (Tn + t_splits - 1) / t_splits;
   const long long t0 = split * per;
   const long long t1 = (t0 + per < Tn) ? t0 + per : Tn;
@@ -163,16 +193,45 @@ layernorm_persample_kernel(const T* __restrict__ A, const T* __restrict__ G, lon
 #pragma unroll
     for (int j = 0; j < 8; ++j) { aw[i][j] = 0.f; ab[i][j] = 0.f; }
   const float invF = 1.f / static_cast<float>(F);
-  for (long long t = t0 + warp; t < t1; t += 8) {
-    const long long off = (static_cast<long long>(n) * Tn + t) * F;
+
+  auto issue = [&](long long t, int slot) {
+    if (t < t1) {
+      const long long off = (static_cast<long long>(n) * Tn + t) * F;
+      T* sa = ring + static_cast<size_t>(slot) * 2 * F;
+      T* sg = sa + F;
+#pragma unroll
+      for (int i = 0; i < NCHUNK; ++i) {
+        const int f = (i * 32 + lane) * 8;
+        if (f < F) {
+#pragma unroll
+          for (int b = 0; b < static_cast<int>(8 * sizeof(T)); b += 16) {
+            cp_async16(reinterpret_cast<unsigned char*>(sa + f) + b, reinterpret_cast<const unsigned char*>(A + off + f) + b);
+            cp_async16(reinterpret_cast<unsigned char*>(sg + f) + b, reinterpret_cast<const unsigned char*>(G + off + f) + b);
+          }
+        }
+      }
+    }
+    cp_async_commit();      // an empty group keeps the group count uniform at the tail
+  };
+
+  long long t = t0 + warp;
+  issue(t, 0);
+  issue(t + 8, 1);
+  int slot = 0;
+  for (; t < t1; t += 8) {
+    issue(t + 16, slot == 0 ? 2 : slot - 1);
+    cp_async_wait<kLnSlots - 1>();
+    const T* sa = ring + static_cast<size_t>(slot) * 2 * F;
+    const T* sg = sa + F;
+    slot = (slot + 1 == kLnSlots) ? 0 : slot + 1;
     float x[NCHUNK][8], g[NCHUNK][8];
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) {       // both rows are requested before any arithmetic
+    for (int i = 0; i < NCHUNK; ++i) {
       const int f = (i * 32 + lane) * 8;
       if (f < F) {
-        Vec8<T>::load(A + off + f, x[i]);
-        Vec8<T>::load(G + off + f, g[i]);
+        Vec8<T>::load(sa + f, x[i]);
+        Vec8<T>::load(sg + f, g[i]);
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) { x[i][j] = 0.f; g[i][j] = 0.f; }
@@ -201,6 +260,8 @@ layernorm_persample_kernel(const T* __restrict__ A, const T* __restrict__ G, lon
         ab[i][j] += g[i][j];
       }
   }
+  cp_async_wait<0>();
+  __syncthreads();          // the rings are reused as the cross-warp reduction scratch
   float* mine = sm + static_cast<size_t>(warp) * 2 * F;
 #pragma unroll
   for (int i = 0; i < NCHUNK; ++i) {
@@ -415,13 +476,16 @@ static int launch_ln(const T* A, const T* G, int N, long long Tn, int F, float e
                  "ghost_layernorm_persample: workspace too small");
     }
     dim3 grid(splits, N);
-    const size_t smem = sizeof(float) * 8 * 2 * static_cast<size_t>(F);
+    // per-warp cp.async rings (3 slots x (A row + G row)), reused for the cross-warp reduction
+    const size_t ring = sizeof(T) * 8 * kLnSlots * 2 * static_cast<size_t>(F);
+    const size_t red = sizeof(float) * 8 * 2 * static_cast<size_t>(F);
+    const size_t smem = ring > red ? ring : red;
     const int nchunk = (F + 255) / 256;
 #define GB_LN_LAUNCH(NC)                                                                              \
     do {                                                                                              \
       if (smem > 48 * 1024)                                                                           \
         GB_CUDA_OK(cudaFuncSetAttribute(layernorm_persample_kernel<T, NC>,                            \
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));     \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));    \
       layernorm_persample_kernel<T, NC><<<grid, 256, smem, st>>>(A, G, Tn, F, eps, gw, gb, ws, splits, rms); \
     } while (0)
     switch (nchunk) {

@@ -416,9 +416,17 @@ extern "C" int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, 
   p.T = n_rows;
   const int kb = ceil_div(n_rows, XtyCfg::BK);
   const int tiles = p.m_tiles * p.n_tiles;
+  // Split-K factor: the CTAs run ceil(units / SMs) rounds of (k-blocks per split + a fixed cost per
+  // unit for the accumulator hand-over and the red.add epilogue, measured at about 64 k-blocks' worth); take
+  // the factor with the shortest critical path.
   int splits = 1;
-  if (tiles < ds->sm_count) splits = (2 * ds->sm_count + tiles - 1) / tiles;
-  if (splits > kb) splits = kb;
+  long long best = -1;
+  for (int s = 1; s <= 64 && s <= kb; ++s) {
+    const long long units = static_cast<long long>(tiles) * s;
+    const long long rounds = (units + ds->sm_count - 1) / ds->sm_count;
+    const long long cost = rounds * (ceil_div(kb, s) + 64);
+    if (best < 0 || cost < best) { best = cost; splits = s; }
+  }
   p.kb_per_split = ceil_div(kb, splits);
   p.k_splits = ceil_div(kb, p.kb_per_split);
   p.acc_ws = static_cast<float*>(ws);

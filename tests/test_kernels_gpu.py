@@ -149,12 +149,13 @@ def test_persample_dot(case, dtype):
     assert O.rel_fro(M, M2.cpu()) < TOL[dtype]
 
 
-def test_persample_dot_in_groups():
+@pytest.mark.parametrize("sizes", [(37, 11, 70, 136, 264), (70, 35, 12, 72, 264)])
+def test_persample_dot_in_groups(sizes):
     """A small workspace budget forces the train samples through in several groups (and several
     validation / train blocks of the streaming kernel): same numbers as the single-pass run."""
     from ghostsuite_b200 import _lib
     lib = _lib.load()
-    n_t, n_v, T, d, p = 37, 11, 70, 136, 264
+    n_t, n_v, T, d, p = sizes
     A, G = make(n_t + n_v, T, d, p, torch.bfloat16, seed=11)
     ref = O.linear_dot_exact(A, G, n_v)
     gref = torch.einsum("btp,btd->pd", G[:n_t].double(), A[:n_t].double())
