@@ -482,7 +482,40 @@ def run_crossover(args):
     emit({"mode": "crossover", "layer": {"d_in": d, "d_out": p, "dtype": "bf16"}, "rows": rows})
 
 
-def run_gradproj_model(args):
+def _gradproj_world(local_rank: int, world: int):
+    """GradProj shards the corpus with no data-path communication; the process group only serves the
+    barrier around the timed region and the max-over-ranks of the step time."""
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    return torch.device("cuda", local_rank)
+
+
+def _gradproj_sync_ms(ms: float, world: int, dev) -> float:
+    if world <= 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _gradproj_barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def _gradproj_done(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def run_gradproj_model(args, rank: int = 0, world: int = 1, local_rank: int = 0):
     """GradProjLoRA on a Pythia-410M-shaped decoder (24 layers, d=1024, 16 heads, MLP 4096, vocab 50304,
     random init, bf16), sequence 2048, batch 16, k_i = k_o = 32 on every attention / MLP Linear,
     projections streamed to pinned host memory and written to disk by the engine's writer thread."""
@@ -492,8 +525,7 @@ def run_gradproj_model(args):
     from transformers import GPTNeoXConfig, GPTNeoXForCausalLM
     from ghostsuite_b200 import _lib
     from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoraEngine
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
+    dev = _gradproj_world(local_rank, world)
     torch.manual_seed(0)
     cfg = GPTNeoXConfig(hidden_size=1024, num_hidden_layers=24, num_attention_heads=16, intermediate_size=4096,
                         vocab_size=50304, max_position_embeddings=2048, use_cache=False)
@@ -505,7 +537,7 @@ def run_gradproj_model(args):
                                  proj_dims_override=(32, 32))
         eng.attach()
     B, T = 16, 2048
-    g = torch.Generator().manual_seed(1)
+    g = torch.Generator().manual_seed(1 + rank)          # every rank draws its own shard of the corpus
     batches = [torch.randint(0, 50304, (B, T), generator=g).pin_memory() for _ in range(4)]
 
     def step(i):
@@ -513,13 +545,14 @@ def run_gradproj_model(args):
         model.zero_grad(set_to_none=True)
         loss = model(input_ids=x, labels=x).loss
         loss.backward()
-        eng.collect_batch(batch_indices=list(range(i * B, (i + 1) * B)))
+        first = (i * world + rank) * B                   # corpus rows of this rank's i-th batch
+        eng.collect_batch(batch_indices=list(range(first, first + B)))
         eng.clear_gradients()
 
     for i in range(args.warmup):
         step(i)
     eng.flush()
-    torch.cuda.synchronize()
+    _gradproj_barrier(world)
     l0 = _lib.launch_count()
     t0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -530,21 +563,25 @@ def run_gradproj_model(args):
     torch.cuda.synchronize()
     eng.flush()
     wall = time.perf_counter() - t0
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = _gradproj_sync_ms(e0.elapsed_time(e1) / args.steps, world, dev)
     _lib.poll_kernel_error()
     n_files = len([f for f in os.listdir(out_dir) if f.startswith("proj_iter_")])
     total_proj_dim, n_layers = eng.total_proj_dim, len(eng.matched_layers)
     eng.cleanup()
     shutil.rmtree(out_dir, ignore_errors=True)
+    _gradproj_done(world)
+    if rank != 0:
+        return
     emit({"mode": "gradproj_model", "workload": " ".join(run_gradproj_model.__doc__.split()),
-                      "layers": n_layers, "total_proj_dim": total_proj_dim,
-                      "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
+                      "layers": n_layers, "total_proj_dim": total_proj_dim, "n_gpus": world,
+                      "scaling": "weak (corpus sharded, no communication)",
+                      "tokens_per_s": world * B * T / (ms * 1e-3), "ms_per_step": ms,
                       "wall_ms_per_step_including_disk_flush": wall * 1e3 / args.steps,
                       "d2h_bytes_per_step": B * total_proj_dim * 4, "files_written": n_files,
                       "gpu_launches": int(_lib.launch_count() - l0)})
 
 
-def run_gradproj_llama(args):
+def run_gradproj_llama(args, rank: int = 0, world: int = 1, local_rank: int = 0):
     """GradProjLoRA on a Llama-3-8B-shaped decoder (32 layers, d=4096, 32 heads / 8 KV heads, SwiGLU 14336,
     vocab 128256, random init, bf16), sequence 4096, k_i = k_o = 64 on all 224 attention / MLP Linears.
     Without recomputation the saved activations of the 32-layer model are about 7.8 MB per token, so
@@ -559,8 +596,7 @@ def run_gradproj_llama(args):
     from ghostsuite_b200 import _lib
     from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoraEngine
     from ghostsuite_b200.ghostEngines.transformers_support import _add_dummy_bias
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
+    dev = _gradproj_world(local_rank, world)
     torch.manual_seed(0)
     cfg = LlamaConfig(hidden_size=4096, num_hidden_layers=args.layers, num_attention_heads=32,
                       num_key_value_heads=8, intermediate_size=14336, vocab_size=128256,
@@ -581,20 +617,21 @@ def run_gradproj_llama(args):
                                  proj_dims_override=(64, 64))
         eng.attach()
     B, T = args.batch, 4096
-    g = torch.Generator().manual_seed(1)
+    g = torch.Generator().manual_seed(1 + rank)          # every rank draws its own shard of the corpus
     batches = [torch.randint(0, 128256, (B, T), generator=g).pin_memory() for _ in range(2)]
 
     def step(i):
         x = batches[i % 2].to(dev, non_blocking=True)
         loss = model(input_ids=x, labels=x).loss
         loss.backward()
-        eng.collect_batch(batch_indices=list(range(i * B, (i + 1) * B)))
+        first = (i * world + rank) * B
+        eng.collect_batch(batch_indices=list(range(first, first + B)))
         eng.clear_gradients()
 
     for i in range(args.warmup):
         step(i)
     eng.flush()
-    torch.cuda.synchronize()
+    _gradproj_barrier(world)
     from ghostsuite_b200 import ops
     l0 = _lib.launch_count()
     ops.start_kernel_timing()
@@ -603,9 +640,10 @@ def run_gradproj_llama(args):
     for i in range(args.steps):
         step(i)
     e1.record()
+    torch.cuda.synchronize()
     prof = ops.stop_kernel_timing()
     eng.flush()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = _gradproj_sync_ms(e0.elapsed_time(e1) / args.steps, world, dev)
     _lib.poll_kernel_error()
     rec = prof["ops"].get("gradproj_kernel", {"ms": 0.0, "calls": 1, "bytes": 0.0})
     peaks = _peaks()
@@ -613,10 +651,14 @@ def run_gradproj_llama(args):
     total_proj_dim, n_layers = eng.total_proj_dim, len(eng.matched_layers)
     eng.cleanup()
     shutil.rmtree(out_dir, ignore_errors=True)
+    _gradproj_done(world)
+    if rank != 0:
+        return
     emit({"mode": "gradproj_llama", "workload": " ".join(run_gradproj_llama.__doc__.split()),
-                      "layers_projected": n_layers, "total_proj_dim": total_proj_dim,
+                      "layers_projected": n_layers, "total_proj_dim": total_proj_dim, "n_gpus": world,
+                      "scaling": "weak (corpus sharded, no communication)",
                       "batch": B, "seq_len": T, "activation_checkpointing": bool(args.checkpoint),
-                      "tokens_per_s": B * T / (ms * 1e-3), "ms_per_step": ms,
+                      "tokens_per_s": world * B * T / (ms * 1e-3), "ms_per_step": ms,
                       "gradproj_kernel_ms_per_step": rec["ms"] / args.steps,
                       "gradproj_kernel_gbs": gbs, "gradproj_kernel_frac_of_measured_hbm": gbs / peaks["hbm"],
                       "d2h_bytes_per_step": B * total_proj_dim * 4,
@@ -654,10 +696,10 @@ def main():
         run_crossover(args)
         return
     if args.mode == "gradproj_model":
-        run_gradproj_model(args)
+        run_gradproj_model(args, rank, world, local_rank)
         return
     if args.mode == "gradproj_llama":
-        run_gradproj_llama(args)
+        run_gradproj_llama(args, rank, world, local_rank)
         return
     if args.impl == "reference":
         line = run_reference_arm(args, rank)
