@@ -35,7 +35,7 @@ def f32(x):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the GhostSuite reference to import from")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import transformers.pytorch_utils as tpu
