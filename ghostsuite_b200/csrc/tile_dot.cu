@@ -234,15 +234,21 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Elements per stage row of the bf16 kernel.  Every warp pays a barrier wait per stage, so a stage
+// is made as wide as the shared memory allows: 512 elements = 64 per warp = four k-steps.
+constexpr int kMmaCols = 512;
+
 template <int NVT>   // 8-row validation blocks per stage (1, 2 or 4)
 struct TdMmaCfg {
   static constexpr int kValRows = 8 * NVT;
-  static constexpr int kPanels = kTdCols / 64;                               // 64-element panels per stage row
+  static constexpr int kPanels = kMmaCols / 64;                              // 64-element panels per stage row
+  static constexpr int kWarpChunks = kMmaCols / 8 / 8;                       // 16-byte chunks per warp and stage
+  static constexpr int kWarpKSteps = kWarpChunks / 2;
   static constexpr int kValBytes = kPanels * kValRows * 128;
-  static constexpr int kStageBytes = kValBytes + kPanels * kTdTrainRows * 128;   // 20 / 24 / 32 KB
-  static constexpr int kStages = NVT == 1 ? 8 : (NVT == 2 ? 6 : 5);
+  static constexpr int kStageBytes = kValBytes + kPanels * kTdTrainRows * 128;   // 40 / 48 / 64 KB
+  static constexpr int kStages = NVT == 1 ? 4 : 3;
   static constexpr int kRedBytes = 8 * kTdTrainRows * kValRows * 4;          // per-warp partial dot blocks
-  static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + kTdCols * 4 + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + 1024 + 256;
 };
 
 template <int NVT>
@@ -254,7 +260,7 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* s_red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);            // [8 warps][32][VR]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kRedBytes + kTdCols * 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kRedBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages);
@@ -262,7 +268,8 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long s_begin = static_cast<long long>(blockIdx.x) * p.stages_per_cta;
   const long long s_end = (s_begin + p.stages_per_cta < p.stages) ? s_begin + p.stages_per_cta : p.stages;
-  constexpr int kStagesPerTile = kTileElems / kTdCols;   // 128
+  constexpr int kStagesPerTile = kTileElems / kMmaCols;   // 64
+  constexpr int KS = Cfg::kWarpKSteps, CW = Cfg::kWarpChunks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 8); }
@@ -282,7 +289,7 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
             if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 431)) { ok = false; break; }
             uint8_t* st = smem + stage * Cfg::kStageBytes;
             const int tile = static_cast<int>(s / kStagesPerTile);
-            const int panel = static_cast<int>(s % kStagesPerTile) * Cfg::kPanels;
+            const int panel = static_cast<int>(s % kStagesPerTile) * Cfg::kPanels;   // 64-element panels
             mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
             tma_load_4d(st, &tm_v, &full_bar[stage], 0, p.v_off + v0, panel, tile);
             tma_load_4d(st + Cfg::kValBytes, &tm_w, &full_bar[stage], 0, j0, panel, tile);
@@ -293,27 +300,29 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
   }
 
   // ------------------------------------------------------------------ compute warps 0-7
-  // This warp's slice of a stage: panel `pn`, 16-byte chunks c0..c0+3 (32 elements, two k-steps).
-  const int pn = warp >> 1, c0 = (warp & 1) * 4;
+  // This warp's slice of a stage: CW 16-byte chunks (KS k-steps) starting at chunk c0 of panel pn.
+  const int pn = (warp * CW) / 8, c0 = (warp * CW) % 8;
   const int g = lane >> 2, q = lane & 3;
   // ldmatrix lane addresses inside a stage (panel rows are 128 bytes, chunk index XOR (row & 7))
-  uint32_t a_off[2][2];      // W as the A operand: [m-tile][k-step]
+  uint32_t a_off[2][KS];     // W as the A operand: [m-tile][k-step]
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
+    for (int ks = 0; ks < KS; ++ks) {
       const int row = mt * 16 + (lane & 15), chunk = c0 + 2 * ks + (lane >> 4);
       a_off[mt][ks] = Cfg::kValBytes + pn * (kTdTrainRows * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
     }
-  uint32_t b_off[NVT];       // V as the B operand: [n-tile], both k-steps in one x4
+  uint32_t b_off[NVT][KS / 2];   // V as the B operand: [n-tile][pair of k-steps], one x4 each
 #pragma unroll
-  for (int nt = 0; nt < NVT; ++nt) {
-    const int row = nt * 8 + (lane & 7), chunk = c0 + (lane >> 3);
-    b_off[nt] = pn * (VR * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
-  }
-  uint32_t t_off[4];         // W transposed, for the column sums: [8-element group], rows = lane
+  for (int nt = 0; nt < NVT; ++nt)
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
+    for (int h = 0; h < KS / 2; ++h) {
+      const int row = nt * 8 + (lane & 7), chunk = c0 + 4 * h + (lane >> 3);
+      b_off[nt][h] = pn * (VR * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
+    }
+  uint32_t t_off[CW];        // W transposed, for the column sums: [8-element group], rows = lane
+#pragma unroll
+  for (int j = 0; j < CW; ++j)
     t_off[j] = Cfg::kValBytes + pn * (kTdTrainRows * 128) + lane * 128 + (((c0 + j) ^ (lane & 7)) << 4);
 
   int stage = 0; uint32_t phase = 0;
@@ -345,49 +354,48 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) { alive = false; break; }
         const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
-        uint32_t a[2][2][4];
+        uint32_t a[2][KS][4];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-          for (int ks = 0; ks < 2; ++ks) ldsm_x4(st + a_off[mt][ks], a[mt][ks]);
+          for (int ks = 0; ks < KS; ++ks) ldsm_x4(st + a_off[mt][ks], a[mt][ks]);
 #pragma unroll
-        for (int nt = 0; nt < NVT; ++nt) {
-          uint32_t b[4];
-          ldsm_x4(st + b_off[nt], b);
+        for (int nt = 0; nt < NVT; ++nt)
 #pragma unroll
-          for (int mt = 0; mt < 2; ++mt) {
-            mma_bf16_16816(acc[mt][nt], a[mt][0], b[0], b[1]);
-            mma_bf16_16816(acc[mt][nt], a[mt][1], b[2], b[3]);
+          for (int h = 0; h < KS / 2; ++h) {
+            uint32_t b[4];
+            ldsm_x4(st + b_off[nt][h], b);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+              mma_bf16_16816(acc[mt][nt], a[mt][2 * h], b[0], b[1]);
+              mma_bf16_16816(acc[mt][nt], a[mt][2 * h + 1], b[2], b[3]);
+            }
           }
-        }
-        float csum[4][4];
+        float t0 = 0.f, t1 = 0.f;
         if (do_sum) {
+          // every row of the column-sum accumulator holds the sums of 8 elements of this warp's
+          // slice; lane (g, q) keeps elements 8g + 2q, 8g + 2q + 1 of each group of 64
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < CW; ++j) {
             uint32_t t[4];
+            float cs[4] = {0.f, 0.f, 0.f, 0.f};
             ldsm_x4_trans(st + t_off[j], t);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) csum[j][e] = 0.f;
-            mma_bf16_16816(csum[j], mask_a[0], t[0], t[1]);
-            mma_bf16_16816(csum[j], mask_a[1], t[2], t[3]);
+            mma_bf16_16816(cs, mask_a[0], t[0], t[1]);
+            mma_bf16_16816(cs, mask_a[1], t[2], t[3]);
+            if (g == (j & 7)) { t0 = cs[0]; t1 = cs[1]; }
           }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[stage]);     // this warp is done with the stage
         if (++stage == kStages) { stage = 0; phase ^= 1; }
-        if (do_sum && g < 4) {
-          // every row of csum[j] holds the sums of elements 8j..8j+7 of this warp's slice; lane
-          // (g = j, q) writes elements 8j + 2q, 8j + 2q + 1: the warp covers 32 adjacent elements
-          float t0 = 0.f, t1 = 0.f;
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (g == j) { t0 = csum[j][0]; t1 = csum[j][1]; }
-          const int e0 = warp * 32 + g * 8 + q * 2;          // element inside the stage row
+        if (do_sum && g < CW) {
+          const int e0 = warp * (CW * 8) + g * 8 + q * 2;    // element inside the stage
           if (p.out != nullptr) {
-            // one stage is one 256-column row segment of one 128 x 256 tile
+            // one stage is kMmaCols / 256 row segments (256 columns each) of one 128 x 256 tile
             const long long tile = s / kStagesPerTile;
-            const int r = static_cast<int>(tile / p.n_tiles_n) * 128 + static_cast<int>(s % kStagesPerTile);
-            const int c = static_cast<int>(tile % p.n_tiles_n) * 256 + e0;
+            const int r = static_cast<int>(tile / p.n_tiles_n) * 128 +
+                          static_cast<int>(s % kStagesPerTile) * (kMmaCols / 256) + (e0 >> 8);
+            const int c = static_cast<int>(tile % p.n_tiles_n) * 256 + (e0 & 255);
             if (r < p.m_cols && c < p.n_cols) {
               const long long o = static_cast<long long>(r) * p.n_cols + c;
               const bool rmw = p.out_accumulate || j0 > 0;
@@ -418,7 +426,7 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
               }
             }
           } else {
-            float2* dst = reinterpret_cast<float2*>(p.sum + s * kTdCols + e0);
+            float2* dst = reinterpret_cast<float2*>(p.sum + s * kMmaCols + e0);
             float2 v = make_float2(t0, t1);
             if (!(p.sum_init && j0 == 0)) { const float2 old = *dst; v.x += old.x; v.y += old.y; }
             *dst = v;
@@ -527,7 +535,7 @@ int launch_tile_dot(const void* V, int v_samples, int v_off, const void* W, int 
   p.v_off = v_off;
   p.out = out; p.out_is_f32 = out_is_f32; p.out_accumulate = out_accumulate;
   p.m_cols = m_cols; p.n_cols = n_cols; p.n_tiles_n = n_tiles_n; p.out_scale = out_scale;
-  p.stages = tiles * (kTileElems / kTdCols);
+  p.stages = tiles * (kTileElems / (is_f32 ? kTdCols : kMmaCols));
   p.stages_per_cta = 0;
   p.n_val = n_val; p.n_grp = n_grp; p.b0 = b0; p.n_train = n_train;
   p.scale = scale; p.M = M; p.sum = sum; p.sum_init = sum_init;
