@@ -56,6 +56,12 @@ struct XtyCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
 
+// one 256-bit store (the address must be 32-byte aligned)
+__device__ __forceinline__ void st_global_v8(void* addr, const uint32_t* v) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(addr), "r"(v[0]), "r"(v[1]),
+               "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
@@ -290,25 +296,21 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0u;
           }
+          // 32-byte stores: every store fills whole sectors of the thread's row
           if (p.v_is_f32) {
-            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.vgrad) + tbase + c0);
+            float* dst = static_cast<float*>(p.vgrad) + tbase + c0;
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                   __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+            for (int q = 0; q < 4; ++q) st_global_v8(dst + 8 * q, &r[8 * q]);
           } else {
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.vgrad) + tbase + c0);
+            uint32_t w[16];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * e]),
-                                                               __uint_as_float(r[8 * q + 2 * e + 1]));
-                w[e] = *reinterpret_cast<const uint32_t*>(&h);
-              }
-              dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int e = 0; e < 16; ++e) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+              w[e] = *reinterpret_cast<const uint32_t*>(&h);
             }
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.vgrad) + tbase + c0;
+            st_global_v8(dst, &w[0]);
+            st_global_v8(dst + 16, &w[8]);
           }
         }
       }
