@@ -287,16 +287,12 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
         //   dst[(tile * samples + sample)][row][col], one 512- or 1024-byte row per thread
         const long long tbase = (static_cast<long long>(tile) * p.samples + sample) * (BM * BN) +
                                 static_cast<long long>(threadIdx.x) * BN;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(t_acc + c0, r);
-          tmem_ld_wait();
+        // two TMEM loads in flight per wait, 32-byte stores (every store fills whole sectors)
+        auto store32 = [&](int c0, uint32_t (&r)[32]) {
           if (empty_k) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0u;
           }
-          // 32-byte stores: every store fills whole sectors of the thread's row
           if (p.v_is_f32) {
             float* dst = static_cast<float*>(p.vgrad) + tbase + c0;
 #pragma unroll
@@ -312,6 +308,15 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             st_global_v8(dst, &w[0]);
             st_global_v8(dst + 16, &w[8]);
           }
+        };
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(t_acc + c0, r0);
+          tmem_ld32(t_acc + c0 + 32, r1);
+          tmem_ld_wait();
+          store32(c0, r0);
+          store32(c0 + 32, r1);
         }
       }
       tc_fence_before_sync();
