@@ -482,6 +482,15 @@ def run_crossover(args):
     emit({"mode": "crossover", "layer": {"d_in": d, "d_out": p, "dtype": "bf16"}, "rows": rows})
 
 
+def _next_token_loss(logits, ids):
+    """Mean next-token cross-entropy from the library's fused loss kernels (targets shifted, last
+    position of every sequence ignored) instead of the model's own fp32 log-softmax."""
+    from ghostsuite_b200.workloads import _FusedTokenLoss
+    B, T, V = logits.shape
+    target = torch.cat((ids[:, 1:], ids.new_full((B, 1), -100)), dim=1).reshape(-1)
+    return _FusedTokenLoss.apply(logits.reshape(-1, V), target, V)
+
+
 def _gradproj_world(local_rank: int, world: int):
     """GradProj shards the corpus with no data-path communication; the process group only serves the
     barrier around the timed region and the max-over-ranks of the step time."""
@@ -518,7 +527,9 @@ def _gradproj_done(world: int):
 def run_gradproj_model(args, rank: int = 0, world: int = 1, local_rank: int = 0):
     """GradProjLoRA on a Pythia-410M-shaped decoder (24 layers, d=1024, 16 heads, MLP 4096, vocab 50304,
     random init, bf16), sequence 2048, batch 16, k_i = k_o = 32 on every attention / MLP Linear,
-    projections streamed to pinned host memory and written to disk by the engine's writer thread."""
+    projections streamed to pinned host memory and written to disk by the engine's writer thread.
+    Weights have requires_grad=False (autograd computes activation gradients only); the loss comes
+    from the library's fused cross-entropy kernels."""
     import contextlib
     import io
     import shutil
@@ -530,6 +541,12 @@ def run_gradproj_model(args, rank: int = 0, world: int = 1, local_rank: int = 0)
     cfg = GPTNeoXConfig(hidden_size=1024, num_hidden_layers=24, num_attention_heads=16, intermediate_size=4096,
                         vocab_size=50304, max_position_embeddings=2048, use_cache=False)
     model = GPTNeoXForCausalLM(cfg).to(torch.bfloat16).to(dev)
+    # projections need activation gradients only: no weight requires grad, a one-element dummy bias on
+    # the embedding keeps the graph alive (the reference's loop computes and discards the weight gradients)
+    from ghostsuite_b200.ghostEngines.transformers_support import _add_dummy_bias
+    for prm in model.parameters():
+        prm.requires_grad = False
+    _add_dummy_bias(model.get_input_embeddings())
     out_dir = tempfile.mkdtemp(prefix="gradproj_bench_")
     with contextlib.redirect_stdout(io.StringIO()):
         eng = GradProjLoraEngine(model, proj_layers="attention,mlp", proj_rank_total=1024, proj_rank_min=4,
@@ -543,8 +560,7 @@ def run_gradproj_model(args, rank: int = 0, world: int = 1, local_rank: int = 0)
     def step(i):
         x = batches[i % 4].to(dev, non_blocking=True)
         model.zero_grad(set_to_none=True)
-        loss = model(input_ids=x, labels=x).loss
-        loss.backward()
+        _next_token_loss(model(input_ids=x).logits, x).backward()
         first = (i * world + rank) * B                   # corpus rows of this rank's i-th batch
         eng.collect_batch(batch_indices=list(range(first, first + B)))
         eng.clear_gradients()
@@ -622,8 +638,7 @@ def run_gradproj_llama(args, rank: int = 0, world: int = 1, local_rank: int = 0)
 
     def step(i):
         x = batches[i % 2].to(dev, non_blocking=True)
-        loss = model(input_ids=x, labels=x).loss
-        loss.backward()
+        _next_token_loss(model(input_ids=x).logits, x).backward()
         first = (i * world + rank) * B
         eng.collect_batch(batch_indices=list(range(first, first + B)))
         eng.clear_gradients()
