@@ -482,6 +482,122 @@ def run_crossover(args):
     emit({"mode": "crossover", "layer": {"d_in": d, "d_out": p, "dtype": "bf16"}, "rows": rows})
 
 
+def run_mlp(args):
+    """GradDotProd on the fp32 MLP 512 -> 1024 -> 1024 -> 10 (Linear + ReLU, cross-entropy), 64 train +
+    16 validation samples, SGD: the launch-latency-bound configuration.  Reports microseconds per step
+    (forward, backward with hooks, prepare_gradients, optimizer step, aggregate with its device-to-host
+    read) for the CUDA engine and for the CPU restatement of the reference's path."""
+    from ghostsuite_b200 import _lib
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    from ghostsuite_b200.workloads import make_mlp
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n_t, n_v = 64, 16
+
+    def run(device, steps, warmup):
+        torch.manual_seed(0)
+        model = make_mlp().to(device)
+        opt = torch.optim.SGD(model.parameters(), lr=0.1)
+        on_gpu = device.type == "cuda"
+        if on_gpu:
+            eng = GradDotProdEngine(module=model, val_batch_size=n_v, loss_reduction="mean")
+            eng.attach(opt)
+        else:
+            from oracle.ghost_engine_cpu import OracleDotProdEngine
+            eng = OracleDotProdEngine(model, n_v)
+            eng.attach()
+        g = torch.Generator().manual_seed(0)
+        X = torch.randn(n_t + n_v, 512, generator=g).to(device)
+        Y = torch.randint(0, 10, (n_t + n_v,), generator=g).to(device)
+
+        def step(i):
+            if on_gpu:
+                eng.attach_train_batch(X[:n_t], Y[:n_t], i, i)
+            torch.nn.functional.cross_entropy(model(X), Y).backward()
+            eng.prepare_gradients()
+            opt.step()
+            if on_gpu:
+                eng.aggregate_and_log()
+                eng.dot_product_log.clear()
+            else:
+                eng.aggregate()
+            eng.clear_gradients()
+            opt.zero_grad(set_to_none=True)
+
+        for i in range(warmup):
+            step(i)
+        if on_gpu:
+            torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            step(i)
+        if on_gpu:
+            torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / steps
+        eng.detach()
+        return dt * 1e6
+
+    def run_graph(steps, warmup):
+        """The same step with forward, backward (hooks included), prepare_gradients and the optimizer
+        step captured once in a CUDA graph and replayed: the hooks' kernels, workspaces and result
+        tensors keep their addresses, so each replay refreshes ``param.grad_dot_prod_matrix`` in place
+        and only the aggregation (one stacked sum and the device-to-host read) runs eagerly."""
+        torch.manual_seed(0)
+        model = make_mlp().to(dev)
+        opt = torch.optim.SGD(model.parameters(), lr=0.1)
+        eng = GradDotProdEngine(module=model, val_batch_size=n_v, loss_reduction="mean")
+        eng.attach(opt)
+        g = torch.Generator().manual_seed(0)
+        X = torch.randn(n_t + n_v, 512, generator=g).to(dev)
+        Y = torch.randint(0, 10, (n_t + n_v,), generator=g).to(dev)
+
+        def body():
+            torch.nn.functional.cross_entropy(model(X), Y).backward()
+            eng.prepare_gradients()
+            opt.step()
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                 # warm-up on the capture stream (lazy initialisations)
+            for _ in range(3):
+                body()
+                eng.clear_gradients()
+                opt.zero_grad(set_to_none=True)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            body()
+        mats = [p_.grad_dot_prod_matrix for p_ in model.parameters() if hasattr(p_, "grad_dot_prod_matrix")]
+
+        def step():
+            graph.replay()
+            total = torch.stack(mats).sum(dim=0)
+            return total.sum(dim=0).cpu()             # the step's device-to-host read (and sync)
+
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            out = step()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / steps
+        assert out.shape == (n_t,) and bool(torch.isfinite(out).all())
+        _lib.poll_kernel_error()
+        return dt * 1e6
+
+    l0 = _lib.launch_count()
+    gpu_us = run(dev, max(args.steps, 50), max(args.warmup, 5))
+    launches = (_lib.launch_count() - l0) / (max(args.steps, 50) + max(args.warmup, 5))
+    _lib.poll_kernel_error()
+    cpu_us = run(torch.device("cpu"), 20, 3)
+    graph_us = run_graph(max(args.steps, 50), max(args.warmup, 5))
+    emit({"mode": "mlp", "workload": " ".join(run_mlp.__doc__.split()), "us_per_step": gpu_us,
+          "us_per_step_cuda_graph": graph_us, "library_launches_per_step": launches,
+          "cpu_baseline": {"us_per_step": cpu_us, "cores": torch.get_num_threads(), "kind": "port"}})
+
+
 def _next_token_loss(logits, ids):
     """Mean next-token cross-entropy from the library's fused loss kernels (targets shifted, last
     position of every sequence ignored) instead of the model's own fp32 log-softmax."""
@@ -693,7 +809,7 @@ def main():
     ap.add_argument("--checkpoint", action="store_true",
                     help="gradproj_llama mode: recompute decoder layers in the backward pass (needed for --batch 8)")
     ap.add_argument("--mode", default="step",
-                    choices=["step", "kernels", "crossover", "gradproj_model", "gradproj_llama"],
+                    choices=["step", "kernels", "crossover", "gradproj_model", "gradproj_llama", "mlp"],
                     help="step: the driver's benchmark line; kernels: per-kernel microbenchmarks; crossover: "
                          "Gram vs per-sample path over T on one Linear layer; gradproj_model: GradProj on a "
                          "Pythia-410M-shaped model")
@@ -709,6 +825,9 @@ def main():
         return
     if args.mode == "crossover":
         run_crossover(args)
+        return
+    if args.mode == "mlp":
+        run_mlp(args)
         return
     if args.mode == "gradproj_model":
         run_gradproj_model(args, rank, world, local_rank)

@@ -640,3 +640,59 @@ def test_gradproj_bin_format(tmp_path):
     assert np.array_equal(np.asarray(rows), torch.cat(got).numpy())
     eng.cleanup()
     assert (tmp_path / "b" / "metadata.json").exists()
+
+
+def test_step_under_cuda_graph_replay():
+    """Forward, backward with the dot-product hooks, prepare_gradients and the optimizer step captured
+    once in a CUDA graph: a replay on a new batch (copied into the static input) gives the same
+    matrices and train gradients as the eager engine."""
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    from ghostsuite_b200.workloads import make_mlp
+    n_t, n_v = 12, 4
+    g = torch.Generator().manual_seed(2)
+    batches = [(torch.randn(n_t + n_v, 512, generator=g).cuda(), torch.randint(0, 10, (n_t + n_v,), generator=g).cuda())
+               for _ in range(2)]
+    torch.manual_seed(1)
+    model = make_mlp().cuda()
+    eager = make_mlp().cuda()
+    eager.load_state_dict(model.state_dict())
+    opt = torch.optim.SGD(model.parameters(), lr=0.0)
+    eng = GradDotProdEngine(module=model, val_batch_size=n_v)
+    eng.attach(opt)
+    X, Y = batches[0][0].clone(), batches[0][1].clone()
+
+    def body():
+        nn.functional.cross_entropy(model(X), Y).backward()
+        eng.prepare_gradients()
+        opt.step()
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            body()
+            eng.clear_gradients()
+            opt.zero_grad(set_to_none=True)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        body()
+    params = [p for p in model.parameters()]
+    X.copy_(batches[1][0]); Y.copy_(batches[1][1])
+    graph.replay()
+    torch.cuda.synchronize()
+    got_M = [p.grad_dot_prod_matrix.clone() for p in params]
+    got_v = [p.grad_dot_prod.clone() for p in params]
+    got_g = [p.train_grad.clone() for p in params]
+
+    e_opt = torch.optim.SGD(eager.parameters(), lr=0.0)
+    e_eng = GradDotProdEngine(module=eager, val_batch_size=n_v)
+    e_eng.attach(e_opt)
+    nn.functional.cross_entropy(eager(batches[1][0]), batches[1][1]).backward()
+    for p, M, v, gr in zip(eager.parameters(), got_M, got_v, got_g):
+        assert O.rel_fro(M, p.grad_dot_prod_matrix) < 1e-5
+        assert O.rel_fro(v, p.grad_dot_prod) < 1e-5
+        assert O.rel_fro(gr, p.train_grad) < 1e-5
+    e_eng.detach()
+    eng.detach()
