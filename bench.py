@@ -246,9 +246,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             gdist.sync_engine(engine, group)
         engine.prepare_gradients()
         opt.step()
-        engine.aggregate_and_log()          # device -> host read of the step's result
-        engine.clear_gradients()
+        engine.clear_gradients()            # host-side bookkeeping first, while the GPU is still busy
         opt.zero_grad(set_to_none=True)
+        engine.aggregate_and_log()          # device -> host read of the step's result (the step's sync)
         engine.dot_product_log.clear()
 
     def timed(from_host: bool, profile: bool):
