@@ -35,7 +35,7 @@ PROTOTYPES = {
     "ghost_wgrad_bf16": (_i, [_vp, _vp, _ll, _i, _i, _ll, _ll, _f, _i, _vp, _i, _vp, _ll, _vp]),
     "ghost_persample_workspace_bytes": (_ll, [_i, _i, _i, _i, _i]),
     "ghost_set_persample_budget_bytes": (_i, [_ll]),
-    "ghost_persample_dot_bf16": (_i, [_vp, _vp, _i, _i, _ll, _i, _i, _ll, _ll, _f, _vp, _i, _vp, _i, _f, _i, _vp, _ll, _vp]),
+    "ghost_persample_dot_bf16": (_i, [_vp, _vp, _i, _i, _ll, _i, _i, _ll, _ll, _f, _vp, _i, _vp, _i, _f, _i, _i, _vp, _vp, _ll, _vp]),
     "ghost_colsum": (_i, [_vp, _i, _i, _ll, _i, _ll, _vp, _vp]),
     "ghost_layernorm_workspace_bytes": (_ll, [_i, _ll, _i]),
     "ghost_layernorm_persample": (_i, [_vp, _vp, _i, _i, _ll, _i, _f, _vp, _vp, _vp, _ll, _vp]),
@@ -48,7 +48,8 @@ PROTOTYPES = {
     "ghost_embedding_wgrad_workspace_bytes": (_ll, [_i, _ll, _i]),
     "ghost_embedding_wgrad": (_i, [_vp, _vp, _i, _i, _ll, _i, _i, _f, _f, _i, _vp, _vp, _ll, _vp]),
     "ghost_gradproj_dense_bf16": (_i, [_vp, _vp, _i, _ll, _i, _i, _ll, _ll, _vp, _vp, _i, _i, _ll, _ll, _f, _vp, _ll, _vp]),
-    "ghost_workload_ce_forward": (_i, [_vp, _i, _ll, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp]),
+    "ghost_workload_ce_forward": (_i, [_vp, _i, _ll, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp]),
+    "ghost_workload_ce_rescale": (_i, [_vp, _i, _ll, _i, _vp, _vp]),
     "ghost_workload_ce_backward": (_i, [_vp, _i, _ll, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp]),
 }
 

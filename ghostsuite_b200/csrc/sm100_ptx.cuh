@@ -87,6 +87,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Bounded wait for a shared-memory progress counter (written by one thread of the CTA) to pass
+// `target`.  Same give-up protocol as mbar_wait.
+__device__ __forceinline__ bool counter_wait(volatile int* counter, int target, volatile int* abort_flag,
+                                             int* err, int code) {
+#pragma unroll 1
+  for (int i = 0; i < 256; ++i)
+    if (*counter > target) return true;
+  const unsigned long long t0 = globaltimer_ns();
+#pragma unroll 1
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (*counter > target) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      atomicCAS(err, 0, code);
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
+
 // Whole-warp form: every lane waits (so every lane acquires), then the warp agrees on the outcome,
 // so that .sync.aligned instructions after it are never executed by a partial warp.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity,

@@ -45,6 +45,10 @@ struct XtyParams {
   long long ld_v;
   int v_is_f32;
   int sample_major;          // unit order (sample, tile), dealt round-robin to the CTAs; needs k_splits == 1
+  // per-sample column sums of one operand (bias terms), taken by four extra warps from the stages
+  // the MMAs consume: 0 = none, 1 = X, 2 = Y; out [all samples, cols of that operand] fp32
+  int colsum_of;
+  float* colsum_out;
   int blocked_x, blocked_y;  // operand map is the blocked 4-D form: one TMA per stage instead of one per 64 columns
   int* err;
 };
@@ -83,7 +87,8 @@ __device__ __forceinline__ void red_add_row32(float* dst, const uint32_t (&r)[32
   }
 }
 
-__global__ void __launch_bounds__(192, 1)
+template <bool kColsum>
+__global__ void __launch_bounds__(kColsum ? 320 : 192, 1)
 xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                 const XtyParams p) {
   using Cfg = XtyCfg;
@@ -96,8 +101,10 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   uint64_t* empty_bar = bars + kStages;
   uint64_t* acc_full = bars + 2 * kStages;     // [2]
   uint64_t* acc_empty = acc_full + 2;          // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* cs_done = acc_empty + 2;           // [kStages], column-sum warps only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cs_done + kStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* issued = abort_flag + 1;       // stages the producer has issued so far (column sums)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -118,12 +125,14 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      if (kColsum) mbar_init(&cs_done[s], 4);        // one arrival per column-sum warp
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);
     }
     *abort_flag = 0;
+    *issued = 0;
     fence_barrier_init();
   }
   if (warp == 5) {
@@ -167,13 +176,26 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // column sums: a stage last filled for a summed unit may only be refilled once the
+      // column-sum warps have read it (bit s of the masks: stage s)
+      uint32_t cs_pending = 0, cs_phase = 0;
+      int n_issued = 0;
       for (long long u = u_begin; u < u_end && ok; u += u_step) {
         int tile, sample, kb0, kb1;
         decode(u, tile, sample, kb0, kb1);
         const int m0 = (tile / p.n_tiles) * BM;
         const int n0 = (tile % p.n_tiles) * BN;
+        const bool summed = kColsum && (p.colsum_of == 2 ? tile / p.n_tiles == 0 : tile % p.n_tiles == 0);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 411)) { ok = false; break; }
+          if (kColsum) {
+            const uint32_t bit = 1u << stage;
+            if (cs_pending & bit) {
+              if (!mbar_wait(&cs_done[stage], (cs_phase >> stage) & 1u, abort_flag, p.err, 412)) { ok = false; break; }
+              cs_phase ^= bit;
+            }
+            cs_pending = summed ? (cs_pending | bit) : (cs_pending & ~bit);
+          }
           uint8_t* st = smem + stage * Cfg::kStageBytes;
           mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           const int row = kb * BK;
@@ -194,6 +216,7 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             for (int j = 0; j < BN / 64; ++j)
               tma_load_3d(st + BM * BK * 2 + j * (BK * 128), &tm_y, &full_bar[stage], n0 + j * 64, row, z);
           }
+          if (kColsum) { __threadfence_block(); *issued = ++n_issued; }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -228,6 +251,64 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
         }
         if (ok) umma_commit(&acc_full[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else if (kColsum && warp >= 6) {
+    // ---------------------------------------------------------------- column sums (warps 6-9)
+    // Thread j owns columns 2j, 2j+1 of the operand tile: one bf16x2 word per token row of the
+    // stage, conflict-free (a row of a panel is 128 bytes = 32 words, one per lane).  The sums are
+    // taken from the units whose other tile index is 0, which see each column block exactly once.
+    // Only the stages of summed units are waited for, read and acknowledged (cs_done); the producer
+    // waits for that acknowledgement before refilling such a stage.  Stages of other units are
+    // skipped by counting.  Because a barrier wait only knows the parity of the phase it waits
+    // for, the warps first wait until the producer's progress counter says that the stage has been
+    // issued: from then on its full barrier can only be in the wanted phase or just past it.  The
+    // four warps do not synchronise with one another.
+    const int j = threadIdx.x - 192;                       // 0..127
+    const bool of_y = p.colsum_of == 2;
+    const int cols_tile = of_y ? BN : BM;
+    const int col = 2 * j;                                 // column inside the tile
+    const bool own = col < cols_tile;
+    const uint32_t op_off = of_y ? BM * BK * 2 : 0;
+    // address of token row 0: panel (col / 64), 16-byte chunk (col % 64) / 8, word ((col % 8) / 2)
+    const uint32_t base_off = op_off + (col >> 6) * (BK * 128) + (((col & 63) >> 1) & 3) * 4;
+    const int chunk = (col & 63) >> 3;
+    const int total_cols = of_y ? p.n_cols : p.m_cols;
+    int kcount = 0;                                        // stages of this CTA before the current unit
+    bool alive = true;
+    for (long long u = u_begin; u < u_end && alive; u += u_step) {
+      int tile, sample, kb0, kb1;
+      decode(u, tile, sample, kb0, kb1);
+      const int tm = tile / p.n_tiles, tn = tile % p.n_tiles;
+      const bool summed = of_y ? tm == 0 : tn == 0;
+      if (!summed) { kcount += kb1 - kb0; continue; }
+      float s0 = 0.f, s1 = 0.f;
+      for (int kb = kb0; kb < kb1; ++kb, ++kcount) {
+        const int stage = kcount % kStages;
+        const uint32_t phase = (kcount / kStages) & 1;
+        int ok = 1;
+        if (lane == 0)
+          ok = (counter_wait(issued, kcount, abort_flag, p.err, 615) &&
+                mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 616)) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { alive = false; break; }
+        if (own) {
+          const uint8_t* st = smem + stage * Cfg::kStageBytes + base_off;
+#pragma unroll 8
+          for (int t = 0; t < BK; ++t) {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(st + t * 128 + ((chunk ^ (t & 7)) << 4));
+            s0 += __uint_as_float(w << 16);
+            s1 += __uint_as_float(w & 0xffff0000u);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&cs_done[stage]);
+      }
+      if (own && alive) {
+        const int c = (of_y ? tn * BN : tm * BM) + col;
+        float* dst = p.colsum_out + static_cast<long long>(p.sample0 + sample) * total_cols + c;
+        if (c < total_cols) dst[0] = s0;
+        if (c + 1 < total_cols) dst[1] = s1;
       }
     }
   } else {
@@ -366,7 +447,9 @@ static int launch_xty(const CUtensorMap& tx, const CUtensorMap& ty, XtyParams p,
                       const DeviceState* ds, cudaStream_t st) {
   static bool attr_set[64] = {};
   if (!attr_set[ds->device]) {
-    GB_CUDA_OK(cudaFuncSetAttribute(xty_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    GB_CUDA_OK(cudaFuncSetAttribute(xty_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    XtyCfg::kSmemBytes));
+    GB_CUDA_OK(cudaFuncSetAttribute(xty_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     XtyCfg::kSmemBytes));
     attr_set[ds->device] = true;
   }
@@ -374,7 +457,10 @@ static int launch_xty(const CUtensorMap& tx, const CUtensorMap& ty, XtyParams p,
   int grid = static_cast<int>(units < ds->sm_count ? units : ds->sm_count);
   p.units_per_cta = static_cast<int>((units + grid - 1) / grid);
   if (!p.sample_major) grid = static_cast<int>((units + p.units_per_cta - 1) / p.units_per_cta);
-  xty_gemm_kernel<<<grid, 192, XtyCfg::kSmemBytes, st>>>(tx, ty, p);
+  if (p.colsum_of != 0 && p.colsum_out != nullptr)
+    xty_gemm_kernel<true><<<grid, 320, XtyCfg::kSmemBytes, st>>>(tx, ty, p);
+  else
+    xty_gemm_kernel<false><<<grid, 192, XtyCfg::kSmemBytes, st>>>(tx, ty, p);
   count_launch();
   return post_launch("xty_gemm_kernel");
 }
@@ -489,10 +575,13 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
                                         int m_cols, int n_cols, long long ldx, long long ldy,
                                         float dot_scale, float* M_out, int v_is_f32, void* grad_out,
                                         int grad_is_f32, float grad_scale, int grad_accumulate,
+                                        int colsum_of, float* colsum_out,
                                         void* ws, long long ws_bytes, void* stream) {
   const DeviceState* ds = device_state();
   if (!ds) return GHOST_ERR_DEVICE;
   GB_REQUIRE(X && Y && M_out && ws, "ghost_persample_dot_bf16: null pointer");
+  GB_REQUIRE(colsum_of >= 0 && colsum_of <= 2 && (colsum_of == 0 || colsum_out != nullptr),
+             "ghost_persample_dot_bf16: colsum_of must be 0, 1 (X) or 2 (Y) with an output buffer");
   GB_REQUIRE(n_train > 0, "No training samples to compute dot product, check batch sizes.");
   GB_REQUIRE(n_val > 0 && T > 0 && m_cols > 0 && n_cols > 0, "ghost_persample_dot_bf16: empty dimension");
   GB_REQUIRE(T < (1ll << 31) - 64, "ghost_persample_dot_bf16: T too large");
@@ -512,6 +601,8 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   p.sample_major = 1;
   p.kb_per_split = ceil_div(T, XtyCfg::BK);
   p.v_is_f32 = v_is_f32;
+  p.colsum_of = colsum_of;
+  p.colsum_out = colsum_out;
   p.err = ds->err_word;
   const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
   const int group = persample_group(n_train, n_val, tiles, esize, kPersampleBudget);

@@ -196,9 +196,16 @@ def _backprop_scale(layer: nn.Module) -> float:
     return float(getattr(layer, "_ghost_backprop_scale", 1.0))
 
 
-def _bias_terms(layer: nn.Module, B: torch.Tensor, val_batch_size: int) -> None:
-    """Bias dot products from per-sample column sums of the out-grad (reference :138-146)."""
-    colsums = ops.colsum(B)                       # [N, p] float32, one pass over B
+#: take the bias terms' per-sample column sums of the out-grad inside the per-sample GEMM pass
+#: (extra warps of that kernel) instead of a separate pass over the out-grad
+FUSE_BIAS_COLSUMS = False
+
+
+def _bias_terms(layer: nn.Module, B: torch.Tensor, val_batch_size: int, colsums=None) -> None:
+    """Bias dot products from per-sample column sums of the out-grad (reference :138-146).  The
+    per-sample GEMM pass can hand the sums over; otherwise they take one pass over B."""
+    if colsums is None:
+        colsums = ops.colsum(B)                   # [N, p] float32
     _set_dot(layer.bias, ops.small_gram(colsums, val_batch_size))
     layer._ghost_colsums = colsums               # reused by the bias train gradient
 
@@ -212,6 +219,7 @@ def _dense_dot_product(layer: nn.Module, A: torch.Tensor, B: torch.Tensor, val_b
     A = A.detach()
     B = B.detach()
     _should_use_ghost_computation(layer, A, B, val_batch_size=val_batch_size)
+    colsums = None
     if val_batch_size > 0:
         if layer.use_ghost_computation:
             M = ops.gram_dot(A, B, val_batch_size)
@@ -220,14 +228,20 @@ def _dense_dot_product(layer: nn.Module, A: torch.Tensor, B: torch.Tensor, val_b
             N = A.size(0)
             X, Y = (A, B) if weight_is_in_by_out else (B, A)
             want = bool(getattr(layer.weight, "initially_requires_grad", True))
-            M, grad = ops.persample_dot(X, Y, val_batch_size, want_grad=want,
-                                        grad_scale=_backprop_scale(layer) / n_train,
-                                        grad_dtype=_grad_dtype(layer.weight, A))
+            has_bias = FUSE_BIAS_COLSUMS and getattr(layer, "bias", None) is not None
+            # the out-grad is Y for [d_in, d_out] weights and X for [d_out, d_in] weights
+            res = ops.persample_dot(X, Y, val_batch_size, want_grad=want,
+                                    grad_scale=_backprop_scale(layer) / n_train,
+                                    grad_dtype=_grad_dtype(layer.weight, A),
+                                    colsum_of=("Y" if weight_is_in_by_out else "X") if has_bias else None)
+            M, grad = res[0], res[1]
+            if has_bias:
+                colsums = res[2]
             if want:
                 layer._ghost_cached_train_grad = (A.data_ptr(), B.data_ptr(), N, grad)
         _set_dot(layer.weight, M)
     if getattr(layer, "bias", None) is not None and val_batch_size > 0:
-        _bias_terms(layer, B, val_batch_size)
+        _bias_terms(layer, B, val_batch_size, colsums)
 
 
 def _dense_train_grad(layer: nn.Module, A: torch.Tensor, B: torch.Tensor, val_batch_size: int,

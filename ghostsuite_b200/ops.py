@@ -275,12 +275,14 @@ def wgrad(X: torch.Tensor, Y: torch.Tensor, scale: float, out_dtype: torch.dtype
 
 def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float = 1.0,
                   want_grad: bool = False, grad_scale: float = 1.0,
-                  grad_dtype: Optional[torch.dtype] = None
-                  ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                  grad_dtype: Optional[torch.dtype] = None, colsum_of: Optional[str] = None):
     """Dot-product matrix through explicit per-sample weight gradients kept in tensor memory.
 
     ``X``/``Y``: ``[N, T, cols]``, train first.  Returns ``(M[n_val, n_train], train_grad or None)``
-    with ``train_grad = grad_scale * sum_b X_b^T Y_b`` of shape ``[X cols, Y cols]``.
+    with ``train_grad = grad_scale * sum_b X_b^T Y_b`` of shape ``[X cols, Y cols]``.  With
+    ``colsum_of='X'`` or ``'Y'`` a third value is returned: the per-sample column sums ``[N, cols]``
+    (float32) of that operand, taken inside the GEMM pass, or None when the operands are fp32 (their
+    bf16 hi/lo split is what the kernel sees).
     """
     lib = _lib.load()
     _require_cuda(X, Y)
@@ -304,14 +306,24 @@ def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float
     ws_bytes = int(lib.ghost_persample_workspace_bytes(n_train, n_val, m, n, v_f32))
     off_ws = arena.plan(ws_bytes)
     base = arena.commit()
+    if colsum_of not in (None, "X", "Y"):
+        raise ValueError("colsum_of must be None, 'X' or 'Y'")
+    colsums = None
+    cs_flag = 0
+    if colsum_of is not None and not split:
+        colsums = torch.empty((N, m if colsum_of == "X" else n), dtype=_F32, device=X.device)
+        cs_flag = 1 if colsum_of == "X" else 2
     with _Timed("xty_gemm_kernel+tile_dot_kernel[persample]", "tensor",
                 2.0 * N * T * m * n + 2.0 * n_val * n_train * m * n, 2.0 * N * T * (m + n)):
         xp, yp, ldx, ldy, T_eff = mat(base)
         _lib.check(lib.ghost_persample_dot_bf16(
             xp, yp, n_train, n_val, T_eff, m, n, ldx, ldy, float(dot_scale), M.data_ptr(), v_f32,
             grad.data_ptr() if want_grad else None, _dt_flag(grad) if want_grad else 0,
-            float(grad_scale), 0, base + off_ws, ws_bytes, _stream_ptr()))
-    return M, grad
+            float(grad_scale), 0, cs_flag, colsums.data_ptr() if colsums is not None else None,
+            base + off_ws, ws_bytes, _stream_ptr()))
+    if colsum_of is None:
+        return M, grad
+    return M, grad, colsums
 
 
 # --------------------------------------------------------------------------------------------
@@ -533,21 +545,41 @@ def ce_supported(logits: torch.Tensor) -> bool:
     return logits.stride(1) == 1 and logits.stride(0) % vec == 0 and logits.data_ptr() % 16 == 0
 
 
-def ce_forward(logits: torch.Tensor, targets: torch.Tensor, valid_cols: int, ignore_index: int = -100
-               ) -> Tuple[torch.Tensor, torch.Tensor]:
+def ce_forward(logits: torch.Tensor, targets: torch.Tensor, valid_cols: int, ignore_index: int = -100,
+               grad_scale: Optional[torch.Tensor] = None):
     """Per-row log-sum-exp over the first ``valid_cols`` columns and per-row loss (0 for ignored
-    rows), both float32 ``[rows]``, in one pass over ``logits``."""
+    rows), both float32 ``[rows]``, in one pass over ``logits``.  With ``grad_scale`` (one-element
+    float32 device tensor) the kernel also writes ``grad_scale * (softmax - onehot)`` in the logits'
+    dtype and returns it as a third value."""
     lib = _lib.load()
     _require_cuda(logits, targets)
     rows, cols = logits.shape
     targets = targets.contiguous()
     lse = torch.empty(rows, dtype=_F32, device=logits.device)
     loss_rows = torch.empty(rows, dtype=_F32, device=logits.device)
-    with _Timed("ce_forward_kernel", "hbm", 0.0, float(rows) * valid_cols * logits.element_size()):
+    dlogits = torch.empty((rows, cols), dtype=logits.dtype, device=logits.device) if grad_scale is not None else None
+    nbytes = float(rows) * valid_cols * logits.element_size() * (1.0 if dlogits is None else 2.0)
+    with _Timed("ce_forward_kernel", "hbm", 0.0, nbytes):
         _lib.check(lib.ghost_workload_ce_forward(logits.data_ptr(), _dt_flag(logits), rows, cols, int(valid_cols),
                                                  logits.stride(0), targets.data_ptr(), int(ignore_index),
-                                                 lse.data_ptr(), loss_rows.data_ptr(), _stream_ptr()))
-    return lse, loss_rows
+                                                 lse.data_ptr(), loss_rows.data_ptr(),
+                                                 grad_scale.data_ptr() if grad_scale is not None else None,
+                                                 dlogits.data_ptr() if dlogits is not None else None,
+                                                 _stream_ptr()))
+    if grad_scale is None:
+        return lse, loss_rows
+    return lse, loss_rows, dlogits
+
+
+def ce_rescale_(dlogits: torch.Tensor, upstream: torch.Tensor) -> torch.Tensor:
+    """``dlogits *= upstream[0]`` in place; the kernel returns at once when the factor is exactly 1."""
+    lib = _lib.load()
+    _require_cuda(dlogits, upstream)
+    rows, cols = dlogits.shape
+    with _Timed("ce_rescale_kernel", "hbm", 0.0, 0.0):
+        _lib.check(lib.ghost_workload_ce_rescale(dlogits.data_ptr(), _dt_flag(dlogits), rows, cols,
+                                                 upstream.data_ptr(), _stream_ptr()))
+    return dlogits
 
 
 def ce_backward(logits: torch.Tensor, targets: torch.Tensor, valid_cols: int, lse: torch.Tensor,

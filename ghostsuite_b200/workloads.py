@@ -34,23 +34,43 @@ except Exception:  # pragma: no cover - transformers is part of the supported en
 
 
 class _FusedTokenLoss(torch.autograd.Function):
-    """Mean next-token cross-entropy over the first ``valid_cols`` logit columns from two streaming
-    kernels (``ops.ce_forward`` / ``ops.ce_backward``): the logits are read once in the forward,
-    once more in the backward, and the gradient is written once, in the logits' dtype.  The usual
-    fp32-copy + log-softmax formulation moves the tensor through HBM about ten times."""
+    """Mean next-token cross-entropy over the first ``valid_cols`` logit columns from the library's
+    streaming kernels.  When the logits need a gradient and their rows are dense, the forward kernel
+    reads them once from HBM and also writes the gradient for an upstream gradient of 1 (in the
+    logits' dtype); the backward only rescales it in place, a no-op for ``loss.backward()``.
+    Otherwise the gradient comes from a second kernel in the backward.  The usual fp32-copy +
+    log-softmax formulation moves the tensor through HBM about ten times."""
 
     @staticmethod
     def forward(ctx, logits2d, target, valid_cols):
         from . import ops
-        lse, loss_rows = ops.ce_forward(logits2d, target, valid_cols)
         n_valid = (target != -100).sum().to(torch.float32)
-        ctx.save_for_backward(logits2d, target, lse, n_valid)
+        vec = 8 if logits2d.dtype == torch.bfloat16 else 4
+        fuse = ctx.needs_input_grad[0] and logits2d.shape[1] % vec == 0
         ctx.valid_cols = valid_cols
+        ctx.fused = fuse
+        if fuse:
+            inv = (1.0 / n_valid).reshape(1)
+            _, loss_rows, dlogits = ops.ce_forward(logits2d, target, valid_cols, grad_scale=inv)
+            # kept on the context, not through save_for_backward: both are updated in place by the
+            # backward.  `applied` is the factor already folded into dlogits, so that a second
+            # backward through a retained graph rescales by the ratio, not by the upstream again
+            ctx.dlogits = dlogits
+            ctx.applied = torch.ones(1, dtype=torch.float32, device=dlogits.device)
+        else:
+            lse, loss_rows = ops.ce_forward(logits2d, target, valid_cols)
+            ctx.save_for_backward(logits2d, target, lse, n_valid)
         return loss_rows.sum() / n_valid
 
     @staticmethod
     def backward(ctx, grad_out):
         from . import ops
+        if ctx.fused:
+            dlogits, applied = ctx.dlogits, ctx.applied
+            up = grad_out.to(torch.float32).reshape(1)
+            factor = up / applied
+            applied.copy_(up)
+            return ops.ce_rescale_(dlogits, factor), None, None
         logits2d, target, lse, n_valid = ctx.saved_tensors
         scale = (grad_out.to(torch.float32) / n_valid).reshape(1).contiguous()
         return ops.ce_backward(logits2d, target, ctx.valid_cols, lse, scale), None, None

@@ -103,11 +103,16 @@ long long ghost_persample_workspace_bytes(int n_train, int n_val, int m_cols, in
 /* Upper bound on that workspace (default 6 GiB); smaller values make the train samples go through
  * in more, smaller groups.  Process-wide; set it before sizing workspaces. */
 int ghost_set_persample_budget_bytes(long long bytes);
+/* colsum_of = 1 (X) or 2 (Y) also writes the per-sample column sums of that operand,
+ * colsum_out[s, c] = sum_t operand[s, t, c] (fp32, [n_train + n_val, cols]): the bias terms of
+ * ghostEngines/supported_layers_grad_samplers_dotprod.py:138-146, 454-471 without a second pass over
+ * the out-grad (four extra warps read the operand stages the MMAs consume).  Only meaningful when
+ * the operand holds the values themselves (not the hi/lo split of fp32 data); 0 = off. */
 int ghost_persample_dot_bf16(const void* X, const void* Y, int n_train, int n_val, long long T,
                              int m_cols, int n_cols, long long ldx, long long ldy, float dot_scale,
                              float* M_out, int v_is_f32, void* grad_out, int grad_is_f32,
-                             float grad_scale, int grad_accumulate, void* ws, long long ws_bytes,
-                             void* stream);
+                             float grad_scale, int grad_accumulate, int colsum_of, float* colsum_out,
+                             void* ws, long long ws_bytes, void* stream);
 
 /* ---- bias / LayerNorm / small reductions ------------------------------------------------------- */
 /* out[n, c] = sum_t G[n, t, c]  (fp32).  Replaces the token sums of
@@ -192,7 +197,13 @@ int ghost_gradproj_dense_bf16(const void* G, const void* A, int B, long long T, 
  * whose models take their loss from torch ops. */
 int ghost_workload_ce_forward(const void* logits, int is_f32, long long rows, int cols, int cols_valid,
                               long long ld, const long long* targets, long long ignore_index, float* lse,
-                              float* loss_rows, void* stream);
+                              float* loss_rows, const float* scale, void* dlogits, void* stream);
+/* With dlogits != NULL the forward also writes scale[0] * (softmax - onehot) as dense [rows, cols]
+ * (the gradient for an upstream gradient of 1 when scale = 1 / counted rows): its second pass over a
+ * row hits L2.  ghost_workload_ce_rescale then multiplies by the actual upstream gradient in place
+ * and returns at once when that is exactly 1. */
+int ghost_workload_ce_rescale(void* dlogits, int is_f32, long long rows, int cols, const float* upstream,
+                              void* stream);
 int ghost_workload_ce_backward(const void* logits, int is_f32, long long rows, int cols, int cols_valid,
                                long long ld, const long long* targets, long long ignore_index,
                                const float* lse, const float* scale, void* dlogits, long long ld_out,

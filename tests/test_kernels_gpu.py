@@ -149,6 +149,24 @@ def test_persample_dot(case, dtype):
     assert O.rel_fro(M, M2.cpu()) < TOL[dtype]
 
 
+@pytest.mark.parametrize("case", [(5, 3, 6, 16, 24), (3, 1, 130, 72, 40), (2, 2, 300, 200, 136), (9, 4, 70, 264, 520)])
+@pytest.mark.parametrize("which", ["X", "Y"])
+def test_persample_dot_column_sums(case, which):
+    """Per-sample column sums of one operand taken inside the GEMM pass (the bias terms)."""
+    n_t, n_v, T, d, p = case
+    A, G = make(n_t + n_v, T, d, p, torch.bfloat16, seed=13)
+    M, grad, cs = ops().persample_dot(G.cuda(), A.cuda(), n_v, want_grad=True, grad_scale=1.0,
+                                      grad_dtype=torch.float32, colsum_of=which)
+    after()
+    src = G if which == "X" else A
+    assert cs.shape == (n_t + n_v, src.shape[-1])
+    assert O.rel_fro(cs, src.double().sum(1)) < 1e-5
+    assert O.rel_fro(M, O.linear_dot_exact(A, G, n_v)) < 2e-2
+    # fp32 operands reach the kernel as a bf16 hi/lo split: no fused sums
+    res = ops().persample_dot(G.float().cuda(), A.float().cuda(), n_v, colsum_of=which)
+    assert res[2] is None
+
+
 @pytest.mark.parametrize("sizes", [(37, 11, 70, 136, 264), (70, 35, 12, 72, 264)])
 def test_persample_dot_in_groups(sizes):
     """A small workspace budget forces the train samples through in several groups (and several
@@ -162,11 +180,12 @@ def test_persample_dot_in_groups(sizes):
     try:
         for budget in (6 << 30, 2 << 20):
             _lib.check(lib.ghost_set_persample_budget_bytes(budget))
-            M, grad = ops().persample_dot(G.cuda(), A.cuda(), n_v, want_grad=True, grad_scale=1.0,
-                                          grad_dtype=torch.float32)
+            M, grad, cs = ops().persample_dot(G.cuda(), A.cuda(), n_v, want_grad=True, grad_scale=1.0,
+                                              grad_dtype=torch.float32, colsum_of="X")
             after()
             assert O.rel_fro(M, ref) < 2e-2
             assert O.rel_fro(grad, gref) < 1e-2
+            assert O.rel_fro(cs, G.double().sum(1)) < 1e-5
     finally:
         _lib.check(lib.ghost_set_persample_budget_bytes(6 << 30))
 
@@ -340,6 +359,17 @@ def test_fused_token_loss_matches_torch(shape, dtype):
     assert (got - want).norm() <= tol * want.norm()
     assert torch.count_nonzero(got[:, valid:]) == 0
     assert torch.count_nonzero(got[::7]) == 0
+    # a retained graph backpropagated twice with different upstream gradients
+    x2 = logits.detach().clone().requires_grad_(True)
+    loss2 = _FusedTokenLoss.apply(x2, target, valid)
+    loss2.backward(retain_graph=True)
+    g1 = x2.grad.float().clone()
+    x2.grad = None
+    (loss2 * 0.25).backward()
+    assert (g1 * 1.7 - want).norm() <= tol * want.norm()
+    assert (x2.grad.float() * 4 * 1.7 - want).norm() <= tol * want.norm()
+    # logits that need no gradient take the forward-only kernel
+    assert abs(_FusedTokenLoss.apply(logits.detach(), target, valid).item() - ref.item()) <= 2e-5 * max(1.0, abs(ref.item()))
 
 
 @pytest.mark.gpu
