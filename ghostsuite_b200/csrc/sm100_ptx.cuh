@@ -91,22 +91,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // `target`.  Same give-up protocol as mbar_wait.
 __device__ __forceinline__ bool counter_wait(volatile int* counter, int target, volatile int* abort_flag,
                                              int* err, int code) {
-#pragma unroll 1
-  for (int i = 0; i < 256; ++i)
-    if (*counter > target) return true;
+  if (*counter > target) return true;
+  // Sleep between polls: a spinning warp would take issue slots from the single threads that drive
+  // the pipeline on the same scheduler.
   const unsigned long long t0 = globaltimer_ns();
 #pragma unroll 1
   while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (*counter > target) return true;
+    __nanosleep(200);
+    if (*counter > target) return true;
     if (*abort_flag) return false;
     if (globaltimer_ns() - t0 > kWaitLimitNs) {
       *abort_flag = 1;
       atomicCAS(err, 0, code);
       return false;
     }
-    __nanosleep(64);
   }
 }
 

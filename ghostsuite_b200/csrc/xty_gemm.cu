@@ -216,7 +216,9 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             for (int j = 0; j < BN / 64; ++j)
               tma_load_3d(st + BM * BK * 2 + j * (BK * 128), &tm_y, &full_bar[stage], n0 + j * 64, row, z);
           }
-          if (kColsum) { __threadfence_block(); *issued = ++n_issued; }
+          // progress counter for the column-sum warps (they only look at it for summed units; no
+          // fence: they need no more than that every earlier phase of the stage is over)
+          if (kColsum) { ++n_issued; if (summed) *issued = n_issued; }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
