@@ -221,6 +221,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     engine = GradDotProdEngine(module=model, val_batch_size=N_VAL, loss_reduction="mean", use_dummy_bias=True)
     engine.attach(opt)
     group = dist.group.WORLD if world > 1 else None
+    if world > 1:
+        gdist.overlap_train_grad_sync(engine, group)      # buckets of finished gradients go out during backward
 
     g = torch.Generator().manual_seed(1)
     val_ids = torch.randint(0, 50257, (N_VAL, SEQ), generator=g)              # replicated

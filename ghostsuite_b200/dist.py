@@ -6,7 +6,8 @@ runs forward/backward on ``cat(train_shard, val)``; afterwards
 * the per-parameter dot-product blocks ``[n_val, n_train_local]`` are packed into one buffer and
   all-gathered (a few hundred KB), giving every rank the ``[n_val, n_train_global]`` matrices;
 * the recovered train gradients (each the mean over the rank's own shard) are all-reduced in
-  flat buckets and averaged.
+  flat buckets and averaged -- after the backward pass (:func:`allreduce_train_grads`) or, with
+  :func:`overlap_train_grad_sync`, bucket by bucket while the backward pass is still running.
 
 With a ``mean`` loss every rank divides by its local batch size, so a local out-grad is
 ``N_global / N_local`` times what a single process over the global batch would see; dot products
@@ -68,10 +69,11 @@ def gather_dot_products(module: torch.nn.Module, group=None,
         n_local = n_val + n_loc
         n_global = n_val + world * n_loc
         full = full * (float(n_local) / float(n_global)) ** 2
+    vectors = full.sum(dim=1)                      # one reduction for all parameters
     out = {}
     for i, (name, p) in enumerate(named):
         p.grad_dot_prod_matrix = full[i]
-        p.grad_dot_prod = full[i].sum(dim=0)
+        p.grad_dot_prod = vectors[i]
         out[name] = full[i]
     return out
 
@@ -113,7 +115,113 @@ def allreduce_train_grads(module: torch.nn.Module, group=None, bucket_bytes: int
     return calls
 
 
+class OverlappedGradSync:
+    """All-reduce of the train gradients started bucket by bucket while the backward pass is still
+    running.
+
+    The hooks report every contribution to ``param.train_grad``; a parameter is final once all the
+    hooked layers that own it have reported (a tied table gets two contributions).  Final gradients
+    are collected into a bucket; a full bucket is flattened and all-reduced asynchronously (NCCL on
+    its own stream), and :meth:`finish` flushes the rest, waits and copies the averages back.  The
+    order in which parameters become final is the backward order, identical on every rank.
+    """
+
+    def __init__(self, module: torch.nn.Module, group=None, bucket_bytes: int = 32 << 20):
+        from .ghostEngines import supported_layers_grad_samplers_dotprod as layers
+        self._layers = layers
+        self.module = module
+        self.group = group
+        self.bucket_bytes = int(bucket_bytes)
+        self.world = dist.get_world_size(group)
+        self.avg_op = dist.ReduceOp.AVG if dist.get_backend(group) == "nccl" else dist.ReduceOp.SUM
+        # number of hooked layers contributing to each parameter
+        self.expected: Dict[int, int] = {}
+        for layer in module.modules():
+            if type(layer) in layers._supported_layers_dotprod:
+                for prm in layer.parameters(recurse=False):
+                    if getattr(prm, "initially_requires_grad", prm.requires_grad):
+                        self.expected[id(prm)] = self.expected.get(id(prm), 0) + 1
+        self._seen: Dict[int, int] = {}
+        self._bucket: List[torch.Tensor] = []
+        self._bucket_size = 0
+        self._bucket_dtype = None
+        self._inflight: List[Tuple[object, torch.Tensor, List[torch.Tensor]]] = []
+        self._reduced: set = set()
+        layers.TRAIN_GRAD_OBSERVER = self._on_train_grad
+
+    def close(self) -> None:
+        if self._layers.TRAIN_GRAD_OBSERVER == self._on_train_grad:
+            self._layers.TRAIN_GRAD_OBSERVER = None
+
+    # ------------------------------------------------------------------ during backward
+    def _on_train_grad(self, param: torch.Tensor) -> None:
+        key = id(param)
+        if key not in self.expected:
+            return
+        seen = self._seen.get(key, 0) + 1
+        self._seen[key] = seen
+        if seen < self.expected[key]:
+            return                                   # another layer still adds to this gradient
+        g = param.train_grad
+        if self._bucket and g.dtype != self._bucket_dtype:
+            self._flush()
+        self._bucket.append(g)
+        self._bucket_dtype = g.dtype
+        self._bucket_size += g.numel() * g.element_size()
+        self._reduced.add(key)
+        if self._bucket_size >= self.bucket_bytes:
+            self._flush()
+
+    def _flush(self) -> None:
+        if not self._bucket:
+            return
+        grads = self._bucket
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        work = dist.all_reduce(flat, op=self.avg_op, group=self.group, async_op=True)
+        self._inflight.append((work, flat, grads))
+        self._bucket, self._bucket_size, self._bucket_dtype = [], 0, None
+
+    # ------------------------------------------------------------------ after backward
+    def finish(self) -> int:
+        """Flush, wait for every bucket, write the averages back.  Gradients that never reported
+        (parameters of layers without hooks) are averaged here in one more bucket.  Returns the
+        number of collectives of this pass."""
+        for _, prm in self.module.named_parameters():
+            g = getattr(prm, "train_grad", None)
+            if g is not None and id(prm) not in self._reduced:
+                if self._bucket and g.dtype != self._bucket_dtype:
+                    self._flush()
+                self._bucket.append(g)
+                self._bucket_dtype = g.dtype
+                self._bucket_size += g.numel() * g.element_size()
+                self._reduced.add(id(prm))
+        self._flush()
+        calls = len(self._inflight)
+        for work, flat, grads in self._inflight:
+            work.wait()
+            if self.avg_op == dist.ReduceOp.SUM:
+                flat.mul_(1.0 / self.world)
+            pieces = flat.split([g.numel() for g in grads])
+            torch._foreach_copy_(grads, [pc.view_as(g) for pc, g in zip(pieces, grads)])
+        self._inflight.clear()
+        self._seen.clear()
+        self._reduced.clear()
+        return calls
+
+
+def overlap_train_grad_sync(engine, group=None, bucket_bytes: int = 32 << 20) -> OverlappedGradSync:
+    """Start all-reducing finished train gradients during the backward pass; :func:`sync_engine`
+    then only has to wait for them.  Call once after ``engine.attach``."""
+    sync = OverlappedGradSync(engine.module, group, bucket_bytes)
+    engine._ghost_grad_sync = sync
+    return sync
+
+
 def sync_engine(engine, group=None, single_process_equivalent: bool = True) -> None:
     """Call between ``loss.backward()`` and ``engine.prepare_gradients()`` on every rank."""
     gather_dot_products(engine.module, group, single_process_equivalent)
-    allreduce_train_grads(engine.module, group)
+    overlapped = getattr(engine, "_ghost_grad_sync", None)
+    if overlapped is not None:
+        overlapped.finish()
+    else:
+        allreduce_train_grads(engine.module, group)

@@ -101,6 +101,12 @@ def _should_use_ghost_computation(layer: nn.Module, A: torch.Tensor, B: torch.Te
     layer.use_ghost_computation = bool(gram <= per)
 
 
+#: optional observer ``fn(param)`` called every time a layer has added its contribution to
+#: ``param.train_grad`` (the data-parallel layer uses it to start all-reducing finished gradients
+#: while the backward pass is still running)
+TRAIN_GRAD_OBSERVER = None
+
+
 def _create_or_accumulate_train_grad(param: torch.Tensor, grad: torch.Tensor) -> None:
     """``param.train_grad`` is created on first use and added to afterwards (reference :44-69)."""
     assert grad.shape == param.shape, \
@@ -110,6 +116,8 @@ def _create_or_accumulate_train_grad(param: torch.Tensor, grad: torch.Tensor) ->
         param.train_grad.add_(grad)
     else:
         param.train_grad = grad
+    if TRAIN_GRAD_OBSERVER is not None:
+        TRAIN_GRAD_OBSERVER(param)
 
 
 # While a backward hook runs, the [n_train] vectors are not reduced one launch per parameter: the

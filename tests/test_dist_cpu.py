@@ -20,7 +20,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, overlap=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -52,7 +52,16 @@ def _worker(rank, world, port, q):
 
         class E:
             module = model
+        if overlap:
+            # the hooks of the CUDA engine report every finished train gradient in backward order;
+            # tiny buckets force several collectives
+            sync = gdist.overlap_train_grad_sync(E, None, bucket_bytes=256)
+            for p in reversed(list(model.parameters())):
+                sync._on_train_grad(p)
+            assert len(sync._inflight) >= 1              # something went out before finish()
         gdist.sync_engine(E, None)
+        if overlap:
+            sync.close()
         ok = True
         for (name, p), (_, r) in zip(model.named_parameters(), ref.named_parameters()):
             m_err = (p.grad_dot_prod_matrix.double() - r.grad_dot_prod_matrix).norm() / r.grad_dot_prod_matrix.norm()
@@ -65,11 +74,12 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_sharded_run_reproduces_single_process_numbers():
+@pytest.mark.parametrize("overlap", [False, True])
+def test_sharded_run_reproduces_single_process_numbers(overlap):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, overlap)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=60) for _ in procs]
