@@ -46,8 +46,11 @@ struct GpCfg {
   static constexpr int kActAtomBytes = BM * BK * 2;
   static constexpr int kProjAtomBytes = KMAX * BK * 2;
   static constexpr int kStageBytes = ATOMS * (kActAtomBytes + kProjAtomBytes);
-  static constexpr int kStages = (KMAX == 32) ? 4 : 3;     // fills the 227 KB of shared memory
-  static constexpr int kProjBytes = 2 * BM * KMAX * 4;     // fp32 staging of both projected blocks
+  // The pipeline is bound by how many bytes are in flight per SM, so the fp32 staging of the
+  // projected blocks is kept to half a tile (64 tokens at a time) and the rest goes to stages.
+  static constexpr int kStageRows = 64;
+  static constexpr int kProjBytes = 2 * kStageRows * KMAX * 4;
+  static constexpr int kStages = (KMAX == 32) ? 5 : (KMAX == 64 ? 4 : 5);     // fills the 227 KB of shared memory
   static constexpr int kSmemBytes = kStages * kStageBytes + kProjBytes + 1024 + 256;
   static constexpr int RT = KMAX / 16;   // output rows per thread (16 thread rows)
   static constexpr int CT = KMAX / 8;    // output cols per thread (8 thread cols)
@@ -72,8 +75,8 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* s_r = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);   // [128][KMAX]
-  float* s_c = s_r + BM * KMAX;                                               // [128][KMAX]
+  float* s_r = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);   // [64][KMAX]
+  float* s_c = s_r + Cfg::kStageRows * KMAX;                                  // [64][KMAX]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kProjBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
@@ -205,7 +208,7 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           if (c0 + j < KMAX)
-            *reinterpret_cast<float4*>(&dst[gp_staged_index<KMAX>(tid, c0 + j)]) =
+            *reinterpret_cast<float4*>(&dst[gp_staged_index<KMAX>(tid & 63, c0 + j)]) =
                 make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
       }
     };
@@ -217,33 +220,39 @@ gradproj_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant_
       if (!named_bar_and(2, 128, mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.err, 124))) { alive = false; break; }
       tc_fence_after_sync();
       const uint32_t t_r = tmem_base + lane_base + acc * 256;
-      stage_block(t_r, p.kr_pad, s_r);
-      stage_block(t_r + 128, p.kc_pad, s_c);
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-      asm volatile("bar.sync 1, 128;" ::: "memory");     // the four epilogue warps only
-      // out[r, c] += sum_t s_r[t][r] * s_c[t][c]
-#pragma unroll 4
-      for (int t = 0; t < BM; ++t) {
-        float rr[RT], cc[CT];
-        if constexpr (RT >= 4) {
-#pragma unroll
-          for (int i = 0; i < RT; i += 4)
-            *reinterpret_cast<float4*>(&rr[i]) = *reinterpret_cast<const float4*>(&s_r[gp_staged_index<KMAX>(t, ty * RT + i)]);
-        } else {
-          *reinterpret_cast<float2*>(&rr[0]) = *reinterpret_cast<const float2*>(&s_r[gp_staged_index<KMAX>(t, ty * RT)]);
+      // two halves of 64 tokens: warps 0-1 own TMEM lanes 0-63, warps 2-3 lanes 64-127
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        if ((warp >> 1) == half) {
+          stage_block(t_r, p.kr_pad, s_r);
+          stage_block(t_r + 128, p.kc_pad, s_c);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[acc]);     // four arrivals per tile, one per warp
         }
+        asm volatile("bar.sync 1, 128;" ::: "memory");     // the four epilogue warps only
+        // out[r, c] += sum_t s_r[t][r] * s_c[t][c]
+#pragma unroll 4
+        for (int t = 0; t < Cfg::kStageRows; ++t) {
+          float rr[RT], cc[CT];
+          if constexpr (RT >= 4) {
 #pragma unroll
-        for (int j = 0; j < CT; j += 4)
-          *reinterpret_cast<float4*>(&cc[j]) = *reinterpret_cast<const float4*>(&s_c[gp_staged_index<KMAX>(t, tx * CT + j)]);
+            for (int i = 0; i < RT; i += 4)
+              *reinterpret_cast<float4*>(&rr[i]) = *reinterpret_cast<const float4*>(&s_r[gp_staged_index<KMAX>(t, ty * RT + i)]);
+          } else {
+            *reinterpret_cast<float2*>(&rr[0]) = *reinterpret_cast<const float2*>(&s_r[gp_staged_index<KMAX>(t, ty * RT)]);
+          }
 #pragma unroll
-        for (int i = 0; i < RT; ++i)
+          for (int j = 0; j < CT; j += 4)
+            *reinterpret_cast<float4*>(&cc[j]) = *reinterpret_cast<const float4*>(&s_c[gp_staged_index<KMAX>(t, tx * CT + j)]);
 #pragma unroll
-          for (int j = 0; j < CT; ++j) o[i][j] = fmaf(rr[i], cc[j], o[i][j]);
+          for (int i = 0; i < RT; ++i)
+#pragma unroll
+            for (int j = 0; j < CT; ++j) o[i][j] = fmaf(rr[i], cc[j], o[i][j]);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (alive && cur_b >= 0) flush(cur_b);
   }
