@@ -31,6 +31,8 @@ PROTOTYPES = {
     "ghost_cast_split_bf16": (_i, [_vp, _i, _ll, _ll, _i, _ll, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp]),
     "ghost_gram_dot_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _ll, _i, _i, _ll, _ll, _ll, _ll, _i, _f, _vp, _vp]),
     "ghost_set_gram_pair_mode": (_i, [_i]),
+    "ghost_set_persample_pair_mode": (_i, [_i]),
+    "ghost_set_wgrad_pair_mode": (_i, [_i]),
     "ghost_wgrad_workspace_bytes": (_ll, [_i, _i]),
     "ghost_wgrad_bf16": (_i, [_vp, _vp, _ll, _i, _i, _ll, _ll, _f, _i, _vp, _i, _vp, _ll, _vp]),
     "ghost_persample_workspace_bytes": (_ll, [_i, _i, _i, _i, _i]),

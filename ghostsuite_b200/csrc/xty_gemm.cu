@@ -431,6 +431,15 @@ __global__ void xty_finalize_kernel(const float* __restrict__ ws, long long ld_w
   }
 }
 
+// CTA-pair variant of the tile-store pass (xty_gemm_pair.cu)
+int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_total, long long T, int m_cols,
+                          int n_cols, long long ldx, long long ldy, int samples, int sample0, void* vgrad,
+                          int v_is_f32, const DeviceState* ds, cudaStream_t st);
+int launch_xty_pair_wgrad(const void* X, const void* Y, long long n_rows, int m_cols, int n_cols, long long ldx,
+                          long long ldy, float* acc_ws, long long ld_acc, const DeviceState* ds, cudaStream_t st);
+static int g_wgrad_pair_mode = 0;      // same meaning as below
+static int g_persample_pair_mode = 1;  // 0 off, 1 where no half of a pair would idle, 2 wherever applicable
+
 // Operand maps: the blocked form (one TMA instruction per operand and stage) when the column count
 // is a multiple of 64, else one box per 64 columns with the tail zero-filled by the bounds check.
 static int make_xty_maps(CUtensorMap* tx, CUtensorMap* ty, XtyParams& p, const void* X, const void* Y,
@@ -485,6 +494,20 @@ using namespace gb;
 
 static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
 
+// a pair covers two 128-row tiles of X's columns: with an odd tile count the last pair's second CTA
+// idles, which costs more than the pair saves unless there are many tiles
+static bool pair_kernel_fits(int mode, int m_cols, int n_cols) {
+  if (mode == 0 || m_cols % 64 != 0 || n_cols % 64 != 0) return false;
+  const int m_tiles128 = (m_cols + 127) / 128;
+  return mode == 2 || m_tiles128 % 2 == 0 || m_tiles128 >= 15;
+}
+
+extern "C" int ghost_set_wgrad_pair_mode(int mode) {
+  if (mode < 0 || mode > 2) return GHOST_ERR_INVALID;
+  g_wgrad_pair_mode = mode;
+  return GHOST_OK;
+}
+
 extern "C" long long ghost_wgrad_workspace_bytes(int m_cols, int n_cols) {
   return static_cast<long long>(m_cols) * round_up(n_cols, 4) * 4;
 }
@@ -531,7 +554,11 @@ extern "C" int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, 
   int rc;
   if ((rc = make_xty_maps(&tx, &ty, p, X, Y, 1, n_rows, ldx, ldy)) != GHOST_OK) return rc;
   GB_CUDA_OK(cudaMemsetAsync(ws, 0, static_cast<size_t>(m_cols) * p.ld_acc * 4, st));
-  if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+  if (pair_kernel_fits(g_wgrad_pair_mode, m_cols, n_cols) && p.blocked_x && p.blocked_y && ds->sm_count >= 2)
+    rc = launch_xty_pair_wgrad(X, Y, n_rows, m_cols, n_cols, ldx, ldy, p.acc_ws, p.ld_acc, ds, st);
+  else
+    rc = launch_xty(tx, ty, p, ds, st);
+  if (rc != GHOST_OK) return rc;
   return finalize_xty(p.acc_ws, p.ld_acc, out, out_is_f32, m_cols, n_cols, scale, accumulate, st);
 }
 
@@ -571,6 +598,12 @@ extern "C" long long ghost_persample_workspace_bytes(int n_train, int n_val, int
 }
 
 // Per-sample-gradient path.  X, Y: [n_train + n_val, T, cols] (train first).  Produces
+extern "C" int ghost_set_persample_pair_mode(int mode) {
+  if (mode < 0 || mode > 2) return GHOST_ERR_INVALID;
+  g_persample_pair_mode = mode;
+  return GHOST_OK;
+}
+
 // M[v, b] = dot_scale * <X_v^T Y_v, X_b^T Y_b> and, if grad_out != null, the train gradient
 // grad_scale * sum_b X_b^T Y_b (written or accumulated, cast to the parameter dtype).
 extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_train, int n_val, long long T,
@@ -616,13 +649,22 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   const long long N = static_cast<long long>(n_train) + n_val;
   if ((rc = make_xty_maps(&tx, &ty, p, X, Y, N, T, ldx, ldy)) != GHOST_OK) return rc;
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
+  // tile pass: the CTA-pair kernel when it is selected and applicable, else the single-CTA kernel
+  const bool use_pair = pair_kernel_fits(g_persample_pair_mode, m_cols, n_cols) && p.blocked_x && p.blocked_y &&
+                        colsum_of == 0 && ds->sm_count >= 2;
+  auto tile_pass = [&](const XtyParams& q) -> int {
+    if (use_pair)
+      return launch_xty_pair_tiles(X, Y, N, T, m_cols, n_cols, ldx, ldy, q.samples, q.sample0, q.vgrad,
+                                   v_is_f32, ds, st);
+    return launch_xty(tx, ty, q, ds, st);
+  };
   if (group == n_train) {
     // everything fits: one GEMM pass over all samples (train first, validation last) into one
     // [tile][N][32768] buffer, one streaming pass over it
     p.samples = static_cast<int>(N);
     p.sample0 = 0;
     p.vgrad = vws;
-    if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+    if ((rc = tile_pass(p)) != GHOST_OK) return rc;
     // With a single group the streaming kernel can write the train gradient itself (scaled, in the
     // parameter dtype): no fp32 sum buffer, no finalize pass.  A bf16 output is only written
     // directly when one 32-sample block covers the batch, so it is rounded once.
@@ -639,13 +681,13 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
     p.samples = n_val;
     p.sample0 = n_train;
     p.vgrad = vws;
-    if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+    if ((rc = tile_pass(p)) != GHOST_OK) return rc;
     for (int b0 = 0; b0 < n_train; b0 += group) {
       const int g = (n_train - b0 < group) ? n_train - b0 : group;
       p.samples = g;
       p.sample0 = b0;
       p.vgrad = wws;
-      if ((rc = launch_xty(tx, ty, p, ds, st)) != GHOST_OK) return rc;
+      if ((rc = tile_pass(p)) != GHOST_OK) return rc;
       if ((rc = launch_tile_dot(vws, n_val, 0, wws, g, v_is_f32, tiles, n_val, g, b0, n_train, dot_scale,
                                 M_out, grad_out ? sum : nullptr, b0 == 0 ? 1 : 0, nullptr, 0, 0, m_cols,
                                 n_cols, p.n_tiles, 1.f, ds, st)) != GHOST_OK)

@@ -103,6 +103,13 @@ long long ghost_persample_workspace_bytes(int n_train, int n_val, int m_cols, in
 /* Upper bound on that workspace (default 6 GiB); smaller values make the train samples go through
  * in more, smaller groups.  Process-wide; set it before sizing workspaces. */
 int ghost_set_persample_budget_bytes(long long bytes);
+/* Selects the kernel of the tile pass: 0 = one CTA per 128 x 256 tile; 1 (default) = a CTA pair
+ * (tcgen05 cta_group::2) per 256 x 256 block when both operands have column counts that are
+ * multiples of 64 and X's 128-column tile count is even or at least 15; 2 = the pair kernel
+ * whenever the column counts allow it.  Both kernels store identical tiles.  Process-wide. */
+int ghost_set_persample_pair_mode(int mode);
+/* The same choice for ghost_wgrad_bf16's split-K pass (modes 0 / 1 / 2 as above; default 0). */
+int ghost_set_wgrad_pair_mode(int mode);
 /* colsum_of = 1 (X) or 2 (Y) also writes the per-sample column sums of that operand,
  * colsum_out[s, c] = sum_t operand[s, t, c] (fp32, [n_train + n_val, cols]): the bias terms of
  * ghostEngines/supported_layers_grad_samplers_dotprod.py:138-146, 454-471 without a second pass over

@@ -119,6 +119,28 @@ def test_wgrad(case, dtype):
     assert O.rel_fro(out, ref2) < (1e-4 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("case", [(70, 64, 128), (130 * 3, 192, 320), (2700, 448, 64), (5000, 768, 1024),
+                                  (64 * 300, 128, 384), (9, 64, 64)])
+def test_wgrad_cta_pair_kernel(case):
+    """The CTA-pair split-K pass (mode 2: wherever the column counts are multiples of 64, odd tile
+    counts included) against the single-CTA pass and the fp64 contraction."""
+    from ghostsuite_b200 import _lib
+    lib = _lib.load()
+    rows, d, p = case
+    A, G = make(1, rows, d, p, torch.bfloat16, seed=23)
+    ref = torch.einsum("btp,btd->pd", G.double(), A.double())
+    res = {}
+    try:
+        for mode in (0, 2):
+            _lib.check(lib.ghost_set_wgrad_pair_mode(mode))
+            res[mode] = ops().wgrad(G.cuda(), A.cuda(), 1.0, torch.float32)
+            after()
+    finally:
+        _lib.check(lib.ghost_set_wgrad_pair_mode(0))
+    assert O.rel_fro(res[2], ref) < 1e-2
+    assert O.rel_fro(res[2], res[0].cpu()) < 1e-5      # same products, another order of fp32 additions
+
+
 def test_wgrad_accumulate():
     A, G = make(6, 40, 64, 48, torch.bfloat16, seed=5)
     o = ops()
@@ -188,6 +210,34 @@ def test_persample_dot_in_groups(sizes):
             assert O.rel_fro(cs, G.double().sum(1)) < 1e-5
     finally:
         _lib.check(lib.ghost_set_persample_budget_bytes(6 << 30))
+
+
+@pytest.mark.parametrize("case", [(5, 3, 70, 64, 128), (3, 1, 130, 192, 320), (9, 4, 300, 448, 64),
+                                  (4, 2, 64, 768, 1024), (33, 20, 9, 64, 256), (37, 11, 70, 128, 384)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_persample_dot_cta_pair_kernel(case, dtype):
+    """The CTA-pair tile pass (mode 2: wherever the column counts allow it, odd tile counts and
+    several train groups included) stores the same tiles as the single-CTA pass: identical train
+    gradient, and dot products equal up to the order of the fp32 additions."""
+    from ghostsuite_b200 import _lib
+    lib = _lib.load()
+    n_t, n_v, T, d, p = case
+    A, G = make(n_t + n_v, T, d, p, dtype, seed=17)
+    res = {}
+    try:
+        _lib.check(lib.ghost_set_persample_budget_bytes(8 << 20))
+        for mode in (0, 2):
+            _lib.check(lib.ghost_set_persample_pair_mode(mode))
+            res[mode] = ops().persample_dot(G.cuda(), A.cuda(), n_v, want_grad=True, grad_scale=1.0,
+                                            grad_dtype=torch.float32)[:2]
+            after()
+    finally:
+        _lib.check(lib.ghost_set_persample_pair_mode(1))
+        _lib.check(lib.ghost_set_persample_budget_bytes(6 << 30))
+    assert torch.equal(res[0][1], res[2][1])
+    assert O.rel_fro(res[2][0], res[0][0].cpu()) < 1e-5
+    assert O.rel_fro(res[2][0], O.linear_dot_exact(A, G, n_v)) < TOL[dtype]
+    assert lib.ghost_set_persample_pair_mode(3) < 0
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
