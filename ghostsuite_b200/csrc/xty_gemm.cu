@@ -437,7 +437,7 @@ int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_tota
                           int v_is_f32, const DeviceState* ds, cudaStream_t st);
 int launch_xty_pair_wgrad(const void* X, const void* Y, long long n_rows, int m_cols, int n_cols, long long ldx,
                           long long ldy, float* acc_ws, long long ld_acc, const DeviceState* ds, cudaStream_t st);
-static int g_wgrad_pair_mode = 0;      // same meaning as below
+static int g_wgrad_pair_mode = 1;      // same meaning as below
 static int g_persample_pair_mode = 1;  // 0 off, 1 where no half of a pair would idle, 2 wherever applicable
 
 // Operand maps: the blocked form (one TMA instruction per operand and stage) when the column count

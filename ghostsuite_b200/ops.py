@@ -313,7 +313,7 @@ def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float
     if colsum_of is not None and not split:
         colsums = torch.empty((N, m if colsum_of == "X" else n), dtype=_F32, device=X.device)
         cs_flag = 1 if colsum_of == "X" else 2
-    with _Timed("xty_gemm_kernel+tile_dot_kernel[persample]", "tensor",
+    with _Timed("xty_gemm_pair_kernel+tile_dot_mma_kernel[persample]", "tensor",
                 2.0 * N * T * m * n + 2.0 * n_val * n_train * m * n, 2.0 * N * T * (m + n)):
         xp, yp, ldx, ldy, T_eff = mat(base)
         _lib.check(lib.ghost_persample_dot_bf16(

@@ -108,7 +108,7 @@ int ghost_set_persample_budget_bytes(long long bytes);
  * multiples of 64 and X's 128-column tile count is even or at least 15; 2 = the pair kernel
  * whenever the column counts allow it.  Both kernels store identical tiles.  Process-wide. */
 int ghost_set_persample_pair_mode(int mode);
-/* The same choice for ghost_wgrad_bf16's split-K pass (modes 0 / 1 / 2 as above; default 0). */
+/* The same choice for ghost_wgrad_bf16's split-K pass (modes 0 / 1 / 2 as above; default 1). */
 int ghost_set_wgrad_pair_mode(int mode);
 /* colsum_of = 1 (X) or 2 (Y) also writes the per-sample column sums of that operand,
  * colsum_out[s, c] = sum_t operand[s, t, c] (fp32, [n_train + n_val, cols]): the bias terms of

@@ -136,7 +136,7 @@ def test_wgrad_cta_pair_kernel(case):
             res[mode] = ops().wgrad(G.cuda(), A.cuda(), 1.0, torch.float32)
             after()
     finally:
-        _lib.check(lib.ghost_set_wgrad_pair_mode(0))
+        _lib.check(lib.ghost_set_wgrad_pair_mode(1))
     assert O.rel_fro(res[2], ref) < 1e-2
     assert O.rel_fro(res[2], res[0].cpu()) < 1e-5      # same products, another order of fp32 additions
 
