@@ -45,3 +45,16 @@ def test_ops_fail_loudly_without_cuda():
         ops.gram_dot(A, A, 1)
     with pytest.raises(RuntimeError):
         ops.colsum(A)
+
+
+def test_kernel_switches_validate_their_argument():
+    """The process-wide kernel switches need no device: modes 0..2 are accepted, others rejected."""
+    from ghostsuite_b200 import build
+    lib = ctypes.CDLL(build.build())
+    for name, default in (("ghost_set_persample_pair_mode", 1), ("ghost_set_wgrad_pair_mode", 1)):
+        fn = getattr(lib, name)
+        fn.argtypes = [ctypes.c_int]
+        fn.restype = ctypes.c_int
+        assert fn(-1) < 0 and fn(3) < 0
+        for mode in (0, 2, default):
+            assert fn(mode) == 0
