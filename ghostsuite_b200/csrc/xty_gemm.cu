@@ -437,6 +437,7 @@ int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_tota
                           int v_is_f32, const DeviceState* ds, cudaStream_t st);
 int launch_xty_pair_wgrad(const void* X, const void* Y, long long n_rows, int m_cols, int n_cols, long long ldx,
                           long long ldy, float* acc_ws, long long ld_acc, const DeviceState* ds, cudaStream_t st);
+bool xty_pair_usable(const DeviceState* ds);
 static int g_wgrad_pair_mode = 1;      // same meaning as below
 static int g_persample_pair_mode = 1;  // 0 off, 1 where no half of a pair would idle, 2 wherever applicable
 
@@ -554,7 +555,7 @@ extern "C" int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, 
   int rc;
   if ((rc = make_xty_maps(&tx, &ty, p, X, Y, 1, n_rows, ldx, ldy)) != GHOST_OK) return rc;
   GB_CUDA_OK(cudaMemsetAsync(ws, 0, static_cast<size_t>(m_cols) * p.ld_acc * 4, st));
-  if (pair_kernel_fits(g_wgrad_pair_mode, m_cols, n_cols) && p.blocked_x && p.blocked_y && ds->sm_count >= 2)
+  if (pair_kernel_fits(g_wgrad_pair_mode, m_cols, n_cols) && p.blocked_x && p.blocked_y && xty_pair_usable(ds))
     rc = launch_xty_pair_wgrad(X, Y, n_rows, m_cols, n_cols, ldx, ldy, p.acc_ws, p.ld_acc, ds, st);
   else
     rc = launch_xty(tx, ty, p, ds, st);
@@ -651,7 +652,7 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
   // tile pass: the CTA-pair kernel when it is selected and applicable, else the single-CTA kernel
   const bool use_pair = pair_kernel_fits(g_persample_pair_mode, m_cols, n_cols) && p.blocked_x && p.blocked_y &&
-                        colsum_of == 0 && ds->sm_count >= 2;
+                        colsum_of == 0 && xty_pair_usable(ds);
   auto tile_pass = [&](const XtyParams& q) -> int {
     if (use_pair)
       return launch_xty_pair_tiles(X, Y, N, T, m_cols, n_cols, ldx, ldy, q.samples, q.sample0, q.vgrad,

@@ -284,6 +284,36 @@ static int pair_kernel_smem_attr(const DeviceState* ds) {
   return GHOST_OK;
 }
 
+// Whether the device can hold at least one cluster of the pair kernel (asked once per device; a
+// partitioned or otherwise restricted device may not): callers fall back to the single-CTA kernel.
+bool xty_pair_usable(const DeviceState* ds) {
+  static int state[64] = {};      // 0 unknown, 1 usable, -1 not
+  if (ds->sm_count < 2) return false;
+  int& st = state[ds->device];
+  if (st == 0) {
+    st = -1;
+    if (pair_kernel_smem_attr(ds) == GHOST_OK) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2, 1, 1);
+      cfg.blockDim = dim3(192, 1, 1);
+      cfg.dynamicSmemBytes = XtyPairCfg::kSmemBytes;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, xty_gemm_pair_kernel, &cfg) == cudaSuccess && clusters > 0)
+        st = 1;
+      else
+        (void)cudaGetLastError();
+    }
+  }
+  return st == 1;
+}
+
 // X: [n_samples_total, T, m_cols], Y: [n_samples_total, T, n_cols] bf16, both column counts multiples
 // of 64.  Writes the tiles of samples [sample0, sample0 + samples) to vgrad ([tile][samples][128][256]).
 int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_total, long long T, int m_cols,
