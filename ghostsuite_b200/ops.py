@@ -265,7 +265,7 @@ def wgrad(X: torch.Tensor, Y: torch.Tensor, scale: float, out_dtype: torch.dtype
     off_ws = arena.plan(ws_bytes)
     mat, _ = _xty_operands(lib, arena, X, Y, S, T)
     base = arena.commit()
-    with _Timed("xty_gemm_kernel[wgrad]", "tensor", 2.0 * S * T * m * n, 2.0 * S * T * (m + n)):
+    with _Timed("xty_gemm_pair_kernel[wgrad]", "tensor", 2.0 * S * T * m * n, 2.0 * S * T * (m + n)):
         xp, yp, ldx, ldy, T_eff = mat(base)
         _lib.check(lib.ghost_wgrad_bf16(xp, yp, S * T_eff, m, n, ldx, ldy, float(scale),
                                         1 if accumulate else 0, out.data_ptr(), _dt_flag(out),
