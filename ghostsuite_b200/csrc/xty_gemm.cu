@@ -583,7 +583,7 @@ static int persample_group(int n_train, int n_val, long long tiles, int esize, l
   if (g > n_train) g = n_train;
   return static_cast<int>(g);
 }
-static long long kPersampleBudget = 6ll << 30;
+static long long kPersampleBudget = 12ll << 30;
 
 extern "C" int ghost_set_persample_budget_bytes(long long bytes) {
   GB_REQUIRE(bytes >= (1ll << 20), "ghost_set_persample_budget_bytes: at least 1 MiB");

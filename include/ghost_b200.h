@@ -100,7 +100,7 @@ int ghost_wgrad_bf16(const void* X, const void* Y, long long n_rows, int m_cols,
  * Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:131-135 and :443-447, per
  * validation sample (the reference's version sums the validation batch first). */
 long long ghost_persample_workspace_bytes(int n_train, int n_val, int m_cols, int n_cols, int v_is_f32);
-/* Upper bound on that workspace (default 6 GiB); smaller values make the train samples go through
+/* Upper bound on that workspace (default 12 GiB); smaller values make the train samples go through
  * in more, smaller groups.  Process-wide; set it before sizing workspaces. */
 int ghost_set_persample_budget_bytes(long long bytes);
 /* Selects the kernel of the tile pass: 0 = one CTA per 128 x 256 tile; 1 (default) = a CTA pair

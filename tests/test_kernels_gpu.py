@@ -200,7 +200,7 @@ def test_persample_dot_in_groups(sizes):
     ref = O.linear_dot_exact(A, G, n_v)
     gref = torch.einsum("btp,btd->pd", G[:n_t].double(), A[:n_t].double())
     try:
-        for budget in (6 << 30, 2 << 20):
+        for budget in (12 << 30, 2 << 20):
             _lib.check(lib.ghost_set_persample_budget_bytes(budget))
             M, grad, cs = ops().persample_dot(G.cuda(), A.cuda(), n_v, want_grad=True, grad_scale=1.0,
                                               grad_dtype=torch.float32, colsum_of="X")
@@ -209,7 +209,7 @@ def test_persample_dot_in_groups(sizes):
             assert O.rel_fro(grad, gref) < 1e-2
             assert O.rel_fro(cs, G.double().sum(1)) < 1e-5
     finally:
-        _lib.check(lib.ghost_set_persample_budget_bytes(6 << 30))
+        _lib.check(lib.ghost_set_persample_budget_bytes(12 << 30))
 
 
 @pytest.mark.parametrize("case", [(5, 3, 70, 64, 128), (3, 1, 130, 192, 320), (9, 4, 300, 448, 64),
@@ -233,7 +233,7 @@ def test_persample_dot_cta_pair_kernel(case, dtype):
             after()
     finally:
         _lib.check(lib.ghost_set_persample_pair_mode(1))
-        _lib.check(lib.ghost_set_persample_budget_bytes(6 << 30))
+        _lib.check(lib.ghost_set_persample_budget_bytes(12 << 30))
     assert torch.equal(res[0][1], res[2][1])
     assert O.rel_fro(res[2][0], res[0][0].cpu()) < 1e-5
     assert O.rel_fro(res[2][0], O.linear_dot_exact(A, G, n_v)) < TOL[dtype]
