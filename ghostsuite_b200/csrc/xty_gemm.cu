@@ -598,13 +598,13 @@ extern "C" long long ghost_persample_workspace_bytes(int n_train, int n_val, int
   return tiles * kTileElems * 4 + (static_cast<long long>(n_val) + g) * tiles * kTileElems * esize + 512;
 }
 
-// Per-sample-gradient path.  X, Y: [n_train + n_val, T, cols] (train first).  Produces
 extern "C" int ghost_set_persample_pair_mode(int mode) {
   if (mode < 0 || mode > 2) return GHOST_ERR_INVALID;
   g_persample_pair_mode = mode;
   return GHOST_OK;
 }
 
+// Per-sample-gradient path.  X, Y: [n_train + n_val, T, cols] (train first).  Produces
 // M[v, b] = dot_scale * <X_v^T Y_v, X_b^T Y_b> and, if grad_out != null, the train gradient
 // grad_scale * sum_b X_b^T Y_b (written or accumulated, cast to the parameter dtype).
 extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_train, int n_val, long long T,
