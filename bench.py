@@ -389,7 +389,7 @@ def run_kernels(args):
         def rnd(*shape, scale=1.0, dtype=torch.bfloat16):
             return (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
 
-        _lib.check(_lib.load().ghost_set_gram_pair_mode(1 if kind == "gram_pair" else 0))
+        _lib.check(_lib.load().ghost_set_gram_pair_mode(2 if kind == "gram_pair" else 0))
         if kind == "gram_pair":
             kind = "gram"
         if kind in ("gram", "persample", "wgrad"):
@@ -444,7 +444,7 @@ def run_kernels(args):
         results[name] = entry
         del fn
         torch.cuda.empty_cache()
-    _lib.check(_lib.load().ghost_set_gram_pair_mode(0))
+    _lib.check(_lib.load().ghost_set_gram_pair_mode(1))
     emit({"mode": "kernels", "peaks": {"tensor_burst_tflops": burst, "hbm_gbs": peaks["hbm"],
                                                     "source": peaks["source"]}, "results": results})
 

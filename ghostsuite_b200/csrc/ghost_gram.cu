@@ -296,13 +296,17 @@ int launch_gram_pair(const void* a_t, const void* a_v, const void* g_t, const vo
                      long long ld_gv, int round_mode, float scale, float* M, const DeviceState* ds,
                      cudaStream_t stream);
 
-// 0: single-CTA kernels only; 1: CTA-pair kernel for problems with at least 512 x 256 tokens
-static int g_gram_pair_mode = 0;
+// 0: single-CTA kernels only; 1: CTA-pair kernel for problems with at least 512 train tokens and 256
+// to 8192 validation tokens (where it measured faster: 1474 against 1339 TFLOP/s with 32768 x 4096
+// tokens, 985 against 1117 with 131072 x 16384); 2: CTA-pair kernel from 512 x 256 tokens up
+static int g_gram_pair_mode = 1;
+bool xty_pair_usable(const DeviceState* ds);     // a cluster of two ~198 KB CTAs fits on the device
 
 }  // namespace gb
 
 extern "C" int ghost_set_gram_pair_mode(int mode) {
-  gb::g_gram_pair_mode = mode ? 1 : 0;
+  if (mode < 0 || mode > 2) return GHOST_ERR_INVALID;
+  gb::g_gram_pair_mode = mode;
   return GHOST_OK;
 }
 
@@ -324,7 +328,8 @@ extern "C" int ghost_gram_dot_bf16(const void* a_train, const void* a_val, const
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
   const long long rows_v = static_cast<long long>(n_val) * T;
-  if (g_gram_pair_mode && rows_v >= 256 && static_cast<long long>(n_train) * T >= 512)
+  const bool pair_wanted = g_gram_pair_mode == 2 || (g_gram_pair_mode == 1 && rows_v <= 8192);
+  if (pair_wanted && rows_v >= 256 && static_cast<long long>(n_train) * T >= 512 && xty_pair_usable(ds))
     return launch_gram_pair(a_train, a_val, g_train, g_val, n_train, n_val, T, ka, kg, ld_at, ld_av, ld_gt,
                             ld_gv, round_mode, scale, M_out, ds, st);
   if (rows_v <= 128)

@@ -1,8 +1,9 @@
 // ghost_gram, CTA-pair variant (tcgen05 cta_group::2).  Same math and epilogue as ghost_gram.cu:
 //   M[v, b] = sum_{t in b, s in v} (A_t . A_s)(G_t . G_s)
 // A cluster of two CTAs owns a 256 (train tokens) x 256 (validation tokens) tile.  CTA r loads its
-// own 128 train rows and its own 128 of the 256 validation rows (32 KB per stage instead of 48 KB,
-// six stages), the leader CTA issues 256x256x16 MMAs that read both CTAs' shared memory, and each CTA
+// own 128 train rows and its own 128 of the 256 validation rows (64 KB per stage of 128 K-elements,
+// three stages: eight MMAs per barrier round trip of the issuing thread), the leader CTA issues
+// 256x256x16 MMAs that read both CTAs' shared memory, and each CTA
 // reduces its own 128 accumulator rows out of its own tensor memory.  Per output element the
 // validation operand crosses L2 -> shared memory half as often as in the single-CTA kernel.
 //
@@ -30,9 +31,10 @@ struct GramPairCfg {
   static constexpr int BM = 128;           // rows per CTA
   static constexpr int BNH = 128;          // validation rows loaded per CTA (half of N = 256)
   static constexpr int BN = 256;
-  static constexpr int BK = 64;
-  static constexpr int kStageBytes = (BM + BNH) * BK * 2;   // 32 KB
-  static constexpr int kStages = 6;
+  static constexpr int BK = 128;           // K elements per stage = two 64-element swizzle atoms per operand
+  static constexpr int kAtomK = 64;
+  static constexpr int kStageBytes = (BM + BNH) * BK * 2;   // 64 KB
+  static constexpr int kStages = 3;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
 
@@ -114,12 +116,15 @@ ghost_gram_pair_kernel(const __grid_constant__ CUtensorMap tm_at, const __grid_c
           // the leader's barrier collects both CTAs' bytes
           if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          if (kb < kb_a) {
-            tma_load_2d_pair(st, &tm_at, bar, kb * BK, m0);
-            tma_load_2d_pair(st + BM * BK * 2, &tm_av, bar, kb * BK, n0);
-          } else {
-            tma_load_2d_pair(st, &tm_gt, bar, (kb - kb_a) * BK, m0);
-            tma_load_2d_pair(st + BM * BK * 2, &tm_gv, bar, (kb - kb_a) * BK, n0);
+          // stage layout: [train atom 0 | train atom 1 | validation atom 0 | validation atom 1]; an atom
+          // past the end of K is zero-filled by the bounds check
+          const CUtensorMap* mt = (kb < kb_a) ? &tm_at : &tm_gt;
+          const CUtensorMap* mv = (kb < kb_a) ? &tm_av : &tm_gv;
+          const int k0 = ((kb < kb_a) ? kb : kb - kb_a) * BK;
+#pragma unroll
+          for (int a = 0; a < BK / Cfg::kAtomK; ++a) {
+            tma_load_2d_pair(st + a * (BM * Cfg::kAtomK * 2), mt, bar, k0 + a * Cfg::kAtomK, m0);
+            tma_load_2d_pair(st + BM * BK * 2 + a * (BNH * Cfg::kAtomK * 2), mv, bar, k0 + a * Cfg::kAtomK, n0);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -141,13 +146,16 @@ ghost_gram_pair_kernel(const __grid_constant__ CUtensorMap tm_at, const __grid_c
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 543)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(sa + BM * BK * 2, 16, 1024);
           const bool first = (kb == 0) || (kb == kb_a);
           const uint32_t dst = (kb < kb_a) ? d_a : d_g;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_bf16_pair(dst, adesc + 2 * k, bdesc + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
+          for (int a = 0; a < BK / Cfg::kAtomK; ++a) {
+            const uint64_t adesc = make_smem_desc_sw128(sa + a * (BM * Cfg::kAtomK * 2), 16, 1024);
+            const uint64_t bdesc = make_smem_desc_sw128(sa + BM * BK * 2 + a * (BNH * Cfg::kAtomK * 2), 16, 1024);
+#pragma unroll
+            for (int k = 0; k < Cfg::kAtomK / 16; ++k)
+              umma_bf16_pair(dst, adesc + 2 * k, bdesc + 2 * k, idesc, (first && a == 0 && k == 0) ? 0u : 1u);
+          }
           umma_commit_pair(&empty_bar[stage], 3);      // frees the stage in both CTAs
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }

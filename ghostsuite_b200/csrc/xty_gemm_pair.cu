@@ -5,13 +5,14 @@
 // every 128 x 256 tile, D = X_s[:, m-block]^T Y_s[:, n-block] contracted over the sample's tokens,
 // written tile-major ([tile][sample][128][256], bf16 or fp32).  A cluster of two CTAs owns a 256 x 256
 // block of the per-sample gradient: CTA r loads its own 128 X columns and its own 128 of the 256 Y
-// columns (32 KB per stage instead of 48 KB, six stages instead of four), the leader issues
-// 256 x 256 x 16 MMAs that read both CTAs' shared memory, and each CTA writes the 128 x 256 tile that
+// columns (64 KB per stage of 128 tokens, three stages), the leader issues 256 x 256 x 16 MMAs that
+// read both CTAs' shared memory (eight per stage: with 64-token stages the issuing thread spent as
+// long on the two barrier operations of a stage as the tensor core on its four MMAs), and each CTA writes the 128 x 256 tile that
 // sits in its own tensor memory.  Per output element the Y operand crosses L2 -> shared memory and
 // shared memory -> tensor core half as often as in the single-CTA kernel.
 //
 // Train-gradient pass (one "sample" holding all token rows): a unit is a 256 x 256 block and one of
-// k_splits ranges of 64-row blocks; units are walked split-major, so the pairs running at the same
+// k_splits ranges of 128-row blocks; units are walked split-major, so the pairs running at the same
 // time read the same token rows; every CTA adds its 128 x 256 half into the fp32 workspace with
 // red.global.add.v4.f32, exactly as the single-CTA kernel does.
 //
@@ -34,7 +35,7 @@ struct XtyPairParams {
   void* vgrad;
   int v_is_f32;
   int accumulate;            // 0: store tiles; 1: add into acc_ws ("samples" = k_splits, one real sample)
-  int kb_per_split;          // 64-row blocks per split (accumulate)
+  int kb_per_split;          // row blocks (BK tokens) per split (accumulate)
   float* acc_ws;             // [m_cols, ld_acc] fp32, zeroed by the host
   long long ld_acc;
   int* err;
@@ -44,9 +45,9 @@ struct XtyPairCfg {
   static constexpr int BM = 128;           // X columns per CTA
   static constexpr int BNH = 128;          // Y columns loaded per CTA (half of N = 256)
   static constexpr int BN = 256;
-  static constexpr int BK = 64;            // tokens per stage
-  static constexpr int kStageBytes = (BM + BNH) * BK * 2;   // 32 KB
-  static constexpr int kStages = 6;
+  static constexpr int BK = 128;           // tokens per stage: eight MMAs per barrier round trip
+  static constexpr int kStageBytes = (BM + BNH) * BK * 2;   // 64 KB
+  static constexpr int kStages = 3;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
 
@@ -105,7 +106,7 @@ xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     tm = n_inner ? outer : in;
     tn = n_inner ? in : outer;
   };
-  // 64-row blocks a unit contracts: the whole sample, or one split of the single sample
+  // row blocks (BK tokens) a unit contracts: the whole sample, or one split of the single sample
   auto k_range = [&](int sample, int& kb0, int& kb1) {
     if (!p.accumulate) { kb0 = 0; kb1 = kb_total; return; }
     kb0 = sample * p.kb_per_split;
@@ -378,7 +379,7 @@ int launch_xty_pair_wgrad(const void* X, const void* Y, long long n_rows, int m_
   long long best = -1;
   for (int s = 1; s <= 64 && s <= kb; ++s) {
     const long long rounds = (blocks * s + pairs_max - 1) / pairs_max;
-    const long long cost = rounds * (ceil_div(kb, s) + 64);
+    const long long cost = rounds * (ceil_div(kb, s) + 32);
     if (best < 0 || cost < best) { best = cost; splits = s; }
   }
   p.kb_per_split = ceil_div(kb, splits);

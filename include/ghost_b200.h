@@ -73,9 +73,9 @@ int ghost_gram_dot_bf16(const void* a_train, const void* a_val, const void* g_tr
                         long long ld_at, long long ld_av, long long ld_gt, long long ld_gv,
                         int round_mode, float scale, float* M_out, void* stream);
 
-/* Selects the kernel behind ghost_gram_dot_bf16: 0 = one CTA per 128 x 256 tile, 1 = a CTA pair
- * (tcgen05 cta_group::2) per 256 x 256 tile for problems of at least 512 train x 256 validation
- * tokens.  Process-wide. */
+/* Selects the kernel behind ghost_gram_dot_bf16: 0 = one CTA per 128 x 256 tile; 1 (default) = a
+ * CTA pair (tcgen05 cta_group::2) per 256 x 256 tile for problems of at least 512 train tokens and
+ * 256 to 8192 validation tokens; 2 = the pair kernel from 512 x 256 tokens up.  Process-wide. */
 int ghost_set_gram_pair_mode(int mode);
 
 /* ---- train-gradient recovery ------------------------------------------------------------------- */

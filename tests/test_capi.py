@@ -51,7 +51,8 @@ def test_kernel_switches_validate_their_argument():
     """The process-wide kernel switches need no device: modes 0..2 are accepted, others rejected."""
     from ghostsuite_b200 import build
     lib = ctypes.CDLL(build.build())
-    for name, default in (("ghost_set_persample_pair_mode", 1), ("ghost_set_wgrad_pair_mode", 1)):
+    for name, default in (("ghost_set_persample_pair_mode", 1), ("ghost_set_wgrad_pair_mode", 1),
+                          ("ghost_set_gram_pair_mode", 1)):
         fn = getattr(lib, name)
         fn.argtypes = [ctypes.c_int]
         fn.restype = ctypes.c_int

@@ -66,13 +66,14 @@ def test_gram_dot_cta_pair_kernel(case, dtype):
     A, G = make(n_t + n_v, T, d, p, dtype, seed=21)
     ref = O.linear_dot_exact(A, G, n_v) if n_t * n_v < 5000 else None
     try:
-        _lib.check(lib.ghost_set_gram_pair_mode(1))
+        _lib.check(lib.ghost_set_gram_pair_mode(2))
         M2 = ops().gram_dot(A.cuda(), G.cuda(), n_v)
         after()
-    finally:
         _lib.check(lib.ghost_set_gram_pair_mode(0))
-    M1 = ops().gram_dot(A.cuda(), G.cuda(), n_v)
-    after()
+        M1 = ops().gram_dot(A.cuda(), G.cuda(), n_v)
+        after()
+    finally:
+        _lib.check(lib.ghost_set_gram_pair_mode(1))
     assert O.rel_fro(M2, M1.cpu()) < 1e-5
     if ref is not None:
         assert O.rel_fro(M2, ref) < TOL[dtype]
