@@ -329,10 +329,10 @@ def dominant_kernel_roofline(prof, peaks):
         achieved = rec["flops"] / calls / avg_s / 1e12
         traffic = None
         if "persample" in name:
-            # ncu capture of the mlp.c_fc shape: 663 MB of DRAM traffic per call (315 MB inputs read
+            # ncu capture of the mlp.c_fc shape: 669 MB of DRAM traffic per call (315 MB inputs read
             # once, 153 MB of tile write-back, 189 MB of tiles read once, 6 MB of results) for
             # 315 MB of input bytes; scaled by input bytes
-            traffic = rec["bytes"] / calls * (663.0 / 315.0)
+            traffic = rec["bytes"] / calls * (669.0 / 315.0)
         return {"kernel": name, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor"],
                 "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": traffic,
                 "launches": calls, "avg_ms": avg_s * 1e3, "peak_source": peaks["source"]}
