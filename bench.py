@@ -330,7 +330,7 @@ def dominant_kernel_roofline(prof, peaks):
         traffic = None
         if "persample" in name:
             # ncu capture of the mlp.c_fc shape: 669 MB of DRAM traffic per call (315 MB inputs read
-            # once, 153 MB of tile write-back, 189 MB of tiles read once, 6 MB of results) for
+            # once, 159 MB of tile write-back, 189 MB of tiles read once, 6 MB of results) for
             # 315 MB of input bytes; scaled by input bytes
             traffic = rec["bytes"] / calls * (669.0 / 315.0)
         return {"kernel": name, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor"],
