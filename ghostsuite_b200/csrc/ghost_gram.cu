@@ -14,7 +14,7 @@
 //   warps 0-3  epilogue: tcgen05.ld both accumulators, Hadamard, segmented reduce, atomicAdd to M
 //   warp  4    TMA producer (one elected lane)
 //   warp  5    TMEM allocator + MMA issuer (one elected lane)
-// Pipeline: kStages shared-memory stages (train tile 128x64 + val tile BNx64 bf16, 128B swizzle),
+// Pipeline: kStages shared-memory stages (train tile 128xBK + val tile BNxBK bf16 in 64-element atoms, 128B swizzle),
 // full/empty mbarriers per stage, acc_full/acc_empty mbarriers per accumulator buffer.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -37,9 +37,13 @@ struct GramParams {
 template <int BN>
 struct GramCfg {
   static constexpr int BM = 128;
-  static constexpr int BK = 64;
+  static constexpr int kAtomK = 64;                        // K elements of one 128-byte swizzle atom
+  // K elements per stage.  BN = 128: two atoms per operand (64 KB stages), so the issuing thread
+  // does one barrier round trip per eight MMAs; BN = 256 keeps one atom (48 KB stages), two would
+  // leave room for two stages only.
+  static constexpr int BK = (BN == 256) ? 64 : 128;
   static constexpr int kStageBytes = (BM + BN) * BK * 2;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? 4 : 3;
   static constexpr int kAccBufs = 512 / (2 * BN);          // 1 (BN=256) or 2 (BN=128)
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -122,12 +126,16 @@ ghost_gram_kernel(const __grid_constant__ CUtensorMap tm_at, const __grid_consta
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 401)) { ok = false; break; }
           uint8_t* st = smem + stage * Cfg::kStageBytes;
           mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          if (kb < kb_a) {
-            tma_load_2d(st, &tm_at, &full_bar[stage], kb * BK, m0);
-            tma_load_2d(st + BM * BK * 2, &tm_av, &full_bar[stage], kb * BK, n0);
-          } else {
-            tma_load_2d(st, &tm_gt, &full_bar[stage], (kb - kb_a) * BK, m0);
-            tma_load_2d(st + BM * BK * 2, &tm_gv, &full_bar[stage], (kb - kb_a) * BK, n0);
+          // stage layout: train atoms, then validation atoms; an atom past the end of K is
+          // zero-filled by the bounds check
+          const CUtensorMap* mt = (kb < kb_a) ? &tm_at : &tm_gt;
+          const CUtensorMap* mv = (kb < kb_a) ? &tm_av : &tm_gv;
+          const int k0 = ((kb < kb_a) ? kb : kb - kb_a) * BK;
+#pragma unroll
+          for (int a = 0; a < BK / Cfg::kAtomK; ++a) {
+            tma_load_2d(st + a * (BM * Cfg::kAtomK * 2), mt, &full_bar[stage], k0 + a * Cfg::kAtomK, m0);
+            tma_load_2d(st + BM * BK * 2 + a * (BN * Cfg::kAtomK * 2), mv, &full_bar[stage],
+                        k0 + a * Cfg::kAtomK, n0);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -151,13 +159,16 @@ ghost_gram_kernel(const __grid_constant__ CUtensorMap tm_at, const __grid_consta
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 503)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(sa + BM * BK * 2, 16, 1024);
           const bool first = (kb == 0) || (kb == kb_a);
           const uint32_t dst = (kb < kb_a) ? d_a : d_g;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_bf16(dst, adesc + 2 * k, bdesc + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
+          for (int a = 0; a < BK / Cfg::kAtomK; ++a) {
+            const uint64_t adesc = make_smem_desc_sw128(sa + a * (BM * Cfg::kAtomK * 2), 16, 1024);
+            const uint64_t bdesc = make_smem_desc_sw128(sa + BM * BK * 2 + a * (BN * Cfg::kAtomK * 2), 16, 1024);
+#pragma unroll
+            for (int k = 0; k < Cfg::kAtomK / 16; ++k)
+              umma_bf16(dst, adesc + 2 * k, bdesc + 2 * k, idesc, (first && a == 0 && k == 0) ? 0u : 1u);
+          }
           umma_commit(&empty_bar[stage]);   // frees the stage once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
