@@ -42,7 +42,14 @@ def shard_indices(n_items: int, rank: int, world: int) -> range:
 
 
 def shard_train_batch(x_train: torch.Tensor, rank: int, world: int) -> torch.Tensor:
-    lo, hi = shard_bounds(x_train.shape[0], rank, world)
+    """Rank ``rank``'s block of the train batch.  The batch must divide by ``world``: the all-gather of
+    the dot-product blocks, the ``(N_local / N_global) ** 2`` rescale and the plain average of the
+    train gradients all rely on equal shards."""
+    n = int(x_train.shape[0])
+    if n % world != 0:
+        raise ValueError(f"train batch of {n} samples does not divide over {world} ranks; the "
+                         "data-parallel GradDotProd path needs equal shards")
+    lo, hi = shard_bounds(n, rank, world)
     return x_train[lo:hi]
 
 
@@ -52,16 +59,29 @@ def _dot_params(module: torch.nn.Module) -> List[Tuple[str, torch.Tensor]]:
 
 
 def gather_dot_products(module: torch.nn.Module, group=None,
-                        single_process_equivalent: bool = True) -> Dict[str, torch.Tensor]:
+                        single_process_equivalent: bool = True,
+                        check_equal_shards: bool = True) -> Dict[str, torch.Tensor]:
     """All-gather every parameter's ``[n_val, n_train_local]`` block along the train dimension
     (equal shard sizes) and store the global ``[n_val, n_train_global]`` matrix (and its column sums)
-    back on the parameter.  One collective for all parameters."""
+    back on the parameter.  One collective for all parameters, preceded by a four-integer MIN
+    all-reduce that makes unequal shards raise ``ValueError`` on every rank instead of reaching the
+    all-gather (``check_equal_shards=False`` skips it when the caller has sharded with
+    :func:`shard_train_batch`, which enforces equal shards itself)."""
     world = dist.get_world_size(group)
     named = _dot_params(module)
     if not named:
         return {}
     packed = torch.stack([p.grad_dot_prod_matrix for _, p in named])       # [P, n_val, n_loc]
     P, n_val, n_loc = packed.shape
+    if check_equal_shards:
+        # a rank with a different shard size would hand the all-gather a buffer of another size
+        # (undefined under NCCL): compare sizes first, one tiny collective
+        probe = torch.tensor([n_loc, -n_loc, P, -P], dtype=torch.int64, device=packed.device)
+        dist.all_reduce(probe, op=dist.ReduceOp.MIN, group=group)
+        lo_n, hi_n, lo_p, hi_p = int(probe[0]), -int(probe[1]), int(probe[2]), -int(probe[3])
+        if lo_n != hi_n or lo_p != hi_p:
+            raise ValueError(f"ranks disagree on the dot-product blocks (train samples per rank {lo_n}..{hi_n}, "
+                             f"parameters {lo_p}..{hi_p}); the data-parallel path needs equal shards")
     gathered = torch.empty((world * P, n_val, n_loc), dtype=packed.dtype, device=packed.device)
     dist.all_gather_into_tensor(gathered, packed.contiguous(), group=group)
     full = gathered.view(world, P, n_val, n_loc).permute(1, 2, 0, 3).reshape(P, n_val, world * n_loc)
@@ -142,11 +162,12 @@ class OverlappedGradSync:
                     if getattr(prm, "initially_requires_grad", prm.requires_grad):
                         self.expected[id(prm)] = self.expected.get(id(prm), 0) + 1
         self._seen: Dict[int, int] = {}
-        self._bucket: List[torch.Tensor] = []
+        self._bucket: List[Tuple[int, torch.Tensor]] = []
         self._bucket_size = 0
         self._bucket_dtype = None
-        self._inflight: List[Tuple[object, torch.Tensor, List[torch.Tensor]]] = []
+        self._inflight: List[Tuple[object, torch.Tensor, List[Tuple[int, torch.Tensor]]]] = []
         self._reduced: set = set()
+        self._dirty: set = set()
         layers.TRAIN_GRAD_OBSERVER = self._on_train_grad
 
     def close(self) -> None:
@@ -162,10 +183,19 @@ class OverlappedGradSync:
         self._seen[key] = seen
         if seen < self.expected[key]:
             return                                   # another layer still adds to this gradient
-        g = param.train_grad
+        if seen > self.expected[key]:
+            # More contributions than hooked layers: a second backward pass before finish() (gradient
+            # accumulation) or a module called twice in one forward.  The gradient was queued after
+            # its first complete set of contributions and has been added to since, so whatever was
+            # (or will be) reduced for it is stale: finish() drops that and reduces the final tensor.
+            self._dirty.add(key)
+            return
+        self._enqueue(key, param.train_grad)
+
+    def _enqueue(self, key: int, g: torch.Tensor) -> None:
         if self._bucket and g.dtype != self._bucket_dtype:
             self._flush()
-        self._bucket.append(g)
+        self._bucket.append((key, g))
         self._bucket_dtype = g.dtype
         self._bucket_size += g.numel() * g.element_size()
         self._reduced.add(key)
@@ -175,37 +205,49 @@ class OverlappedGradSync:
     def _flush(self) -> None:
         if not self._bucket:
             return
-        grads = self._bucket
-        flat = torch.cat([g.reshape(-1) for g in grads])
+        entries = self._bucket
+        flat = torch.cat([g.reshape(-1) for _, g in entries])
         work = dist.all_reduce(flat, op=self.avg_op, group=self.group, async_op=True)
-        self._inflight.append((work, flat, grads))
+        self._inflight.append((work, flat, entries))
         self._bucket, self._bucket_size, self._bucket_dtype = [], 0, None
 
     # ------------------------------------------------------------------ after backward
     def finish(self) -> int:
         """Flush, wait for every bucket, write the averages back.  Gradients that never reported
-        (parameters of layers without hooks) are averaged here in one more bucket.  Returns the
-        number of collectives of this pass."""
+        (parameters of layers without hooks) and gradients that were added to after they had been
+        queued are averaged here in one more bucket.  Returns the number of collectives of this
+        pass."""
+        dirty = self._dirty
+        if dirty:
+            kept = [(k, g) for k, g in self._bucket if k not in dirty]
+            self._bucket = kept
+            self._bucket_size = sum(g.numel() * g.element_size() for _, g in kept)
+            self._reduced -= dirty
+        n_early = len(self._inflight)          # buckets that went out during the backward pass
         for _, prm in self.module.named_parameters():
             g = getattr(prm, "train_grad", None)
             if g is not None and id(prm) not in self._reduced:
-                if self._bucket and g.dtype != self._bucket_dtype:
-                    self._flush()
-                self._bucket.append(g)
-                self._bucket_dtype = g.dtype
-                self._bucket_size += g.numel() * g.element_size()
-                self._reduced.add(id(prm))
+                self._enqueue(id(prm), g)
         self._flush()
         calls = len(self._inflight)
-        for work, flat, grads in self._inflight:
+        for i, (work, flat, entries) in enumerate(self._inflight):
             work.wait()
             if self.avg_op == dist.ReduceOp.SUM:
                 flat.mul_(1.0 / self.world)
-            pieces = flat.split([g.numel() for g in grads])
-            torch._foreach_copy_(grads, [pc.view_as(g) for pc, g in zip(pieces, grads)])
+            pieces = flat.split([g.numel() for _, g in entries])
+            dst, src = [], []
+            for (k, g), pc in zip(entries, pieces):
+                # an early bucket's snapshot of a gradient that was added to afterwards is stale: it
+                # is not copied back; the same gradient sits, complete, in one of the last buckets
+                if i >= n_early or k not in dirty:
+                    dst.append(g)
+                    src.append(pc.view_as(g))
+            if dst:
+                torch._foreach_copy_(dst, src)
         self._inflight.clear()
         self._seen.clear()
         self._reduced.clear()
+        self._dirty.clear()
         return calls
 
 

@@ -17,7 +17,12 @@ What is different underneath:
   instead of hanging;
 * optional keyword ``proj_dims_override`` -- ``(k_i, k_o)`` for every layer or a
   ``{layer_name: (k_i, k_o)}`` dict -- replaces the ``choose_ki_ko`` heuristic where given (the
-  heuristic does not produce ``k_i == k_o`` for non-square layers).
+  heuristic does not produce ``k_i == k_o`` for non-square layers);
+* optional keyword ``freeze_weights=True``: while the engine is attached no model parameter requires
+  grad, so autograd computes activation gradients only (the reference's loop,
+  ``Examples/GradProj_LM/gradproj_loop.py:66``, computes every weight gradient and throws it away --
+  about a third of the backward flops).  A one-element ``dummy_bias`` on the input embedding keeps
+  the autograd graph alive; ``detach()`` removes it and restores every ``requires_grad`` flag.
 """
 from __future__ import annotations
 
@@ -152,6 +157,9 @@ class GradProjLoraEngine:
         self._bin_file = None
         self._bin_rows = 0
         self._bin_index: List[dict] = []
+        self.freeze_weights = bool(kwargs.get("freeze_weights", False))
+        self._frozen_flags: Optional[Dict[int, Tuple[torch.Tensor, bool]]] = None
+        self._frozen_embeddings: List[nn.Embedding] = []
 
         self.matched_layers = OrderedDict()
         self.projection_matrices = {}
@@ -242,10 +250,57 @@ class GradProjLoraEngine:
             hooks.attach(layer)
             self.hooks[name] = hooks
 
+    # ------------------------------------------------------------------ frozen weights
+    def _input_embeddings(self) -> List[nn.Embedding]:
+        """The embeddings that start the autograd graph: ``get_input_embeddings()`` of a Hugging Face
+        model, else every nn.Embedding of the module."""
+        getter = getattr(self.module, "get_input_embeddings", None)
+        if callable(getter):
+            try:
+                emb = getter()
+            except Exception:
+                emb = None
+            if isinstance(emb, nn.Embedding):
+                return [emb]
+        return [m for m in self.module.modules() if isinstance(m, nn.Embedding)]
+
+    def _freeze(self) -> None:
+        if self._frozen_flags is not None:
+            return
+        from ..transformers_support import _add_dummy_bias
+        embeddings = self._input_embeddings()
+        if not embeddings:
+            raise RuntimeError("freeze_weights=True needs an nn.Embedding at the model's input: with no "
+                               "trainable parameter upstream of the projected layers, backward hooks "
+                               "would never fire")
+        self._frozen_flags = {id(p): (p, bool(p.requires_grad)) for p in self.module.parameters()}
+        for p, _ in self._frozen_flags.values():
+            p.requires_grad = False
+        for emb in embeddings:
+            if not hasattr(emb, "dummy_bias"):
+                _add_dummy_bias(emb)
+                self._frozen_embeddings.append(emb)
+
+    def _unfreeze(self) -> None:
+        if self._frozen_flags is None:
+            return
+        for emb in self._frozen_embeddings:
+            handle = emb.__dict__.pop("_ghost_dummy_bias_handle", None)
+            if handle is not None:
+                handle.remove()
+            if "dummy_bias" in emb._parameters:
+                del emb._parameters["dummy_bias"]
+        self._frozen_embeddings = []
+        for p, flag in self._frozen_flags.values():
+            p.requires_grad = flag
+        self._frozen_flags = None
+
     # ------------------------------------------------------------------ attach / detach
     def attach(self):
         if self.is_attached:
             return
+        if self.freeze_weights:
+            self._freeze()
         self._attach_hooks()
         self.is_attached = True
         print(f"Attached projection hooks to {len(self.matched_layers)} layers")
@@ -254,6 +309,7 @@ class GradProjLoraEngine:
         if not self.is_attached:
             return
         self.flush()
+        self._unfreeze()
         for name, hooks in self.hooks.items():
             hooks.detach()
             layer = self.matched_layers[name]
@@ -386,6 +442,8 @@ class GradProjLoraEngine:
 
     def reattach_after_evaluation(self):
         if not self.is_attached:
+            if self.freeze_weights:
+                self._freeze()
             self._attach_hooks()
             self.is_attached = True
 

@@ -89,6 +89,106 @@ def test_sharded_run_reproduces_single_process_numbers(overlap):
     assert sorted(results) == [(0, True), (1, True)]
 
 
+def _run_ranks(target, world=2, args=()):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, q) + tuple(args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=60) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return sorted(results)
+
+
+def _worker_unequal(rank, world, port, q):
+    """Ranks that hold different numbers of train samples: the gather must raise on every rank
+    instead of calling the all-gather with mismatched buffers."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        model = nn.Linear(4, 3)
+        n_loc = 3 + rank                                  # 3 on rank 0, 4 on rank 1
+        for p in model.parameters():
+            p.initially_requires_grad = True
+            p.grad_dot_prod_matrix = torch.ones(2, n_loc)
+        try:
+            gdist.gather_dot_products(model, None)
+            raised = False
+        except ValueError as exc:
+            raised = "equal shards" in str(exc)
+        q.put((rank, raised))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_unequal_shards_raise():
+    with pytest.raises(ValueError, match="does not divide"):
+        gdist.shard_train_batch(torch.zeros(7, 3), 0, 2)
+    assert gdist.shard_train_batch(torch.zeros(8, 3), 1, 2).shape[0] == 4
+    assert _run_ranks(_worker_unequal) == [(0, True), (1, True)]
+
+
+def _worker_two_backwards(rank, world, port, q):
+    """Gradient accumulation: two backward passes report every parameter twice before the sync.  The
+    overlapped path must average the final sums, exactly like the plain bucketed all-reduce."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        n_v, d = 2, 6
+        model = nn.Sequential(nn.Linear(d, 8), nn.ReLU(), nn.Linear(8, 3))
+        twin = nn.Sequential(nn.Linear(d, 8), nn.ReLU(), nn.Linear(8, 3))
+        twin.load_state_dict(model.state_dict())
+        g = torch.Generator().manual_seed(10 + rank)      # every rank has its own micro-batches
+        micro = [(torch.randn(4 + n_v, d, generator=g), torch.randint(0, 3, (4 + n_v,), generator=g))
+                 for _ in range(2)]
+
+        class E:
+            module = model
+
+        class T:
+            module = twin
+        eng = OracleDotProdEngine(model, n_v, exact=True)
+        eng.attach()
+        ref = OracleDotProdEngine(twin, n_v, exact=True)
+        ref.attach()
+        sync = gdist.overlap_train_grad_sync(E, None, bucket_bytes=64)     # tiny buckets: sent at once
+        for x, y in micro:
+            nn.functional.cross_entropy(model(x), y).backward()
+            nn.functional.cross_entropy(twin(x), y).backward()
+            for p in reversed(list(model.parameters())):                   # what the CUDA hooks report
+                sync._on_train_grad(p)
+        for m in (model, twin):
+            for p in m.parameters():
+                p.grad_dot_prod_matrix = p.grad_dot_prod_matrix.float()
+                p.train_grad = p.train_grad.float() if p.train_grad.dtype != torch.float32 else p.train_grad
+        early = len(sync._inflight)
+        gdist.sync_engine(E, None)
+        sync.close()
+        gdist.gather_dot_products(twin, None)
+        gdist.allreduce_train_grads(twin, None)
+        ok = early >= 1 and len(sync._dirty) == 0
+        for p, r in zip(model.parameters(), twin.parameters()):
+            ok = ok and bool(torch.allclose(p.train_grad, r.train_grad, rtol=1e-6, atol=1e-7))
+        # and the averages really are cross-rank means: all ranks now hold the same tensors
+        flat = torch.cat([p.train_grad.reshape(-1) for p in model.parameters()])
+        both = [torch.empty_like(flat) for _ in range(world)]
+        dist.all_gather(both, flat)
+        ok = ok and bool(torch.equal(both[0], both[1]))
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_overlapped_sync_with_two_backward_passes():
+    assert _run_ranks(_worker_two_backwards) == [(0, True), (1, True)]
+
+
 def test_shard_bounds_cover_everything():
     for n in (1, 7, 8, 65536):
         for world in (1, 2, 3, 8):

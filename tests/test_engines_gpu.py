@@ -134,20 +134,13 @@ def test_mlp_config1_exact_parity_fp32():
     ora.detach()
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("path_rule", ["cost", "reference", "persample"])
-def test_gpt2_like_per_module_parity(dtype, path_rule):
-    """GPT-2 architecture (tied head, Conv1D, LayerNorm, two embeddings), dummy-bias mode.  The
-    (A, B) pairs seen by every hook are captured on the GPU and the oracle is evaluated on exactly
-    those tensors, per (module, parameter role) because tied parameters keep the last hook's value."""
+def _check_dotprod_model(model, run, ids, n_t, n_v, dtype, path_rule, n_hooked):
+    """Drives ``GradDotProdEngine`` (dummy-bias mode) over one backward pass of ``model`` and checks
+    every hooked module.  The (A, B) pairs seen by every hook are captured on the GPU and the oracle
+    is evaluated on exactly those tensors, per (module, parameter role) because tied parameters keep
+    the last hook's value.  ``run(model, ids)`` returns the mean loss over the given sequences."""
     from ghostsuite_b200.ghostEngines import GradDotProdEngine
     from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as L
-    from ghostsuite_b200.workloads import GPT2Like, GPT2Config
-    torch.manual_seed(1)
-    cfg = GPT2Config(vocab_size=211, n_positions=48, n_embd=64, n_layer=2, n_head=4)
-    model = GPT2Like(cfg).to(dtype).cuda()
-    n_t, n_v, T = 3, 2, 40
-    ids = torch.randint(0, cfg.vocab_size, (n_t + n_v, T)).cuda()
     opt = torch.optim.SGD(model.parameters(), lr=0.0)
     old_rule = L.PATH_RULE
     L.PATH_RULE = path_rule
@@ -177,14 +170,14 @@ def test_gpt2_like_per_module_parity(dtype, path_rule):
             handles.append(m.register_forward_hook(cap_fwd(n)))
             # registered after the engine's hook, so it observes the values that hook just wrote
             handles.append(m.register_full_backward_hook(cap_bwd(n)))
-        loss, _ = model(ids, labels=ids)
-        loss.backward()
+        run(model, ids).backward()
         torch.cuda.synchronize()
         tol = 1e-4 if dtype == torch.float32 else 2e-2
         N = n_t + n_v
-        assert len(hooked) == 2 + 2 * 6 + 1 + 1   # 2 embeddings, 2 blocks x (2 LN + 4 Conv1D), ln_f, head
+        assert len(hooked) == n_hooked
         for name, m in hooked:
             A, B = captured[name]["A"], captured[name]["B"]
+            assert A.shape[0] == N and B.shape[0] == N, (name, A.shape, B.shape)   # batch-shaped ids too
             if isinstance(m, nn.Embedding):
                 ref = O.embedding_dot_exact(A, B, n_v)
                 assert O.rel_fro(results[(name, "weight")], ref) < tol, name
@@ -209,14 +202,46 @@ def test_gpt2_like_per_module_parity(dtype, path_rule):
         model.zero_grad(set_to_none=True)
         # the engine's convention: (N / n_t) * d(mean loss over the concatenated batch)/dW restricted
         # to the train samples' tokens == gradient of the train-only token-mean loss
-        loss_t, _ = model(ids[:n_t], labels=ids[:n_t])
-        loss_t.backward()
+        run(model, ids[:n_t]).backward()
         for n, p in model.named_parameters():
             if "dummy_bias" in n:
                 continue
             assert O.rel_fro(got[n], p.grad.float().cpu()) < (1e-3 if dtype == torch.float32 else 5e-2), n
     finally:
         L.PATH_RULE = old_rule
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("path_rule", ["cost", "reference", "persample"])
+def test_gpt2_like_per_module_parity(dtype, path_rule):
+    """GPT-2 architecture (tied head, Conv1D, LayerNorm, two embeddings), dummy-bias mode."""
+    from ghostsuite_b200.workloads import GPT2Like, GPT2Config
+    torch.manual_seed(1)
+    cfg = GPT2Config(vocab_size=211, n_positions=48, n_embd=64, n_layer=2, n_head=4)
+    model = GPT2Like(cfg).to(dtype).cuda()
+    n_t, n_v, T = 3, 2, 40
+    ids = torch.randint(0, cfg.vocab_size, (n_t + n_v, T)).cuda()
+    # 2 embeddings, 2 blocks x (2 LN + 4 Conv1D), ln_f, head
+    _check_dotprod_model(model, lambda m, x: m(x, labels=x)[0], ids, n_t, n_v, dtype, path_rule, 2 + 2 * 6 + 1 + 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("path_rule", ["cost", "persample"])
+def test_hf_gpt2_lm_head_model_per_module_parity(dtype, path_rule):
+    """``transformers.GPT2LMHeadModel`` (small configuration, tied head, odd vocabulary) through
+    ``GradDotProdEngine`` in dummy-bias mode: ``forward_swapper`` gives the position embedding
+    batch-shaped ids and both embeddings a dummy bias, every Conv1D / LayerNorm / Embedding and the
+    head are hooked, and the recovered train gradients equal autograd's on the train-only batch."""
+    from transformers import GPT2Config as HFConfig, GPT2LMHeadModel
+    torch.manual_seed(2)
+    cfg = HFConfig(vocab_size=317, n_positions=64, n_embd=64, n_layer=2, n_head=4, resid_pdrop=0.0,
+                   embd_pdrop=0.0, attn_pdrop=0.0, use_cache=False)
+    model = GPT2LMHeadModel(cfg).to(dtype).cuda()
+    assert model.lm_head.weight is model.transformer.wte.weight
+    n_t, n_v, T = 3, 2, 40
+    ids = torch.randint(0, cfg.vocab_size, (n_t + n_v, T)).cuda()
+    _check_dotprod_model(model, lambda m, x: m(input_ids=x, labels=x).loss, ids, n_t, n_v, dtype, path_rule,
+                         2 + 2 * 6 + 1 + 1)
 
 
 @pytest.mark.parametrize("path_rule", ["gram", "persample"])
@@ -463,6 +488,71 @@ def test_gradproj_engine_on_gpt2_like_bf16(tmp_path):
     meta = eng.get_projection_metadata()
     assert meta["total_proj_dim"] == eng.total_proj_dim and len(meta["layers"]) == 9
     eng.cleanup()
+
+
+def _hf_decoder(family):
+    if family == "gpt_neox":
+        from transformers import GPTNeoXConfig, GPTNeoXForCausalLM
+        cfg = GPTNeoXConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=256,
+                            vocab_size=320, max_position_embeddings=64, use_cache=False,
+                            hidden_dropout=0.0, attention_dropout=0.0)
+        return GPTNeoXForCausalLM(cfg), "attention,mlp", 2 * 4
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                      intermediate_size=176, vocab_size=320, max_position_embeddings=64, use_cache=False,
+                      attention_dropout=0.0)
+    return LlamaForCausalLM(cfg), "self_attn,mlp", 2 * 7
+
+
+@pytest.mark.parametrize("family", ["gpt_neox", "llama"])
+def test_gradproj_engine_on_hf_decoders_bf16(tmp_path, family):
+    """``transformers.GPTNeoXForCausalLM`` / ``LlamaForCausalLM`` (small configurations, bf16) through
+    ``GradProjLoraEngine``: every projected Linear's slice equals the float64 oracle on the (A, B)
+    pair its hook saw, and the run with ``freeze_weights=True`` (autograd computes activation
+    gradients only) gives the same projections and leaves the model as it found it."""
+    from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoraEngine
+    torch.manual_seed(6)
+    model, patterns, n_layers = _hf_decoder(family)
+    model = model.bfloat16().cuda()
+    ids = torch.randint(0, 320, (4, 48)).cuda()
+    flags = {n: p.requires_grad for n, p in model.named_parameters()}
+    outs = {}
+    for frozen in (False, True):
+        with contextlib.redirect_stdout(io.StringIO()):
+            eng = GradProjLoraEngine(model, proj_layers=patterns, proj_rank_total=64, proj_rank_min=4,
+                                     proj_seed=11, proj_dtype="float32", proj_dir=str(tmp_path / f"f{int(frozen)}"),
+                                     proj_save_interval=1, proj_dims_override=(8, 8), freeze_weights=frozen)
+            eng.attach()
+        assert len(eng.matched_layers) == n_layers
+        if frozen:
+            trainable = [n for n, p in model.named_parameters() if p.requires_grad]
+            assert trainable and all("dummy_bias" in n for n in trainable)
+        cap, handles = {}, []
+        for name, layer in eng.matched_layers.items():
+            handles.append(layer.register_forward_hook(
+                lambda l, i, o, n=name: cap.setdefault(n, {}).__setitem__("A", i[0].detach().cpu())))
+            handles.append(layer.register_full_backward_hook(
+                lambda l, gi, go, n=name: cap[n].__setitem__("B", go[0].detach().cpu())))
+        model.zero_grad(set_to_none=True)
+        model(input_ids=ids, labels=ids).loss.backward()
+        proj = eng.collect_batch(batch_indices=list(range(4)))
+        eng.flush()
+        assert proj.shape == (4, n_layers * 64)
+        for name in sorted(eng.matched_layers):
+            P_i, P_o = eng.projection_matrices[name]
+            lo, hi = eng.slice_ranges[name]
+            ref = O.gradproj_dense(cap[name]["A"], cap[name]["B"], P_i.cpu(), P_o.cpu(),
+                                   compute_dtype=torch.float64)
+            assert O.rel_fro(proj[:, lo:hi].reshape(ref.shape), ref) < 2e-2, (frozen, name)
+        if frozen:      # no weight gradient was computed
+            assert all(p.grad is None for n, p in model.named_parameters() if "dummy_bias" not in n)
+        outs[frozen] = proj.cpu()
+        for h in handles:
+            h.remove()
+        eng.cleanup()
+        assert {n: p.requires_grad for n, p in model.named_parameters()} == flags      # restored, dummy bias gone
+    # same math in both runs; the attention backward of the model may order its sums differently
+    assert O.rel_fro(outs[True], outs[False]) < 5e-3
 
 
 def test_manager_facade(tmp_path):

@@ -102,24 +102,49 @@ def test_ghost_linear_microbenchmark_shape_full_size():
     assert rel(M_per, M[:8, :24]) < 5e-3
 
 
-def test_gradproj_llama_q_proj_shape_full_size():
-    """Llama-3-8B q_proj: 8 sequences of 4096 tokens, 4096 -> 4096, k_i = k_o = 64, bf16."""
-    B, T, n, k = 8, 4096, 4096, 64
-    g = torch.Generator(device="cuda").manual_seed(5)
-    A = (torch.randn(B, T, n, generator=g, device="cuda") / n ** 0.5).bfloat16()
-    G = (torch.randn(B, T, n, generator=g, device="cuda") / n ** 0.5).bfloat16()
-    P_i = torch.randn(k, n, generator=g, device="cuda") / k ** 0.5
-    P_o = torch.randn(k, n, generator=g, device="cuda") / k ** 0.5
+def _gradproj_case(B, T, n_i, n_o, k, seed, conv1d=False):
+    """One GradProj call at a configuration's full size against the float64 oracle evaluated with the
+    float32 projection matrices (the kernel's one-time bf16 rounding of P is inside the check)."""
+    from oracle import ghost_oracle as O
+    torch.cuda.empty_cache()
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    A = (torch.randn(B, T, n_i, generator=g, device="cuda") / n_i ** 0.5).bfloat16()
+    G = (torch.randn(B, T, n_o, generator=g, device="cuda") / n_o ** 0.5).bfloat16()
+    P_i = torch.randn(k, n_i, generator=g, device="cuda") / k ** 0.5          # float32, N(0, 1/k)
+    P_o = torch.randn(k, n_o, generator=g, device="cuda") / k ** 0.5
     Pi, Po = ops().prepare_projection(P_i, False), ops().prepare_projection(P_o, False)
     out = torch.empty(B, k * k, device="cuda")
     ops().gradproj_dense(G, A, Po, Pi, k, k, float(B), out)
     after()
-    ref = torch.stack([(G[b].float() @ Po.float().t()).t() @ (A[b].float() @ Pi.float().t()) for b in range(B)])
-    assert rel(out.view(B, k, k), ref * B) < 1e-3
+    # one sample at a time keeps the float64 copies of the operands small
+    ref = torch.cat([O.gradproj_dense(A[b:b + 1], G[b:b + 1], P_i, P_o, compute_dtype=torch.float64)
+                     for b in range(B)]).double() * B
+    err = rel(out.view(B, k, k), ref)
+    assert err < 2e-2, err
     out2 = torch.empty(B, k * k, device="cuda")
     ops().gradproj_dense((G.float() * 0.5).bfloat16(), A, Po, Pi, k, k, float(B), out2)
     after()
     assert rel(out2, 0.5 * out) < 1e-5                    # linear in the out-grad (exact power of two)
+    return err
+
+
+def test_gradproj_llama_q_proj_shape_full_size():
+    """Llama-3-8B q_proj: 8 sequences of 4096 tokens, 4096 -> 4096, k_i = k_o = 64, bf16."""
+    _gradproj_case(8, 4096, 4096, 4096, 64, seed=5)
+
+
+@pytest.mark.parametrize("n_i,n_o", [(4096, 14336), (14336, 4096), (4096, 1024)],
+                         ids=["gate_up_proj", "down_proj", "kv_proj"])
+def test_gradproj_llama_other_shapes_full_size(n_i, n_o):
+    """The other Linear shapes of a Llama-3-8B block (SwiGLU 14336, 8 KV heads) at 8 x 4096 tokens, k = 64."""
+    _gradproj_case(8, 4096, n_i, n_o, 64, seed=8)
+
+
+@pytest.mark.parametrize("n_i,n_o", [(1024, 4096), (4096, 1024), (1024, 3072), (1024, 1024)],
+                         ids=["dense_h_to_4h", "dense_4h_to_h", "query_key_value", "attention_dense"])
+def test_gradproj_pythia_shapes_full_size(n_i, n_o):
+    """Pythia-410M-shaped Linears at the configuration's 16 x 2048 tokens, k_i = k_o = 32."""
+    _gradproj_case(16, 2048, n_i, n_o, 32, seed=9)
 
 
 def test_layernorm_and_bias_gpt2_shape_full_size():
@@ -161,3 +186,89 @@ def test_embedding_gpt2_vocab_full_size():
     table.index_add_(0, ids[:n_t].reshape(-1), (G[:n_t] * float(n_t + n_v)).reshape(-1, d))
     ref = table / float(n_t)
     assert torch.equal(grad.cpu().view(torch.int16), ref.view(torch.int16))
+
+
+def make_gpu_chunked(N, T, d, p, seed):
+    """Like make_gpu, drawn one sample at a time so that no float32 copy of a whole operand exists
+    (the 4096 -> 11008 layer at 288 x 8192 tokens holds 71 GB of bf16 operands)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    A = torch.empty(N, T, d, dtype=torch.bfloat16, device="cuda")
+    G = torch.empty(N, T, p, dtype=torch.bfloat16, device="cuda")
+    for s in range(N):
+        A[s] = torch.randn(T, d, generator=g, device="cuda") / d ** 0.5
+        G[s] = torch.randn(T, p, generator=g, device="cuda") / p ** 0.5
+    return A, G
+
+
+def seeded_pairs(n_v, n_t, vals, trains, seed):
+    """vals x trains (validation, train) index pairs from a seeded draw without replacement."""
+    g = torch.Generator().manual_seed(seed)
+    vs = torch.randperm(n_v, generator=g)[:vals].tolist()
+    bs = torch.randperm(n_t, generator=g)[:trains].tolist()
+    return [(v, b) for v in vs for b in bs]
+
+
+@pytest.mark.parametrize("name,d,p,linear", [
+    ("attn.c_attn", 768, 2304, False), ("attn.c_proj", 768, 768, False),
+    ("mlp.c_proj", 3072, 768, False), ("lm_head", 768, 50304, True)])
+def test_gpt2_other_layer_shapes_full_size(name, d, p, linear):
+    """The remaining dense layers of the GPT-2-small step at 32 train + 8 validation sequences of 1024
+    tokens: both dot-product paths against float64 values of 16 seeded pairs, and the train gradient
+    of the per-sample pass against a float32 GEMM.  Conv1D layers store [d_in, d_out] (X = A), the
+    head is an nn.Linear with [d_out, d_in] (X = out-grad), as the engine calls them."""
+    n_t, n_v, T = 32, 8, 1024
+    torch.cuda.empty_cache()
+    A, G = make_gpu_chunked(n_t + n_v, T, d, p, seed=11)
+    X, Y = (G, A) if linear else (A, G)
+    M_per, grad = ops().persample_dot(X, Y, n_v, want_grad=True, grad_scale=1.0, grad_dtype=torch.float32)
+    M_gram = ops().gram_dot(A, G, n_v)
+    after()
+    assert torch.isfinite(M_per).all() and torch.isfinite(M_gram).all()
+    assert rel(M_per, M_gram) < 5e-3
+    pairs = seeded_pairs(n_v, n_t, 4, 4, seed=12)
+    want = exact_pairs(A, G, n_t, pairs)
+    assert rel(torch.stack([M_per[v, b] for v, b in pairs]), want) < 2e-2
+    assert rel(torch.stack([M_gram[v, b] for v, b in pairs]), want) < 2e-2
+    Xt, Yt = X[:n_t].reshape(-1, X.shape[-1]), Y[:n_t].reshape(-1, Y.shape[-1])
+    ref = Xt.float().t() @ Yt.float()
+    assert rel(grad, ref) < 5e-3
+    # the split-K train-gradient kernel on the same operands (fp32 accumulation throughout)
+    W = ops().wgrad(X[:n_t], Y[:n_t], 1.0, torch.float32)
+    after()
+    assert rel(W, ref) < 1e-3
+
+
+@pytest.mark.parametrize("T,gram", [(512, True), (2048, False), (8192, False)])
+def test_ghost_linear_microbenchmark_long_sequences_full_size(T, gram):
+    """Single layer 4096 -> 11008 with 256 train and 32 validation samples (bf16) at T = 512, 2048 and
+    8192: the per-sample path (the product path at these lengths) against float64 values of 64 seeded
+    (validation, train) pairs; at T = 512 the Gram kernel as well.  At T = 8192 the operands hold
+    71 GB and every sample's token block starts beyond 2^31 elements for most samples, which is what
+    this case is for."""
+    n_t, n_v, d, p = 256, 32, 4096, 11008
+    torch.cuda.empty_cache()
+    A, G = make_gpu_chunked(n_t + n_v, T, d, p, seed=13)
+    M_per, grad = ops().persample_dot(G, A, n_v, want_grad=True, grad_scale=1.0, grad_dtype=torch.float32)
+    after()
+    assert M_per.shape == (n_v, n_t) and torch.isfinite(M_per).all()
+    pairs = seeded_pairs(n_v, n_t, 8, 8, seed=14)          # 64 pairs, 16 float64 per-sample gradients
+    want = exact_pairs(A, G, n_t, pairs)
+    got = torch.stack([M_per[v, b] for v, b in pairs])
+    assert rel(got, want) < 2e-2
+    # the last train and the last validation sample sit at the far end of the buffers
+    far = exact_pairs(A, G, n_t, [(n_v - 1, n_t - 1)])
+    assert rel(M_per[n_v - 1, n_t - 1].reshape(1), far) < 2e-2
+    # train gradient: the per-sample pass sums bf16 tiles; check it on a seeded set of output rows
+    # against float64 (a full float32 GEMM reference would need a 105 GB float32 copy at T = 8192)
+    rows = torch.randperm(p, generator=torch.Generator().manual_seed(15))[:64].cuda()
+    ref = torch.zeros(64, d, dtype=torch.float64, device="cuda")
+    for s in range(n_t):
+        ref += G[s][:, rows].double().t() @ A[s].double()
+    assert rel(grad[rows], ref) < 1e-2
+    if gram:
+        M_gram = ops().gram_dot(A, G, n_v)
+        after()
+        assert rel(M_gram, M_per) < 5e-3
+        assert rel(torch.stack([M_gram[v, b] for v, b in pairs]), want) < 2e-2
+    del A, G
+    torch.cuda.empty_cache()

@@ -80,3 +80,13 @@ def test_flat_projection_file_round_trip(tmp_path):
     assert index["batches"][2]["batch_idx"] == [200, 201, 202, 203, 204]
     assert np.array_equal(np.asarray(data), torch.cat(rows).numpy())
     eng.cleanup()
+
+
+def test_choose_ki_ko_reproduces_the_reference_table(golden):
+    """``choose_ki_ko`` against the (n_i, n_o, k_total, k_min) -> (k_i, k_o) rows that the golden
+    script recorded from the reference's projection_utils.choose_ki_ko (:12-66 there)."""
+    from ghostsuite_b200.ghostEngines.gradProjection.projection_utils import choose_ki_ko
+    table = golden["choose_ki_ko_table"]
+    assert table.shape[0] >= 7
+    for n_i, n_o, k_total, k_min, k_i, k_o in table.tolist():
+        assert choose_ki_ko(n_i, n_o, k_total, k_min) == (k_i, k_o), (n_i, n_o, k_total, k_min)
