@@ -17,6 +17,10 @@ shards.
 
 GradProj shards the corpus (:func:`shard_indices`) and needs no communication at all.
 
+With :func:`shard_validation` the validation batch is split over the ranks as well: every rank runs
+``cat(train_shard, val_shard)`` through the model, and in each hooked layer the other ranks'
+validation rows of the two operands are all-gathered into local buffers before the kernels run.
+
 Only ``torch.distributed`` collectives on local buffers are used (NCCL on GPUs, gloo in the CPU
 tests); no kernel reads another GPU's memory.
 """
@@ -60,7 +64,8 @@ def _dot_params(module: torch.nn.Module) -> List[Tuple[str, torch.Tensor]]:
 
 def gather_dot_products(module: torch.nn.Module, group=None,
                         single_process_equivalent: bool = True,
-                        check_equal_shards: bool = True) -> Dict[str, torch.Tensor]:
+                        check_equal_shards: bool = True,
+                        n_val_local: Optional[int] = None) -> Dict[str, torch.Tensor]:
     """All-gather every parameter's ``[n_val, n_train_local]`` block along the train dimension
     (equal shard sizes) and store the global ``[n_val, n_train_global]`` matrix (and its column sums)
     back on the parameter.  One collective for all parameters, preceded by a four-integer MIN
@@ -86,7 +91,8 @@ def gather_dot_products(module: torch.nn.Module, group=None,
     dist.all_gather_into_tensor(gathered, packed.contiguous(), group=group)
     full = gathered.view(world, P, n_val, n_loc).permute(1, 2, 0, 3).reshape(P, n_val, world * n_loc)
     if single_process_equivalent:
-        n_local = n_val + n_loc
+        # samples in this rank's loss mean against samples in the single-process loss mean
+        n_local = (n_val if n_val_local is None else int(n_val_local)) + n_loc
         n_global = n_val + world * n_loc
         full = full * (float(n_local) / float(n_global)) ** 2
     vectors = full.sum(dim=1)                      # one reduction for all parameters
@@ -251,6 +257,61 @@ class OverlappedGradSync:
         return calls
 
 
+class ShardedValidation:
+    """Splits the validation batch over the ranks.
+
+    Rank ``r`` runs ``cat(train_shard_r, val[r * v : (r + 1) * v])`` (``v = n_val / world``) through the
+    model, with the engine built for ``val_batch_size = v``.  In every hooked layer's backward hook this
+    object replaces the layer's operands ``A`` and ``B`` (``[n_train_local + v, ...]``) by
+    ``cat(train rows, all ranks' validation rows)`` -- one ``all_gather_into_tensor`` per operand
+    straight into the tail of a new local buffer -- and reports ``n_val`` validation samples, so the
+    layer functions and kernels work exactly as with a replicated validation batch while the model's
+    forward and backward pass cover ``1 / world`` of it.  Every rank's loss is a mean over the same
+    number of samples, so all gathered out-grads carry the same factor.
+    """
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.calls = 0
+        self.bytes = 0
+
+    def __call__(self, layer, A: torch.Tensor, B: torch.Tensor, n_val_local: int):
+        if self.world == 1:
+            return A, B, n_val_local
+        n_train = A.shape[0] - n_val_local
+        if n_train <= 0 or n_val_local <= 0 or B.shape[0] != A.shape[0]:
+            raise ValueError("sharded validation needs train and validation rows in every rank's batch")
+        out = []
+        for x in (A, B):
+            x = x.contiguous()
+            full = x.new_empty((n_train + n_val_local * self.world,) + tuple(x.shape[1:]))
+            full[:n_train].copy_(x[:n_train])
+            dist.all_gather_into_tensor(full[n_train:], x[n_train:], group=self.group)
+            self.calls += 1
+            self.bytes += full[n_train:].numel() * full.element_size()
+            out.append(full)
+        return out[0], out[1], n_val_local * self.world
+
+
+def shard_validation(engine, group=None) -> ShardedValidation:
+    """Install :class:`ShardedValidation` for the hooks of ``engine`` (built with the per-rank
+    validation count).  Pass ``n_val_local`` to :func:`sync_engine` afterwards; undo with
+    :func:`unshard_validation`."""
+    from .ghostEngines import autograd_grad_sample_dotprod as plumbing
+    sv = ShardedValidation(group)
+    plumbing.VALIDATION_GATHER = sv
+    engine._ghost_val_shard = sv
+    return sv
+
+
+def unshard_validation(engine=None) -> None:
+    from .ghostEngines import autograd_grad_sample_dotprod as plumbing
+    plumbing.VALIDATION_GATHER = None
+    if engine is not None and hasattr(engine, "_ghost_val_shard"):
+        del engine._ghost_val_shard
+
+
 def overlap_train_grad_sync(engine, group=None, bucket_bytes: int = 32 << 20) -> OverlappedGradSync:
     """Start all-reducing finished train gradients during the backward pass; :func:`sync_engine`
     then only has to wait for them.  Call once after ``engine.attach``."""
@@ -259,9 +320,11 @@ def overlap_train_grad_sync(engine, group=None, bucket_bytes: int = 32 << 20) ->
     return sync
 
 
-def sync_engine(engine, group=None, single_process_equivalent: bool = True) -> None:
+def sync_engine(engine, group=None, single_process_equivalent: bool = True,
+                check_equal_shards: bool = True) -> None:
     """Call between ``loss.backward()`` and ``engine.prepare_gradients()`` on every rank."""
-    gather_dot_products(engine.module, group, single_process_equivalent)
+    n_val_local = engine.val_batch_size if getattr(engine, "_ghost_val_shard", None) is not None else None
+    gather_dot_products(engine.module, group, single_process_equivalent, check_equal_shards, n_val_local)
     overlapped = getattr(engine, "_ghost_grad_sync", None)
     if overlapped is not None:
         overlapped.finish()

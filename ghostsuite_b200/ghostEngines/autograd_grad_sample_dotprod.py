@@ -26,6 +26,14 @@ from .supported_layers_grad_samplers_dotprod import (
 )
 
 
+#: optional ``fn(layer, A, B, n_val_local) -> (A_full, B_full, n_val_global)`` applied to every hooked
+#: layer's operands before its layer functions run.  The data-parallel layer installs one when the
+#: validation batch is split over ranks: it appends the other ranks' validation rows (an all-gather
+#: into local memory), so the kernels see ``cat(train_local, val_global)`` without every rank having
+#: run the whole validation batch through the model.
+VALIDATION_GATHER = None
+
+
 def requires_grad(module: nn.Module) -> bool:
     """True if any parameter of ``module`` was trainable when the engine was built."""
     return any(getattr(p, "initially_requires_grad", p.requires_grad) for p in module.parameters())
@@ -94,8 +102,13 @@ def _prepare_sample_grad_or_dotprod(layer: nn.Module, grad_output: Tuple[torch.T
         backprops = backprops.to(common)
         layer.activations = A
 
-    # 'mean' losses carry a 1/batch factor; the train-gradient kernels undo it in their epilogue
+    # 'mean' losses carry a 1/batch factor (the batch this process ran); the train-gradient kernels
+    # undo it in their epilogue
     layer._ghost_backprop_scale = float(backprops.shape[0]) if loss_reduction == "mean" else 1.0
+    if VALIDATION_GATHER is not None and A is not None:
+        A, backprops, val_batch_size = VALIDATION_GATHER(layer, A, backprops, val_batch_size)
+        layer.activations = A
+    layer._ghost_val_batch = val_batch_size
     # the per-parameter [n_train] vectors are reduced in one batched op when the backward pass ends
     if _layers.begin_deferred_dots():
         try:
@@ -113,6 +126,7 @@ def _prepare_sample_grad_or_dotprod(layer: nn.Module, grad_output: Tuple[torch.T
 def _apply_train_grad(layer: nn.Module, val_batch_size: int, loss_reduction: str = "mean"):
     """Backward hook, part 2: averaged train gradients into ``param.train_grad`` (reference :140-196)."""
     _, train_grad_fn = _supported_layers_dotprod.get(type(layer), (None, None))
+    val_batch_size = layer.__dict__.get("_ghost_val_batch", val_batch_size)
     if not train_grad_fn:
         raise ValueError(
             f"Layer {layer.__class__.__name__} is not supported for training gradient computation. "
@@ -134,7 +148,7 @@ def _apply_train_grad(layer: nn.Module, val_batch_size: int, loss_reduction: str
                 grad_bias = _train_grad_bias_from_layer(layer, val_batch_size, loss_reduction)
                 _create_or_accumulate_train_grad(bias, grad_bias)
     finally:
-        for attr in ("activations", "backprops", "_ghost_backprop_scale", "_ghost_colsums",
+        for attr in ("activations", "backprops", "_ghost_backprop_scale", "_ghost_val_batch", "_ghost_colsums",
                      "_ghost_cached_train_grad", "_ghost_ln_cache", "_ghost_conv_tokens"):
             layer.__dict__.pop(attr, None)
 

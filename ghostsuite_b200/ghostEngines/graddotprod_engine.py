@@ -42,7 +42,13 @@ class GradDotProdEngine:
 
         # remember what was trainable; in dummy-bias mode autograd then only computes
         # activation gradients (the hooks produce every weight gradient themselves)
-        for _, param in module.named_parameters():
+        for name, param in module.named_parameters():
+            if name.endswith("dummy_bias"):
+                # left behind by an earlier engine on the same model: it is what keeps the autograd
+                # graph alive in dummy-bias mode, so it stays trainable
+                param.initially_requires_grad = True
+                param.requires_grad = True
+                continue
             param.initially_requires_grad = bool(param.requires_grad)
             param.requires_grad = not use_dummy_bias
         transformers_support.forward_swapper(module=module)

@@ -189,6 +189,49 @@ def test_overlapped_sync_with_two_backward_passes():
     assert _run_ranks(_worker_two_backwards) == [(0, True), (1, True)]
 
 
+def _worker_val_shard(rank, world, port, q):
+    """Validation batch split over ranks: after the per-layer gather every rank holds
+    cat(own train rows, all validation rows), and the blocks it computes, gathered and rescaled,
+    reproduce the single-process matrix over the global batch."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import ghost_oracle as O
+        g = torch.Generator().manual_seed(3)
+        n_t, n_v, T, d, p = 4, 2, 5, 6, 7
+        A = torch.randn(n_t + n_v, T, d, generator=g)            # the global batch, train first
+        G = torch.randn(n_t + n_v, T, p, generator=g)
+        ids = torch.randint(0, 50, (n_t + n_v, T), generator=g)
+        t_lo, t_hi = gdist.shard_bounds(n_t, rank, world)
+        v_lo, v_hi = gdist.shard_bounds(n_v, rank, world)
+        rows = list(range(t_lo, t_hi)) + list(range(n_t + v_lo, n_t + v_hi))
+        n_global, n_local = n_t + n_v, len(rows)
+        # a mean loss over the local batch makes every local out-grad n_global / n_local times larger
+        G_loc = G[rows] * (n_global / n_local)
+        sv = gdist.ShardedValidation(None)
+        A_full, G_full, nv = sv(None, A[rows], G_loc, v_hi - v_lo)
+        ok = nv == n_v and A_full.shape[0] == (t_hi - t_lo) + n_v
+        ok = ok and torch.equal(A_full, torch.cat((A[t_lo:t_hi], A[n_t:])))
+        ok = ok and torch.allclose(G_full, torch.cat((G[t_lo:t_hi], G[n_t:])) * (n_global / n_local))
+        ids_full, _, _ = sv(None, ids[rows], G_loc, v_hi - v_lo)
+        ok = ok and ids_full.dtype == torch.int64 and torch.equal(ids_full, torch.cat((ids[t_lo:t_hi], ids[n_t:])))
+        # the local block -> gathered, rescaled -> the global matrix
+        lin = nn.Linear(d, p, bias=False)
+        lin.weight.initially_requires_grad = True
+        lin.weight.grad_dot_prod_matrix = O.linear_dot_exact(A_full, G_full, n_v).float()
+        full = gdist.gather_dot_products(lin, None, n_val_local=v_hi - v_lo)["weight"]
+        want = O.linear_dot_exact(A, G, n_v)
+        ok = ok and full.shape == (n_v, n_t) and float((full.double() - want).norm() / want.norm()) < 1e-5
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_validation_gather():
+    assert _run_ranks(_worker_val_shard) == [(0, True), (1, True)]
+
+
 def test_shard_bounds_cover_everything():
     for n in (1, 7, 8, 65536):
         for world in (1, 2, 3, 8):
