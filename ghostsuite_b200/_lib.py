@@ -17,8 +17,16 @@ GHOST_ERR_INVALID = -1
 GHOST_ERR_CUDA = -2
 GHOST_ERR_DEVICE = -3
 GHOST_ERR_KERNEL_TIMEOUT = -4
+GHOST_ERR_INDEX = -5
 
 _vp, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+
+
+class SmallJob(C.Structure):
+    """``ghost_small_job`` of include/ghost_b200.h."""
+    _fields_ = [("X", _vp), ("M", _vp), ("sum_out", _vp), ("n_train", _i), ("n_val", _i), ("F", _i),
+                ("sum_is_f32", _i), ("dot_scale", _f), ("sum_scale", _f)]
+
 
 # name -> (restype, argtypes); mirrors include/ghost_b200.h one to one
 PROTOTYPES = {
@@ -44,12 +52,16 @@ PROTOTYPES = {
     "ghost_rmsnorm_persample": (_i, [_vp, _vp, _i, _i, _ll, _i, _f, _vp, _vp, _vp, _ll, _vp]),
     "ghost_small_gram_f32": (_i, [_vp, _i, _i, _i, _f, _vp, _vp]),
     "ghost_rows_sum": (_i, [_vp, _i, _i, _f, _vp, _i, _i, _vp]),
+    "ghost_small_reduce_batch": (_i, [C.POINTER(SmallJob), _i, _vp]),
     "ghost_embedding_dot_workspace_bytes": (_ll, [_i, _ll, _i]),
     "ghost_embedding_dot": (_i, [_vp, _vp, _i, _i, _i, _ll, _i, _i, _f, _vp, _vp, _ll, _vp]),
     "ghost_embedding_dot_noalloc": (_i, [_vp, _vp, _i, _i, _i, _ll, _i, _i, _f, _vp, _vp]),
     "ghost_embedding_wgrad_workspace_bytes": (_ll, [_i, _ll, _i]),
     "ghost_embedding_wgrad": (_i, [_vp, _vp, _i, _i, _ll, _i, _i, _f, _f, _i, _vp, _vp, _ll, _vp]),
     "ghost_gradproj_dense_bf16": (_i, [_vp, _vp, _i, _ll, _i, _i, _ll, _ll, _vp, _vp, _i, _i, _ll, _ll, _f, _vp, _ll, _vp]),
+    "ghost_gradproj_embedding": (_i, [_vp, _vp, _i, _i, _ll, _i, _ll, _vp, _ll, _i, _i, _vp, _ll, _i, _i, _i, _f,
+                                      _i, _vp, _ll, _i, _vp]),
+    "ghost_projection_similarity": (_i, [_vp, _vp, _i, _i, _i, _ll, _ll, _ll, _f, _vp, _ll, _vp]),
     "ghost_workload_ce_forward": (_i, [_vp, _i, _ll, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp]),
     "ghost_workload_ce_rescale": (_i, [_vp, _i, _ll, _i, _vp, _vp]),
     "ghost_workload_ce_backward": (_i, [_vp, _i, _ll, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp]),
@@ -91,6 +103,8 @@ def check(status: int) -> None:
     msg = last_error()
     if status == GHOST_ERR_INVALID:
         raise ValueError(msg)
+    if status == GHOST_ERR_INDEX:
+        raise IndexError(msg)
     if status == GHOST_ERR_DEVICE:
         raise RuntimeError(f"ghostsuite_b200 needs a B200 (sm_100) GPU: {msg}")
     raise GhostKernelError(msg)

@@ -10,8 +10,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libghost_b200.so")
-SOURCES = ["common.cu", "ghost_gram.cu", "ghost_gram_pair.cu", "xty_gemm.cu", "xty_gemm_pair.cu", "tile_dot.cu", "rowwise.cu", "embedding.cu", "gradproj.cu", "workload_loss.cu"]
-HEADERS = ["common.cuh", "sm100_ptx.cuh", os.path.join("..", "..", "include", "ghost_b200.h")]
+SOURCES = ["common.cu", "ghost_gram.cu", "ghost_gram_pair.cu", "xty_gemm.cu", "xty_gemm_pair.cu", "tile_dot.cu", "rowwise.cu", "embedding.cu", "gradproj.cu", "proj_extras.cu", "workload_loss.cu"]
+HEADERS = ["common.cuh", "sm100_ptx.cuh", "mma_sync.cuh", os.path.join("..", "..", "include", "ghost_b200.h")]
 
 
 def _nvcc() -> str:
@@ -37,8 +37,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-             "-Xcompiler", "-fPIC", "--use_fast_math=false"]
-    flags = [f for f in flags if f != "--use_fast_math=false"]
+             "-Xcompiler", "-fPIC"]
     if verbose:
         flags += ["-Xptxas", "-v"]
     objs = []

@@ -231,12 +231,16 @@ int ghost_poll_kernel_error(int clear) {
     return gb::fail(GHOST_ERR_CUDA, "reading the kernel error word failed: %s",
                     cudaGetErrorString(cudaGetLastError()));
   if (v != 0) {
-    gb::set_error("a kernel gave up a bounded wait (code %d: role %d, barrier kind %d)", v, v / 100,
-                  v % 100);
     if (clear) {
       int zero = 0;
       cudaMemcpy(s->err_word, &zero, sizeof(int), cudaMemcpyHostToDevice);
     }
+    if (v == 9001) {      // kErrBadIndex of the embedding-projection kernel
+      gb::set_error("an embedding id outside [0, vocab) reached a kernel (its contribution was skipped)");
+      return GHOST_ERR_INDEX;
+    }
+    gb::set_error("a kernel gave up a bounded wait (code %d: role %d, barrier kind %d)", v, v / 100,
+                  v % 100);
     return GHOST_ERR_KERNEL_TIMEOUT;
   }
   return GHOST_OK;

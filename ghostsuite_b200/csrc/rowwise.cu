@@ -397,9 +397,87 @@ __global__ void rows_sum_kernel(const float* __restrict__ X, int n_rows, int F, 
   out[c] = static_cast<OutT>(s);
 }
 
+// Many small reductions in one launch: job j (blockIdx.y) is the pair of reductions the bias /
+// LayerNorm / RMS-norm terms of one layer need on its per-sample vectors X[n_train + n_val, F]:
+//   M[v, b]  = dot_scale * <X[n_train + v], X[b]>          (if M != null)
+//   sum[c]   = sum_scale * sum_{b < n_train} X[b, c]       (if sum_out != null)
+// A backward pass of a GPT-2-sized model has about a hundred of these, each a few microseconds of
+// work; the jobs travel as kernel parameters (by value), so the launch is self-contained.
+static constexpr int kSmallJobsPerLaunch = 48;
+struct SmallJobs {
+  ghost_small_job job[kSmallJobsPerLaunch];
+};
+
+__global__ void __launch_bounds__(256) small_reduce_batch_kernel(const __grid_constant__ SmallJobs jobs) {
+  const ghost_small_job& j = jobs.job[blockIdx.y];
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * 8;
+  const float* X = j.X;
+  const int F = j.F;
+  if (j.M != nullptr) {
+    const int pairs = j.n_train * j.n_val;
+    const bool vec = (F & 3) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0;
+    for (int pair = blockIdx.x * 8 + (threadIdx.x >> 5); pair < pairs; pair += warps) {
+      const int v = pair / j.n_train, b = pair % j.n_train;
+      const float* xv = X + static_cast<long long>(j.n_train + v) * F;
+      const float* xb = X + static_cast<long long>(b) * F;
+      float s = 0.f;
+      if (vec) {
+        const float4* xv4 = reinterpret_cast<const float4*>(xv);
+        const float4* xb4 = reinterpret_cast<const float4*>(xb);
+        const int F4 = F >> 2;
+        float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll 4
+        for (int f = lane; f < F4; f += 32) {
+          const float4 a = __ldg(xv4 + f), c = __ldg(xb4 + f);
+          s = fmaf(a.x, c.x, s); s1 = fmaf(a.y, c.y, s1); s2 = fmaf(a.z, c.z, s2); s3 = fmaf(a.w, c.w, s3);
+        }
+        s = (s + s1) + (s2 + s3);
+      } else {
+        for (int f = lane; f < F; f += 32) s = fmaf(xv[f], xb[f], s);
+      }
+      s = warp_sum(s);
+      if (lane == 0) j.M[pair] = s * j.dot_scale;
+    }
+  }
+  if (j.sum_out != nullptr) {
+    for (int c = blockIdx.x * 256 + threadIdx.x; c < F; c += gridDim.x * 256) {
+      float s = 0.f;
+#pragma unroll 8
+      for (int n = 0; n < j.n_train; ++n) s += __ldg(X + static_cast<long long>(n) * F + c);
+      s *= j.sum_scale;
+      if (j.sum_is_f32) static_cast<float*>(j.sum_out)[c] = s;
+      else static_cast<__nv_bfloat16*>(j.sum_out)[c] = __float2bfloat16_rn(s);
+    }
+  }
+}
+
 }  // namespace gb
 
 using namespace gb;
+
+extern "C" int ghost_small_reduce_batch(const ghost_small_job* jobs, int n_jobs, void* stream) {
+  const DeviceState* ds = device_state();
+  if (!ds) return GHOST_ERR_DEVICE;
+  GB_REQUIRE(jobs != nullptr && n_jobs > 0, "ghost_small_reduce_batch: no jobs");
+  for (int i = 0; i < n_jobs; ++i) {
+    const ghost_small_job& j = jobs[i];
+    GB_REQUIRE(j.X != nullptr && (j.M != nullptr || j.sum_out != nullptr), "ghost_small_reduce_batch: job %d has no input or no output", i);
+    GB_REQUIRE(j.n_train > 0 && j.F > 0 && j.n_val >= 0 && (j.M == nullptr || j.n_val > 0),
+               "ghost_small_reduce_batch: job %d has an empty dimension", i);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int first = 0; first < n_jobs; first += kSmallJobsPerLaunch) {
+    const int n = (n_jobs - first < kSmallJobsPerLaunch) ? n_jobs - first : kSmallJobsPerLaunch;
+    SmallJobs batch = {};
+    for (int i = 0; i < n; ++i) batch.job[i] = jobs[first + i];
+    small_reduce_batch_kernel<<<dim3(8, n, 1), 256, 0, st>>>(batch);
+    count_launch();
+    const int rc = post_launch("small_reduce_batch_kernel");
+    if (rc != GHOST_OK) return rc;
+  }
+  return GHOST_OK;
+}
 
 extern "C" int ghost_cast_split_bf16(const void* src, int src_is_f32, long long samples, long long T,
                                      int cols, long long ld_src, void* dst, long long ld_dst, int cpad,

@@ -145,16 +145,16 @@ def _apply_train_grad(layer: nn.Module, val_batch_size: int, loss_reduction: str
                 _create_or_accumulate_train_grad(weight, grad_weight)
             bias = getattr(layer, "bias", None)
             if bias is not None and getattr(bias, "initially_requires_grad", bias.requires_grad):
-                grad_bias = _train_grad_bias_from_layer(layer, val_batch_size, loss_reduction)
-                _create_or_accumulate_train_grad(bias, grad_bias)
+                _train_grad_bias_from_layer(layer, val_batch_size, loss_reduction)
     finally:
         for attr in ("activations", "backprops", "_ghost_backprop_scale", "_ghost_val_batch", "_ghost_colsums",
                      "_ghost_cached_train_grad", "_ghost_ln_cache", "_ghost_conv_tokens"):
             layer.__dict__.pop(attr, None)
 
 
-def _train_grad_bias_from_layer(layer: nn.Module, val_batch_size: int, loss_reduction: str):
-    """Bias train gradient from the per-sample column sums the dot-product pass already made."""
+def _train_grad_bias_from_layer(layer: nn.Module, val_batch_size: int, loss_reduction: str) -> None:
+    """Bias train gradient from the per-sample column sums the dot-product pass already made, added to
+    ``layer.bias.train_grad`` (inside a backward pass: by the batched launch at its end)."""
     B = layer.backprops
     n_train = B.size(0) - val_batch_size
     if n_train <= 0:
@@ -168,7 +168,7 @@ def _train_grad_bias_from_layer(layer: nn.Module, val_batch_size: int, loss_redu
     if loss_reduction == "mean":
         scale /= n_train
     out_dtype = layer.bias.dtype if layer.bias.dtype in (torch.float32, torch.bfloat16) else torch.float32
-    return ops.rows_sum(colsums, n_train, scale, out_dtype)
+    _layers._train_grad_from_vectors(layer.bias, colsums, n_train, scale, out_dtype)
 
 
 def _compute_train_grad_bias(B: torch.Tensor, val_batch_size: int, loss_reduction: str = "mean") -> torch.Tensor:

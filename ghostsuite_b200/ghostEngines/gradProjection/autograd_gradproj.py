@@ -40,6 +40,7 @@ class GradProjHooks:
         self._handle_forward = None
         self._handle_backward = None
         self._kernel_P = {}       # split flag -> (P_i, P_o) in the kernel's bf16 layout
+        self._P_i_t = None        # embedding layers: float32 [vocab, k_i] transpose of P_i
         self._out_fn: Optional[Callable[[int], torch.Tensor]] = None
 
     # -- engine integration ------------------------------------------------------------------
@@ -49,8 +50,9 @@ class GradProjHooks:
 
     def _prepared(self, split: bool) -> Tuple[torch.Tensor, torch.Tensor]:
         if split not in self._kernel_P:
-            self._kernel_P[split] = (ops.prepare_projection(self.P_i, split),
-                                     ops.prepare_projection(self.P_o, split))
+            # an embedding's P_i [k_i, vocab] is gathered by token id, never multiplied: no bf16 copy
+            P_i = None if self.layer_type == "Embedding" else ops.prepare_projection(self.P_i, split)
+            self._kernel_P[split] = (P_i, ops.prepare_projection(self.P_o, split))
         return self._kernel_P[split]
 
     # -- hooks -----------------------------------------------------------------------------------
@@ -106,15 +108,23 @@ class GradProjHooks:
 
     def _compute_embedding_proj(self, module: nn.Module, indices: torch.Tensor,
                                 grad_output: torch.Tensor) -> None:
-        """Embedding projection ``sum_t (P_o g_t)(P_i[:, id_t])^T`` (reference :167-222).  Off by
-        default (``include_embeddings=False``) and not part of the kernel library: it is evaluated
-        with batched torch operations instead of the reference's per-token Python loop."""
+        """Embedding projection ``module._ghost_grad_proj[b] = sum_t (P_o g_t)(P_i[:, id_t])^T`` as
+        ``[B, k_o, k_i]`` float32 (reference :167-222, a Python loop over every token there): one
+        kernel that streams the out-grad rows once and gathers the rows of ``P_i^T`` by token id."""
         batch = indices.shape[0]
         ids = indices.reshape(batch, -1)
-        g = grad_output.reshape(batch, ids.shape[1], grad_output.shape[-1]).to(torch.float32)
-        g_proj = torch.matmul(g, self.P_o.t().to(g.device))                # [B, T, k_o]
-        cols = self.P_i.to(g.device).t()[ids]                              # [B, T, k_i]
-        module._ghost_grad_proj = torch.einsum("bto,bti->boi", g_proj, cols).to(torch.float32)
+        g = grad_output.reshape(batch, ids.shape[1], grad_output.shape[-1])
+        if g.dtype not in (torch.float32, torch.bfloat16):
+            g = g.float()
+        split = g.dtype == torch.float32
+        _, P_o = self._prepared(split)
+        if self._P_i_t is None:
+            self._P_i_t = ops.prepare_embedding_projection(self.P_i.to(g.device))
+        k_i, k_o = self.P_i.shape[0], self.P_o.shape[0]
+        out = self._out_fn(batch) if self._out_fn is not None else \
+            torch.empty((batch, k_o * k_i), dtype=torch.float32, device=g.device)
+        ops.gradproj_embedding(ids, g, P_o, self._P_i_t, k_o, k_i, 1.0, out)
+        module._ghost_grad_proj = out.view(batch, k_o, k_i)
 
     def attach(self, module: nn.Module) -> None:
         self._handle_forward = module.register_forward_hook(self.forward_hook_store_inputs)

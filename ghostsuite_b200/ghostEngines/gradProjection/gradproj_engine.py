@@ -245,8 +245,7 @@ class GradProjLoraEngine:
         for name, layer in self.matched_layers.items():
             P_i, P_o = self.projection_matrices[name]
             hooks = create_projection_hooks(layer, name, P_i, P_o)
-            if hooks.layer_type != "Embedding":
-                hooks.bind_output(self._slice_for(name))
+            hooks.bind_output(self._slice_for(name))
             hooks.attach(layer)
             self.hooks[name] = hooks
 

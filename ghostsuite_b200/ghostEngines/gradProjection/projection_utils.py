@@ -115,11 +115,18 @@ def compute_projection_metadata(layer_name: str, layer: nn.Module, k_i: int, k_o
 def projection_similarity(proj_a: torch.Tensor, proj_b: torch.Tensor) -> torch.Tensor:
     """Gradient-similarity scores ``proj_a @ proj_b.T`` between two sets of projected per-sample
     gradients (``[Na, D]``, ``[Nb, D]`` -> ``[Na, Nb]`` float32): the downstream step of the
-    reference's examples (Examples/ghost_gradproj_lm.py:190-196), done while the projections are
-    still on the device.  A plain dense GEMM, so it is the library's (cuBLAS through torch), in
-    full fp32 so that scores do not depend on the TF32 setting."""
+    reference's examples (Examples/ghost_gradproj_lm.py:190-196;
+    Examples/GradProj_LM/plot_error_with_dim.py:69-86), done while the projections are still on the
+    device.  Batch-sized blocks (up to ``ops.SIMILARITY_KERNEL_MAX_ROWS`` rows each: the
+    ``[B, total_proj_dim]`` buffers ``collect_batch`` returns) go through the library's streaming
+    kernel, which reads both operands once; larger sets are a plain dense GEMM and use cuBLAS
+    through torch, in full fp32 so that scores do not depend on the TF32 setting.  Host tensors
+    are multiplied on the host."""
     if proj_a.shape[-1] != proj_b.shape[-1]:
         raise ValueError("projection sets have different dimensions")
+    if proj_a.is_cuda and proj_b.is_cuda and proj_a.dim() == 2 and proj_b.dim() == 2 and \
+            max(proj_a.shape[0], proj_b.shape[0]) <= ops.SIMILARITY_KERNEL_MAX_ROWS:
+        return ops.projection_similarity(proj_a, proj_b)
     a, b = proj_a.float(), proj_b.float()
     if a.is_cuda:
         prev = torch.backends.cuda.matmul.allow_tf32

@@ -120,32 +120,84 @@ def _create_or_accumulate_train_grad(param: torch.Tensor, grad: torch.Tensor) ->
         TRAIN_GRAD_OBSERVER(param)
 
 
-# While a backward hook runs, the [n_train] vectors are not reduced one launch per parameter: the
-# (parameter, matrix) pairs are collected here and ``finalize_pending_dots`` reduces them all in one
-# batched op when the backward pass ends.  Direct callers of the layer functions get the vector at
-# once.
+# While a backward pass runs, two kinds of small work are not launched layer by layer but collected
+# and run when the pass ends (``finalize_pending_dots``, queued as an autograd callback by the hook
+# plumbing): the per-parameter [n_train] vectors (one stacked reduction per matrix shape), and the
+# bias / LayerNorm / RMS-norm terms' small reductions -- the [n_val, n_train] Gram of a layer's
+# per-sample vectors and the sum of its train rows -- which go out as ONE batched launch instead of
+# two launches per parameter.  Their output tensors exist from the moment the hook ran (the
+# parameter's ``grad_dot_prod_matrix`` is set at once) and are filled when the pass ends; train
+# gradients that come out of the batch are handed to ``_create_or_accumulate_train_grad`` after it.
+# Direct callers of the layer functions (no backward pass in flight) get everything at once.
 _PENDING_DOTS = None
+_PENDING_SMALL = None                 # list of job dicts for ops.small_reduce_batch
 _PENDING_LOCK = threading.Lock()      # backward hooks of different devices run on different threads
 
 
 def begin_deferred_dots() -> bool:
-    """Start collecting; returns True when this call opened the list (its caller must arrange for
+    """Start collecting; returns True when this call opened the lists (its caller must arrange for
     ``finalize_pending_dots`` to run)."""
-    global _PENDING_DOTS
+    global _PENDING_DOTS, _PENDING_SMALL
     with _PENDING_LOCK:
         if _PENDING_DOTS is not None:
             return False
         _PENDING_DOTS = []
+        _PENDING_SMALL = []
         return True
 
 
+def _small_job_for(X: torch.Tensor, n_train: int, n_val: int, want: str):
+    """The pending job on ``X`` whose ``want`` output ('M' or 'sum_out') is still free, or a new one
+    (the Gram and the row sum of one layer's vectors share a job).  None when nothing is deferred."""
+    with _PENDING_LOCK:
+        if _PENDING_SMALL is None:
+            return None
+        for job in reversed(_PENDING_SMALL[-4:]):
+            if job["X"] is X and job["n_train"] == n_train and job.get(want) is None:
+                return job
+        job = {"X": X, "n_train": n_train, "n_val": n_val}
+        _PENDING_SMALL.append(job)
+        return job
+
+
+def _gram_of_vectors(X: torch.Tensor, val_batch_size: int) -> torch.Tensor:
+    """``[n_val, n_train]`` Gram of per-sample vectors: at once, or as part of the batched launch at
+    the end of the backward pass in flight."""
+    n_train = X.shape[0] - val_batch_size
+    job = _small_job_for(X, n_train, val_batch_size, "M")
+    if job is None:
+        return ops.small_gram(X, val_batch_size)
+    M = torch.empty((val_batch_size, n_train), dtype=torch.float32, device=X.device)
+    job["M"], job["n_val"], job["dot_scale"] = M, val_batch_size, 1.0
+    return M
+
+
+def _train_grad_from_vectors(param: torch.Tensor, X: torch.Tensor, n_train: int, scale: float,
+                             out_dtype: torch.dtype) -> None:
+    """``param.train_grad (+)= scale * X[:n_train].sum(0)``: at once, or from the batched launch."""
+    job = _small_job_for(X, n_train, X.shape[0] - n_train, "sum_out")
+    if job is None:
+        _create_or_accumulate_train_grad(param, ops.rows_sum(X, n_train, scale, out_dtype))
+        return
+    out = torch.empty((X.shape[1],), dtype=out_dtype, device=X.device)
+    job["sum_out"], job["sum_scale"], job["param"] = out, scale, param
+
+
 def finalize_pending_dots() -> None:
-    """Set ``param.grad_dot_prod = param.grad_dot_prod_matrix.sum(0)`` for every collected parameter
-    with one stack + one reduction per matrix shape.  A tied parameter keeps its last matrix, as it
-    does when every hook overwrites the attribute.  Safe to call when nothing is pending."""
-    global _PENDING_DOTS
+    """Run the collected small reductions in one batched launch, hand their train gradients over,
+    then set ``param.grad_dot_prod = param.grad_dot_prod_matrix.sum(0)`` for every collected
+    parameter with one stack + one reduction per matrix shape.  A tied parameter keeps its last
+    matrix, as it does when every hook overwrites the attribute.  Safe to call when nothing is
+    pending."""
+    global _PENDING_DOTS, _PENDING_SMALL
     with _PENDING_LOCK:
         pending, _PENDING_DOTS = _PENDING_DOTS, None
+        small, _PENDING_SMALL = _PENDING_SMALL, None
+    if small:
+        ops.small_reduce_batch(small)
+        for job in small:
+            if job.get("param") is not None:
+                _create_or_accumulate_train_grad(job["param"], job["sum_out"].view_as(job["param"]))
     if not pending:
         return
     last = {}
@@ -214,7 +266,7 @@ def _bias_terms(layer: nn.Module, B: torch.Tensor, val_batch_size: int, colsums=
     per-sample GEMM pass can hand the sums over; otherwise they take one pass over B."""
     if colsums is None:
         colsums = ops.colsum(B)                   # [N, p] float32
-    _set_dot(layer.bias, ops.small_gram(colsums, val_batch_size))
+    _set_dot(layer.bias, _gram_of_vectors(colsums, val_batch_size))
     layer._ghost_colsums = colsums               # reused by the bias train gradient
 
 
@@ -339,9 +391,9 @@ def _compute_layernorm_dot_product(layer: nn.LayerNorm, A: torch.Tensor, B: torc
     if A.size(0) - val_batch_size <= 0:
         return
     gw, gb = _layernorm_vectors(layer, A, B)
-    _set_dot(layer.weight, ops.small_gram(gw, val_batch_size))
+    _set_dot(layer.weight, _gram_of_vectors(gw, val_batch_size))
     if layer.bias is not None:
-        _set_dot(layer.bias, ops.small_gram(gb, val_batch_size))
+        _set_dot(layer.bias, _gram_of_vectors(gb, val_batch_size))
 
 
 def _compute_layernorm_train_grad(layer: nn.LayerNorm, A: torch.Tensor, B: torch.Tensor,
@@ -353,9 +405,9 @@ def _compute_layernorm_train_grad(layer: nn.LayerNorm, A: torch.Tensor, B: torch
     gw, gb = _layernorm_vectors(layer, A, B)
     layer.__dict__.pop("_ghost_ln_cache", None)
     scale = _backprop_scale(layer) / n_train
-    _create_or_accumulate_train_grad(layer.weight, ops.rows_sum(gw, n_train, scale, layer.weight.dtype))
+    _train_grad_from_vectors(layer.weight, gw, n_train, scale, layer.weight.dtype)
     if layer.bias is not None:
-        _create_or_accumulate_train_grad(layer.bias, ops.rows_sum(gb, n_train, scale, layer.bias.dtype))
+        _train_grad_from_vectors(layer.bias, gb, n_train, scale, layer.bias.dtype)
     return None
 
 
@@ -387,7 +439,7 @@ def _compute_rmsnorm_dot_product(layer: nn.Module, A: torch.Tensor, B: torch.Ten
     """RMS norm: weight dot products from one pass over A and B."""
     if A.size(0) - val_batch_size <= 0:
         return
-    _set_dot(layer.weight, ops.small_gram(_rmsnorm_vectors(layer, A, B), val_batch_size))
+    _set_dot(layer.weight, _gram_of_vectors(_rmsnorm_vectors(layer, A, B), val_batch_size))
 
 
 def _compute_rmsnorm_train_grad(layer: nn.Module, A: torch.Tensor, B: torch.Tensor,
@@ -399,7 +451,7 @@ def _compute_rmsnorm_train_grad(layer: nn.Module, A: torch.Tensor, B: torch.Tens
     gw = _rmsnorm_vectors(layer, A, B)
     layer.__dict__.pop("_ghost_ln_cache", None)
     scale = _backprop_scale(layer) / n_train
-    _create_or_accumulate_train_grad(layer.weight, ops.rows_sum(gw, n_train, scale, layer.weight.dtype))
+    _train_grad_from_vectors(layer.weight, gw, n_train, scale, layer.weight.dtype)
     return None
 
 

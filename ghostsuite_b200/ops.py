@@ -373,6 +373,39 @@ def rows_sum(X: torch.Tensor, n_rows: int, scale: float, out_dtype: torch.dtype,
     return out
 
 
+def small_reduce_batch(jobs) -> None:
+    """Run many :func:`small_gram` / :func:`rows_sum` reductions in one launch (48 jobs per launch).
+    ``jobs``: dicts with ``X`` (contiguous float32 ``[n_train + n_val, F]``), ``n_train``, ``n_val`` and
+    optionally ``M`` (float32 ``[n_val, n_train]`` output, with ``dot_scale``) and ``sum_out``
+    (float32 / bfloat16 ``[F]`` output, with ``sum_scale``); the outputs are written in place."""
+    if not jobs:
+        return
+    lib = _lib.load()
+    arr = (_lib.SmallJob * len(jobs))()
+    nbytes = 0.0
+    for rec, job in zip(arr, jobs):
+        X = job["X"]
+        M, out = job.get("M"), job.get("sum_out")
+        _require_cuda(X)
+        if X.dtype != _F32 or X.dim() != 2 or not X.is_contiguous():
+            raise ValueError("small_reduce_batch takes contiguous float32 [N, F] tensors")
+        if M is not None and (M.dtype != _F32 or not M.is_contiguous()
+                              or M.numel() != job["n_val"] * job["n_train"]):
+            raise ValueError("small_reduce_batch: M must be a contiguous float32 [n_val, n_train] tensor")
+        if out is not None and (not out.is_contiguous() or out.numel() != X.shape[1]):
+            raise ValueError("small_reduce_batch: sum_out must be a contiguous [F] tensor")
+        rec.X = X.data_ptr()
+        rec.M = M.data_ptr() if M is not None else None
+        rec.sum_out = out.data_ptr() if out is not None else None
+        rec.n_train, rec.n_val, rec.F = int(job["n_train"]), int(job["n_val"]), int(X.shape[1])
+        rec.sum_is_f32 = _dt_flag(out) if out is not None else 1
+        rec.dot_scale = float(job.get("dot_scale", 1.0))
+        rec.sum_scale = float(job.get("sum_scale", 1.0))
+        nbytes += 4.0 * X.numel()
+    with _Timed("small_reduce_batch_kernel", "hbm", 0.0, nbytes):
+        _lib.check(lib.ghost_small_reduce_batch(arr, len(jobs), _stream_ptr()))
+
+
 def layernorm_persample(A: torch.Tensor, G: torch.Tensor, eps: float, rms: bool = False
                         ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-sample LayerNorm gamma/beta gradients ``([N, F], [N, F])`` float32 in one pass.  With
@@ -528,6 +561,88 @@ def gradproj_dense(G: torch.Tensor, A: torch.Tensor, P_r: torch.Tensor, P_c: tor
                                              out.stride(0), _stream_ptr()))
     timer.__exit__(None, None, None)
     return out
+
+
+def prepare_embedding_projection(P_i: torch.Tensor) -> torch.Tensor:
+    """``P_i [k_i, vocab]`` as the embedding-projection kernel reads it: float32 ``[vocab, k_i]``, so
+    that a token id selects one contiguous row (made once per layer)."""
+    _require_cuda(P_i)
+    return P_i.detach().to(_F32).t().contiguous()
+
+
+def gradproj_embedding(ids: torch.Tensor, G: torch.Tensor, P_o_prepared: torch.Tensor, P_i_t: torch.Tensor,
+                       k_o: int, k_i: int, scale: float = 1.0,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[b] = scale * sum_t (P_o g_bt)(P_i[:, id_bt])^T`` as ``[B, k_o*k_i]`` float32 (written into
+    ``out`` when given: a ``[B, >= k_o*k_i]`` row-major view, e.g. a column slice of the engine's
+    buffer).  ``P_o_prepared`` comes from :func:`prepare_projection` (split layout iff ``G`` is
+    float32), ``P_i_t`` from :func:`prepare_embedding_projection`."""
+    lib = _lib.load()
+    _require_cuda(ids, G, P_o_prepared, P_i_t)
+    ids = _ids2d(ids)
+    G = _as3d(G)
+    B, T, d = G.shape
+    if ids.shape[0] != B or ids.shape[1] != T:
+        raise RuntimeError("Batch size mismatch between token ids and output gradients")
+    split = G.dtype == _F32
+    cp = _pad8(d)
+    if P_o_prepared.dtype != _BF16 or P_o_prepared.shape[0] != k_o or P_o_prepared.shape[1] != (3 if split else 1) * cp:
+        raise ValueError("P_o was prepared for a different dtype/feature size")
+    if P_i_t.dtype != _F32 or P_i_t.dim() != 2 or P_i_t.shape[1] != k_i or not P_i_t.is_contiguous():
+        raise ValueError("P_i must be passed as the contiguous float32 [vocab, k_i] transpose")
+    if out is None:
+        out = torch.empty((B, k_o * k_i), dtype=_F32, device=G.device)
+    elif out.dtype != _F32 or out.dim() != 2 or out.shape[0] != B or out.stride(1) != 1 or out.shape[1] < k_o * k_i:
+        raise ValueError("embedding projection output must be a float32 [B, >= k_o*k_i] row-major view")
+    with _Timed("gradproj_embedding_kernel", "hbm", 2.0 * B * T * (d * k_o + k_o * k_i),
+                float(B) * T * (d * G.element_size() + 8 + 4 * k_i) + 4.0 * B * k_o * k_i):
+        # _SPLIT_RIGHT lays a float32 matrix out as (hi, hi, lo): the residual part starts at 2 * cp.
+        # The kernel covers up to 64 x 64 of a sample's block per launch; larger projections go
+        # block by block into the zeroed output.
+        chunked = k_o > 64 or k_i > 64
+        if chunked:
+            out[:, :k_o * k_i].zero_()
+        ld_po = P_o_prepared.shape[1]
+        for o0 in range(0, k_o, 64):
+            for i0 in range(0, k_i, 64):
+                _lib.check(lib.ghost_gradproj_embedding(
+                    ids.data_ptr(), G.data_ptr(), _dt_flag(G), B, T, d, d,
+                    P_o_prepared.data_ptr() + o0 * ld_po * 2, ld_po, cp, 2 * cp if split else 0,
+                    P_i_t.data_ptr() + i0 * 4, k_i, P_i_t.shape[0], min(64, k_o - o0), min(64, k_i - i0),
+                    float(scale), 1 if chunked else 0, out.data_ptr() + (o0 * k_i + i0) * 4,
+                    out.stride(0), k_i, _stream_ptr()))
+    return out
+
+
+#: largest block (rows of either operand) the similarity kernel is used for; beyond it the operands
+#: would be re-read once per 16 x 16 output block and a library GEMM is the better tool
+SIMILARITY_KERNEL_MAX_ROWS = 128
+
+
+def projection_similarity(P1: torch.Tensor, P2: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """``scale * P1 @ P2.T`` -> ``[n1, n2]`` float32 for two blocks of projection rows (float32 or
+    bfloat16, same dtype, unit stride along the projection dimension)."""
+    lib = _lib.load()
+    _require_cuda(P1, P2)
+    if P1.dim() != 2 or P2.dim() != 2 or P1.shape[1] != P2.shape[1]:
+        raise ValueError("projection sets have different dimensions")
+    if P1.dtype != P2.dtype:
+        common = torch.promote_types(P1.dtype, P2.dtype)
+        P1, P2 = P1.to(common), P2.to(common)
+    if P1.dtype not in (_F32, _BF16):
+        P1, P2 = P1.float(), P2.float()
+    if P1.stride(1) != 1:
+        P1 = P1.contiguous()
+    if P2.stride(1) != 1:
+        P2 = P2.contiguous()
+    n1, D = P1.shape
+    n2 = P2.shape[0]
+    S = torch.empty((n1, n2), dtype=_F32, device=P1.device)
+    with _Timed("proj_similarity_kernel", "hbm", 2.0 * n1 * n2 * D, float(n1 + n2) * D * P1.element_size()):
+        _lib.check(lib.ghost_projection_similarity(P1.data_ptr(), P2.data_ptr(), _dt_flag(P1), n1, n2, D,
+                                                   P1.stride(0), P2.stride(0), float(scale), S.data_ptr(),
+                                                   S.stride(0), _stream_ptr()))
+    return S
 
 
 def launch_count() -> int:

@@ -33,7 +33,8 @@ enum {
   GHOST_ERR_INVALID = -1,        /* bad argument (the Python layer raises ValueError) */
   GHOST_ERR_CUDA = -2,           /* a CUDA runtime / driver call failed */
   GHOST_ERR_DEVICE = -3,         /* current device is not sm_100 */
-  GHOST_ERR_KERNEL_TIMEOUT = -4  /* a kernel gave up a bounded wait (see ghost_poll_kernel_error) */
+  GHOST_ERR_KERNEL_TIMEOUT = -4, /* a kernel gave up a bounded wait (see ghost_poll_kernel_error) */
+  GHOST_ERR_INDEX = -5           /* a kernel met an embedding id outside [0, vocab) (the Python layer raises IndexError) */
 };
 
 /* ---- library / device ---------------------------------------------------------------------- */
@@ -44,8 +45,9 @@ int ghost_device_check(void);
 int ghost_sm_count(void);
 /* Number of kernels this library has launched in this process (all threads, all devices). */
 long long ghost_launch_count(void);
-/* Reads (synchronously) the per-device word that kernels set when a bounded mbarrier wait ran out.
- * Returns GHOST_OK or GHOST_ERR_KERNEL_TIMEOUT; `clear` resets the word. */
+/* Reads (synchronously) the per-device word that kernels set when a bounded mbarrier wait ran out or
+ * an out-of-range embedding id was met.  Returns GHOST_OK, GHOST_ERR_KERNEL_TIMEOUT or
+ * GHOST_ERR_INDEX; `clear` resets the word. */
 int ghost_poll_kernel_error(int clear);
 
 /* ---- operand preparation --------------------------------------------------------------------- */
@@ -156,6 +158,22 @@ int ghost_small_gram_f32(const float* X, int n_train, int n_val, int F, float sc
  * of a bias / LayerNorm parameter from the per-sample vectors. */
 int ghost_rows_sum(const float* X, int n_rows, int F, float scale, void* out, int out_is_f32,
                    int accumulate, void* stream);
+/* Many of the two small reductions above in one launch.  Job j works on its layer's per-sample
+ * vectors X[n_train + n_val, F] (fp32): M[v, b] = dot_scale * <X[n_train + v], X[b]> when M is not
+ * NULL, and sum_out[c] = sum_scale * sum_{b < n_train} X[b, c] (fp32 or bf16) when sum_out is not
+ * NULL.  `jobs` is a HOST array; its entries travel to the device as kernel parameters, 48 per
+ * launch.  Replaces, for a whole backward pass at once, the per-layer einsum('bp,p->b') / sum(dim=0)
+ * calls of ghostEngines/supported_layers_grad_samplers_dotprod.py:143-146, 281-300, 347-363 and
+ * ghostEngines/autograd_grad_sample_dotprod.py:211-220. */
+typedef struct ghost_small_job {
+  const float* X;
+  float* M;
+  void* sum_out;
+  int n_train, n_val, F;
+  int sum_is_f32;
+  float dot_scale, sum_scale;
+} ghost_small_job;
+int ghost_small_reduce_batch(const ghost_small_job* jobs, int n_jobs, void* stream);
 
 /* ---- Embedding -------------------------------------------------------------------------------- */
 /* M[v,b] = scale * sum_{t,s : ids_b[t] == ids_v[s]} <G_b[t], G_v[s]>.  ids: int64 [N, T]; G: [N, T, d].
@@ -196,6 +214,31 @@ int ghost_gradproj_dense_bf16(const void* G, const void* A, int B, long long T, 
                               long long ldg, long long lda, const void* P_r, const void* P_c, int k_r,
                               int k_c, long long ldpr, long long ldpc, float scale, float* out,
                               long long out_stride, void* stream);
+/* out + b * out_stride + o * out_ld + i (+)= scale * sum_t (P_o g_bt)[o] * P_i[i, id_bt] for every sample
+ * b, o < k_o, i < k_i: the projected gradient of an embedding table.  ids: [B, T] int64; G: [B, T, d]
+ * out-grad rows (fp32 or bf16, row pitch ldg); P_o: bf16 [k_o, ldp_o] as ghost_cast_split_bf16 lays
+ * it out -- bf16(P_o) in columns [0, p_cols), p_cols = d rounded up to a multiple of 8, and, for fp32
+ * out-grads, the residual P_o - bf16(P_o) in columns [p_lo_offset, p_lo_offset + p_cols);
+ * P_i_t: fp32 [vocab, >= k_i] with row pitch ld_pit, P_i transposed, so that a token id selects one
+ * contiguous row.  k_o, k_i <= 64 per call: larger projections are covered block by block (row
+ * offsets into P_o / out, column offsets into P_i_t / out, out_ld = the full k_i).  accumulate = 0
+ * zeroes the samples' blocks first and needs out_ld == k_i.  An id outside [0, vocab) contributes
+ * nothing and makes the next ghost_poll_kernel_error return GHOST_ERR_INDEX.
+ * Replaces ghostEngines/gradProjection/autograd_gradproj.py:167-222 (a Python loop over all
+ * tokens with one host synchronisation per token). */
+int ghost_gradproj_embedding(const long long* ids, const void* G, int g_is_f32, int B, long long T, int d,
+                             long long ldg, const void* P_o, long long ldp_o, int p_cols, int p_lo_offset,
+                             const float* P_i_t, long long ld_pit, int vocab, int k_o, int k_i, float scale,
+                             int accumulate, float* out, long long out_stride, int out_ld, void* stream);
+/* S[n1, n2] (row pitch ld_s, fp32) <- scale * P1 P2^T for two blocks of projection rows
+ * P1: [n1, D], P2: [n2, D] (both fp32 or both bf16, row pitches ld1, ld2).  Meant for batch-sized
+ * blocks (tens of rows) against a very long D = total_proj_dim, where both operands are streamed
+ * once; larger blocks are correct but re-read the operands once per 16 x 16 output block.
+ * Replaces the proj1 @ proj2.t() of Examples/ghost_gradproj_lm.py:190-196 and
+ * Examples/GradProj_LM/plot_error_with_dim.py:69-86 while the rows are still on the device. */
+int ghost_projection_similarity(const void* P1, const void* P2, int is_f32, int n1, int n2, long long D,
+                                long long ld1, long long ld2, float scale, float* S, long long ld_s,
+                                void* stream);
 
 /* ---- benchmark model helper (not part of the ghost hot path) ------------------------------------ */
 /* Token cross-entropy of a [rows, cols] logit matrix whose last cols - cols_valid columns are padding

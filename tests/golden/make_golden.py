@@ -11,7 +11,7 @@ The reference functions exercised (paths inside the reference project):
   ghostEngines/supported_layers_grad_samplers_dotprod.py  -- every (dot_fn, train_grad_fn) pair
   ghostEngines/autograd_grad_sample_dotprod.py            -- _compute_train_grad_bias, add_hooks
   ghostEngines/graddotprod_engine.py                      -- 3-step MLP run (engine level)
-  ghostEngines/gradProjection/autograd_gradproj.py        -- _compute_dense_proj
+  ghostEngines/gradProjection/autograd_gradproj.py        -- _compute_dense_proj, _compute_embedding_proj
   ghostEngines/gradProjection/projection_utils.py         -- choose_ki_ko, gaussian initialiser
   ghostEngines/gradProjection/gradproj_engine.py          -- engine-level MLP projection
 """
@@ -249,6 +249,21 @@ def main():
     geng.iteration = 1   # skip the disk write (interval is huge)
     out["gpmlp_proj"] = f32(geng.collect_batch())
     geng.detach()
+
+    # ---------------- GradProj embedding projection (own generator: earlier draws stay as they are) ----
+    ge = torch.Generator().manual_seed(31)
+    V_e, d_e, T_e, B_e, ki_e, ko_e = 19, 12, 7, 3, 5, 4
+    ids_e = torch.randint(0, V_e, (B_e, T_e), generator=ge)
+    G_e = torch.randn(B_e, T_e, d_e, generator=ge)
+    P_i_e = pu.init_projection_matrix_gaussian(ki_e, V_e, seed=44)
+    P_o_e = pu.init_projection_matrix_gaussian(ko_e, d_e, seed=1044)
+    emb = nn.Embedding(V_e, d_e)
+    GradProjHooks(P_i_e, P_o_e, "emb", "Embedding")._compute_embedding_proj(emb, ids_e, G_e)
+    out["gp_emb_ids"] = ids_e.numpy()
+    out["gp_emb_G"] = f32(G_e)
+    out["gp_emb_P_i"] = f32(P_i_e)
+    out["gp_emb_P_o"] = f32(P_o_e)
+    out["gp_emb"] = f32(emb._ghost_grad_proj)
 
     path = os.path.join(HERE, "reference_outputs.npz")
     np.savez_compressed(path, **out)

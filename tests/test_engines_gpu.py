@@ -161,7 +161,9 @@ def _check_dotprod_model(model, run, ids, n_t, n_v, dtype, path_rule, n_hooked):
                 for role in ("weight", "bias"):
                     q = getattr(layer, role, None)
                     if q is not None and hasattr(q, "grad_dot_prod_matrix"):
-                        results[(name, role)] = q.grad_dot_prod_matrix.detach().cpu()
+                        # the tensor this hook set; the bias / LayerNorm matrices are filled by one
+                        # batched launch when the backward pass ends, so they are read after it
+                        results[(name, role)] = q.grad_dot_prod_matrix.detach()
             return f
 
         handles = []
@@ -553,6 +555,50 @@ def test_gradproj_engine_on_hf_decoders_bf16(tmp_path, family):
         assert {n: p.requires_grad for n, p in model.named_parameters()} == flags      # restored, dummy bias gone
     # same math in both runs; the attention backward of the model may order its sums differently
     assert O.rel_fro(outs[True], outs[False]) < 5e-3
+
+
+def test_gradproj_engine_with_embeddings_and_similarity(tmp_path):
+    """include_embeddings=True: the token and position embeddings go through the embedding-projection
+    kernel straight into their slices of the engine's buffer (the reference loops over tokens in
+    Python), next to the dense layers; then the similarity scores of the collected batch against
+    itself, the downstream step of the reference's examples, taken while it is still on the device."""
+    from ghostsuite_b200.ghostEngines.gradProjection.gradproj_engine import GradProjLoraEngine
+    from ghostsuite_b200.ghostEngines.gradProjection.projection_utils import projection_similarity
+    from ghostsuite_b200.workloads import GPT2Like, GPT2Config
+    for dtype in (torch.float32, torch.bfloat16):
+        torch.manual_seed(8)
+        cfg = GPT2Config(vocab_size=300, n_positions=64, n_embd=64, n_layer=1, n_head=4, tie_weights=False)
+        model = GPT2Like(cfg).to(dtype).cuda()
+        with contextlib.redirect_stdout(io.StringIO()):
+            eng = GradProjLoraEngine(model, proj_layers="wte,wpe,mlp", proj_rank_total=64, proj_rank_min=2,
+                                     proj_seed=5, proj_dtype="float32", proj_dir=str(tmp_path / str(dtype)),
+                                     include_embeddings=True, proj_save_interval=10 ** 9)
+            eng.attach()
+        assert set(eng.matched_layers) == {"wte", "wpe", "h.0.mlp.c_fc", "h.0.mlp.c_proj"}
+        cap = {}
+        for name, layer in eng.matched_layers.items():
+            layer.register_forward_hook(lambda l, i, o, n=name: cap.setdefault(n, {}).__setitem__("A", i[0].detach().cpu()))
+            layer.register_full_backward_hook(lambda l, gi, go, n=name: cap[n].__setitem__("B", go[0].detach().cpu()))
+        ids = torch.randint(0, 300, (5, 48)).cuda()
+        loss, _ = model(ids, labels=ids)
+        loss.backward()
+        eng.iteration = 1
+        proj = eng.collect_batch()
+        tol = 1e-4 if dtype == torch.float32 else 2e-2
+        for name in sorted(eng.matched_layers):
+            P_i, P_o = eng.projection_matrices[name]
+            lo, hi = eng.slice_ranges[name]
+            if isinstance(eng.matched_layers[name], nn.Embedding):
+                ref = O.gradproj_embedding(cap[name]["A"], cap[name]["B"], P_i.cpu(), P_o.cpu(),
+                                           compute_dtype=torch.float64)
+            else:
+                ref = O.gradproj_dense(cap[name]["A"], cap[name]["B"], P_i.cpu(), P_o.cpu(), conv1d=True,
+                                       compute_dtype=torch.float64)
+            assert O.rel_fro(proj[:, lo:hi].reshape(ref.shape), ref) < tol, (dtype, name)
+        sims = projection_similarity(proj, proj)
+        assert sims.shape == (5, 5)
+        assert O.rel_fro(sims, O.projection_similarity(proj.cpu(), proj.cpu())) < 1e-4
+        eng.cleanup()
 
 
 def test_manager_facade(tmp_path):

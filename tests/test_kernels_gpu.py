@@ -372,6 +372,126 @@ def test_gradproj_golden(golden):
     assert torch.allclose(out.cpu().reshape(8, 4, 6), torch.from_numpy(golden["gp_c1d"]), rtol=1e-3, atol=1e-4)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", [
+    # B, T, d, vocab, k_i, k_o
+    (3, 7, 12, 19, 5, 4),          # the golden case's sizes: everything smaller than one tile
+    (4, 130, 72, 300, 32, 32),     # T straddles the 64-token blocks, d not a multiple of 16
+    (2, 300, 512, 50, 64, 64),     # heavy id repetition, the largest single-launch block
+    (3, 1, 10, 20, 3, 5),          # one token per sample, d with a 2-element tail
+    (2, 65, 11, 40, 7, 9),         # odd feature size: the element-wise load path
+    (2, 257, 128, 1000, 12, 85),   # k_o > 64: covered block by block
+    (2, 33, 64, 64, 70, 66)])      # both larger than 64
+def test_gradproj_embedding(case, dtype):
+    B, T, d, vocab, k_i, k_o = case
+    g = torch.Generator().manual_seed(21)
+    ids = torch.randint(0, vocab, (B, T), generator=g)
+    G = (torch.randn(B, T, d, generator=g) / d ** 0.5).to(dtype)
+    P_i = torch.randn(k_i, vocab, generator=g) / k_i ** 0.5
+    P_o = torch.randn(k_o, d, generator=g) / k_o ** 0.5
+    o = ops()
+    split = dtype == torch.float32
+    Po = o.prepare_projection(P_o.cuda(), split)
+    PiT = o.prepare_embedding_projection(P_i.cuda())
+    total = k_o * k_i + 9
+    buf = torch.full((B, total), 55.0, device="cuda")
+    o.gradproj_embedding(ids.cuda(), G.cuda(), Po, PiT, k_o, k_i, 1.0, buf[:, 4:4 + k_o * k_i])
+    after()
+    ref = O.gradproj_embedding(ids, G, P_i, P_o, compute_dtype=torch.float64)
+    got = buf[:, 4:4 + k_o * k_i].reshape(B, k_o, k_i)
+    assert O.rel_fro(got, ref) < (1e-4 if split else 2e-2)
+    assert torch.all(buf[:, :4] == 55.0) and torch.all(buf[:, 4 + k_o * k_i:] == 55.0)
+    # a second call into the same buffer overwrites (the kernel adds into a block it zeroed itself)
+    o.gradproj_embedding(ids.cuda(), G.cuda(), Po, PiT, k_o, k_i, 2.0, buf[:, 4:4 + k_o * k_i])
+    after()
+    assert O.rel_fro(buf[:, 4:4 + k_o * k_i].reshape(B, k_o, k_i), 2 * ref) < (1e-4 if split else 2e-2)
+
+
+def test_gradproj_embedding_golden_and_bad_ids(golden):
+    """The reference's per-token loop (golden output), then an id outside the table: the kernel skips
+    it and the next poll raises IndexError, as indexing P_i[:, id] does in the reference."""
+    ids = torch.from_numpy(golden["gp_emb_ids"])
+    G = torch.from_numpy(golden["gp_emb_G"])
+    P_i, P_o = torch.from_numpy(golden["gp_emb_P_i"]), torch.from_numpy(golden["gp_emb_P_o"])
+    o = ops()
+    Po = o.prepare_projection(P_o.cuda(), True)
+    PiT = o.prepare_embedding_projection(P_i.cuda())
+    out = o.gradproj_embedding(ids.cuda(), G.cuda(), Po, PiT, 4, 5)
+    after()
+    want = torch.from_numpy(golden["gp_emb"])
+    assert O.rel_fro(out.reshape(3, 4, 5), want) < 1e-4
+    assert torch.allclose(out.cpu().reshape(3, 4, 5), want, rtol=1e-3, atol=1e-4)
+    bad = ids.clone()
+    bad[1, 2] = 19                                        # vocab is 19
+    out2 = o.gradproj_embedding(bad.cuda(), G.cuda(), Po, PiT, 4, 5)
+    torch.cuda.synchronize()
+    from ghostsuite_b200 import _lib
+    with pytest.raises(IndexError):
+        _lib.poll_kernel_error()
+    _lib.poll_kernel_error()                              # the word was cleared
+    keep = torch.ones(3, 7, dtype=torch.bool)
+    keep[1, 2] = False
+    ref = O.gradproj_embedding(ids, G * keep.unsqueeze(-1), P_i, P_o, compute_dtype=torch.float64)
+    assert O.rel_fro(out2.reshape(3, 4, 5), ref) < 1e-4     # the bad token contributed nothing
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", [(3, 5, 64), (16, 16, 98304), (8, 40, 1000), (33, 17, 4096),
+                                  (5, 3, 12345), (1, 1, 7), (16, 8, 917504)])
+def test_projection_similarity(case, dtype):
+    n1, n2, D = case
+    g = torch.Generator().manual_seed(22)
+    P1 = torch.randn(n1, D, generator=g).to(dtype)
+    P2 = (torch.randn(n2, D, generator=g) + 0.05 * torch.randn(1, D, generator=g)).to(dtype)
+    S = ops().projection_similarity(P1.cuda(), P2.cuda(), 0.5)
+    after()
+    ref = 0.5 * O.projection_similarity(P1, P2)
+    assert S.shape == (n1, n2) and S.dtype == torch.float32
+    assert O.rel_fro(S, ref) < 1e-4
+    # rows of a wider buffer (the engine's [B, total_proj_dim] buffer, a column range of it)
+    if D >= 64:
+        wide = torch.zeros(n1, D + 24, dtype=dtype, device="cuda")
+        wide[:, 8:8 + D] = P1.cuda()
+        S2 = ops().projection_similarity(wide[:, 8:8 + D], P2.cuda(), 0.5)
+        after()
+        assert O.rel_fro(S2, ref) < 1e-4
+
+
+def test_small_reduce_batch_matches_single_launches():
+    """One batched launch for many layers' small reductions against the per-layer kernels: more jobs
+    than fit one launch, mixed sizes, Gram only / sum only / both, bf16 and fp32 sums."""
+    o = ops()
+    g = torch.Generator().manual_seed(23)
+    jobs, want = [], []
+    for i in range(110):
+        n_t, n_v = (5, 3) if i % 3 else (32, 8)
+        F = (768, 10, 3072, 37, 1)[i % 5]
+        X = torch.randn(n_t + n_v, F, generator=g).cuda()
+        job = {"X": X, "n_train": n_t, "n_val": n_v}
+        rec = {}
+        if i % 4 != 1:
+            job["M"] = torch.full((n_v, n_t), 7.0, device="cuda")
+            job["dot_scale"] = 0.5
+            rec["M"] = o.small_gram(X, n_v, 0.5)
+        if i % 4 != 2:
+            dt = torch.bfloat16 if i % 2 else torch.float32
+            job["sum_out"] = torch.full((F,), 7.0, dtype=dt, device="cuda")
+            job["sum_scale"] = 0.25
+            rec["sum"] = o.rows_sum(X, n_t, 0.25, dt)
+        jobs.append(job)
+        want.append(rec)
+    from ghostsuite_b200 import _lib
+    l0 = _lib.launch_count()
+    o.small_reduce_batch(jobs)
+    assert _lib.launch_count() - l0 == 3                      # 48 jobs per launch
+    after()
+    for job, rec in zip(jobs, want):
+        if "M" in rec:
+            assert torch.equal(job["M"], rec["M"])
+        if "sum" in rec:
+            assert torch.equal(job["sum_out"], rec["sum"])
+
+
 def test_error_codes_are_python_exceptions():
     o = ops()
     A = torch.randn(4, 3, 8, device="cuda")

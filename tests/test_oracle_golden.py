@@ -140,6 +140,24 @@ def test_gradproj_dense(golden):
     close(torch.from_numpy(golden["gp_linear"]), naive, rtol=1e-4, atol=1e-5)
 
 
+def test_gradproj_embedding(golden):
+    """The vectorised restatement against the reference's per-token Python loop."""
+    ids = torch.from_numpy(golden["gp_emb_ids"])
+    G = torch.from_numpy(golden["gp_emb_G"])
+    P_i = torch.from_numpy(golden["gp_emb_P_i"])
+    P_o = torch.from_numpy(golden["gp_emb_P_o"])
+    got = O.gradproj_embedding(ids, G, P_i, P_o)
+    ref = torch.from_numpy(golden["gp_emb"])
+    assert got.shape == ref.shape == (3, 4, 5)
+    close(got, ref, 1e-5, 1e-6)
+    # the definition, token by token
+    b, t = 1, 2
+    one = torch.outer(P_o @ G[b, t], P_i[:, ids[b, t]])
+    full = sum(torch.outer(P_o @ G[b, tt], P_i[:, ids[b, tt]]) for tt in range(G.shape[1]))
+    assert one.shape == (4, 5)
+    close(got[b], full, 1e-5, 1e-6)
+
+
 def test_conv2d(golden):
     """Materialised branch of the reference (its ghost branch for Conv2d raises on shape grounds)."""
     assert int(golden["conv_ghost_branch_runs"][0]) == 0
