@@ -14,6 +14,8 @@ from typing import Optional, Tuple
 import torch
 import torch.nn as nn
 
+from ... import ops
+
 
 def choose_ki_ko(n_i: int, n_o: int, k_total: int, k_min: int = 1) -> Tuple[int, int]:
     """Pick ``(k_i, k_o)`` with ``k_i * k_o ~ k_total``, ``k_i / k_o ~ sqrt(n_o / n_i)`` and both at
