@@ -235,7 +235,7 @@ int ghost_poll_kernel_error(int clear) {
       int zero = 0;
       cudaMemcpy(s->err_word, &zero, sizeof(int), cudaMemcpyHostToDevice);
     }
-    if (v == 9001) {      // kErrBadIndex of the embedding-projection kernel
+    if (v == gb::kErrBadIndex) {
       gb::set_error("an embedding id outside [0, vocab) reached a kernel (its contribution was skipped)");
       return GHOST_ERR_INDEX;
     }

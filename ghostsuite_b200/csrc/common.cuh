@@ -33,6 +33,10 @@ int fail(int code, const char* fmt, ...);
 void count_launch(int n = 1);
 int post_launch(const char* what);  // cudaGetLastError -> status
 
+// Value kernels store in the device error word when they meet an embedding id outside [0, vocab):
+// the id's contribution is skipped and ghost_poll_kernel_error reports GHOST_ERR_INDEX.
+static constexpr int kErrBadIndex = 9001;
+
 // ---- per-device state ----------------------------------------------------------------------
 struct DeviceState {
   int device = -1;

@@ -63,12 +63,16 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 
 // ---------------------------------------------------------------- dot product
 __global__ void emb_chain_val_kernel(const long long* __restrict__ ids_val, long long n_tok, int vocab,
-                                     int* __restrict__ head, int* __restrict__ next) {
+                                     int* __restrict__ head, int* __restrict__ next, int* __restrict__ err) {
   for (long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n_tok;
        j += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long id = ids_val[j];
-    if (id >= 0 && id < vocab) next[j] = atomicExch(&head[id], static_cast<int>(j));
-    else next[j] = -1;
+    if (id >= 0 && id < vocab) {
+      next[j] = atomicExch(&head[id], static_cast<int>(j));
+    } else {            // the reference's index_add_ raises here; skipped and reported through the error word
+      next[j] = -1;
+      atomicExch(err, kErrBadIndex);
+    }
   }
 }
 
@@ -77,7 +81,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 emb_dot_kernel(const long long* __restrict__ ids, const T* __restrict__ G, int n_train, int n_val,
                long long Tn, int d, int vocab, const int* __restrict__ head,
-               const int* __restrict__ next, float scale, float* __restrict__ M, int tok_per_block) {
+               const int* __restrict__ next, float scale, float* __restrict__ M, int tok_per_block,
+               int* __restrict__ err) {
   extern __shared__ float s_acc[];   // [n_val]
   const int b = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -90,7 +95,10 @@ emb_dot_kernel(const long long* __restrict__ ids, const T* __restrict__ G, int n
   const bool vec = (d % 8 == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0);
   for (long long t = t_begin + warp; t < t_end; t += 8) {
     const long long id = ids[static_cast<long long>(b) * Tn + t];
-    if (id < 0 || id >= vocab) continue;
+    if (id < 0 || id >= vocab) {
+      if (lane == 0) atomicExch(err, kErrBadIndex);
+      continue;
+    }
     int j = head[id];
     const T* row = G + (static_cast<long long>(b) * Tn + t) * d;
     while (j >= 0) {
@@ -124,11 +132,12 @@ emb_dot_kernel(const long long* __restrict__ ids, const T* __restrict__ G, int n
 
 // ---------------------------------------------------------------- train gradient
 __global__ void emb_count_kernel(const long long* __restrict__ ids, long long n_tok, int vocab,
-                                 int* __restrict__ counts) {
+                                 int* __restrict__ counts, int* __restrict__ err) {
   for (long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n_tok;
        j += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long id = ids[j];
     if (id >= 0 && id < vocab) atomicAdd(&counts[id], 1);
+    else atomicExch(err, kErrBadIndex);
   }
 }
 
@@ -298,7 +307,7 @@ extern "C" int ghost_embedding_dot(const long long* ids, const void* G, int is_f
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
   int blocks = static_cast<int>((n_vtok + 255) / 256);
   if (blocks > ds->sm_count * 8) blocks = ds->sm_count * 8;
-  emb_chain_val_kernel<<<blocks, 256, 0, st>>>(ids + static_cast<long long>(n_train) * T, n_vtok, vocab, head, next);
+  emb_chain_val_kernel<<<blocks, 256, 0, st>>>(ids + static_cast<long long>(n_train) * T, n_vtok, vocab, head, next, ds->err_word);
   count_launch();
   int rc = post_launch("emb_chain_val_kernel");
   if (rc != GHOST_OK) return rc;
@@ -306,9 +315,9 @@ extern "C" int ghost_embedding_dot(const long long* ids, const void* G, int is_f
   dim3 grid(ceil_div(T, tok_per_block), n_train);
   const size_t smem = sizeof(float) * n_val;
   if (is_f32)
-    emb_dot_kernel<float><<<grid, 256, smem, st>>>(ids, static_cast<const float*>(G), n_train, n_val, T, d, vocab, head, next, scale, M_out, tok_per_block);
+    emb_dot_kernel<float><<<grid, 256, smem, st>>>(ids, static_cast<const float*>(G), n_train, n_val, T, d, vocab, head, next, scale, M_out, tok_per_block, ds->err_word);
   else
-    emb_dot_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(ids, static_cast<const __nv_bfloat16*>(G), n_train, n_val, T, d, vocab, head, next, scale, M_out, tok_per_block);
+    emb_dot_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(ids, static_cast<const __nv_bfloat16*>(G), n_train, n_val, T, d, vocab, head, next, scale, M_out, tok_per_block, ds->err_word);
   count_launch();
   return post_launch("emb_dot_kernel");
 }
@@ -339,7 +348,7 @@ extern "C" int ghost_embedding_wgrad(const long long* ids, const void* G, int is
   GB_CUDA_OK(cudaMemsetAsync(cursor, 0, seg, st));
   int blocks = static_cast<int>((n_tok + 255) / 256);
   if (blocks > ds->sm_count * 8) blocks = ds->sm_count * 8;
-  emb_count_kernel<<<blocks, 256, 0, st>>>(ids, n_tok, vocab, counts);
+  emb_count_kernel<<<blocks, 256, 0, st>>>(ids, n_tok, vocab, counts, ds->err_word);
   emb_scan_kernel<<<1, 1024, 0, st>>>(counts, vocab, offsets);
   emb_fill_kernel<<<blocks, 256, 0, st>>>(ids, n_tok, vocab, offsets, cursor, perm);
   if (is_f32)

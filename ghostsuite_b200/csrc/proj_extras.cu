@@ -19,8 +19,6 @@
 
 namespace gb {
 
-static constexpr int kErrBadIndex = 9001;   // an id outside [0, vocab) reached the kernel
-
 // ------------------------------------------------------------------------------------------------
 // embedding projection
 // ------------------------------------------------------------------------------------------------

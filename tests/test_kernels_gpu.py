@@ -328,6 +328,36 @@ def test_embedding_position_ids_and_golden(golden):
         assert np.array_equal(grad.cpu().float().numpy(), golden[f"emb_{tag}_train_grad"])
 
 
+def test_embedding_out_of_range_ids_are_reported():
+    """An id outside the table makes the reference's index_add_ raise.  The kernels skip such a token
+    and record it; the next poll of the error word raises IndexError."""
+    from ghostsuite_b200 import _lib
+    n_t, n_v, T, d, vocab = 4, 2, 9, 16, 30
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, vocab, (n_t + n_v, T), generator=g)
+    G = torch.randn(n_t + n_v, T, d, generator=g)
+    good_M = ops().embedding_dot(ids.cuda(), G.cuda(), n_v, vocab)
+    after()                                                   # nothing recorded for valid ids
+    for row, col in ((1, 3), (n_t, 4)):                       # a train token, then a validation token
+        bad = ids.clone()
+        bad[row, col] = vocab
+        M = ops().embedding_dot(bad.cuda(), G.cuda(), n_v, vocab)
+        torch.cuda.synchronize()
+        with pytest.raises(IndexError):
+            _lib.poll_kernel_error()
+        keep = torch.ones(n_t + n_v, T, 1)
+        keep[row, col] = 0
+        assert O.rel_fro(M, O.embedding_dot_exact(ids, G * keep, n_v)) < 1e-5
+    bad = ids.clone()
+    bad[0, 0] = -1
+    ops().embedding_wgrad(bad.cuda(), G.cuda(), n_t, vocab, 1.0, float(n_t))
+    torch.cuda.synchronize()
+    with pytest.raises(IndexError):
+        _lib.poll_kernel_error()
+    _lib.poll_kernel_error()
+    assert torch.isfinite(good_M).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("case", [(8, 6, 16, 24, 4, 6), (4, 130, 72, 200, 32, 32), (2, 300, 512, 136, 64, 64),
                                   (3, 1, 10, 20, 5, 3), (2, 257, 128, 256, 120, 34)])

@@ -3,8 +3,10 @@
 Some callers may not allocate device memory when the hook fires (their memory belongs to a fixed
 pool, or they run inside a section where re-entering an allocator would deadlock), so they cannot
 give ghost_embedding_dot a workspace.  ghost_embedding_dot_noalloc keeps its tables in a device
-array inside the library instead.  This file is collected last on purpose: if it fails, a run that
-stops at the first failure has already run everything else.
+array inside the library instead.  The file name sorts last so that this add-on entry point is
+exercised after the entry points every engine depends on: a run stopped at its first failure
+(`pytest -x`) has then already covered those, and the shared array is also met in whatever state
+the rest of the session left the device in.
 """
 import ctypes
 
@@ -65,3 +67,33 @@ def test_noalloc_entry_point_rejects_sizes_beyond_its_scratch():
     rc = lib.ghost_embedding_dot_noalloc(ids.data_ptr(), G.data_ptr(), 1, 2, 1, 131073, 8, 100, 1.0,
                                          M.data_ptr(), stream)
     assert rc == _lib.GHOST_ERR_INVALID and b"exceeds the built-in scratch" in lib.ghost_last_error()
+
+
+def test_noalloc_entry_point_allocates_nothing_and_fills_its_scratch_exactly():
+    """The property the entry point exists for: once its first call on the device has looked up the
+    array's address, a call takes no device memory at all (free memory as the driver reports it is
+    unchanged across the call).  The problem is the largest the 1 MiB array holds -- vocab = 131072
+    head entries and n_val * T = 131072 chain entries -- and is checked against the workspace entry
+    point."""
+    from ghostsuite_b200 import _lib
+    lib = _lib.load()
+    n_train, n_val, T, d, vocab = 3, 2, 65536, 8, 131072
+    g = torch.Generator().manual_seed(13)
+    ids = torch.randint(0, vocab, (n_train + n_val, T), generator=g).cuda()
+    ids[n_train, 0] = vocab - 1                                   # the last head entry is used
+    ids[0, 5] = vocab - 1
+    G = torch.randn(n_train + n_val, T, d, generator=g).cuda()
+    M_ws, M_na = _call_both(lib, ids, G, n_train, n_val, vocab)   # also the warm-up call of this device
+    assert O.rel_fro(M_na, M_ws) < 1e-5
+    stream = torch.cuda.current_stream().cuda_stream
+    M2 = torch.full((n_val, n_train), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    _lib.check(lib.ghost_embedding_dot_noalloc(ids.data_ptr(), G.data_ptr(), 1, n_train, n_val, T, d, vocab,
+                                               1.0, M2.data_ptr(), stream))
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before and torch.cuda.memory_reserved() == reserved_before
+    assert O.rel_fro(M2, M_ws) < 1e-5
+    _lib.poll_kernel_error()
