@@ -802,6 +802,12 @@ KERNEL_CASES = {
     "gradproj_llama_gate": ("gradproj", dict(B=8, T=4096, n_i=4096, n_o=14336, k=64)),
     "gradproj_pythia_fc": ("gradproj", dict(B=16, T=2048, n_i=1024, n_o=4096, k=32)),
     "gradproj_small": ("gradproj", dict(B=8, T=4096, n_i=1024, n_o=2048, k=64)),   # sized for an ncu capture
+    # embedding projection of a Pythia-410M-shaped token embedding at the configuration's 16 x 2048 tokens
+    "gradproj_embedding_pythia": ("gradproj_embedding", dict(B=16, T=2048, d=1024, vocab=50304, k_i=32, k_o=32)),
+    # similarity of one Llama-3-8B-shaped batch of projections ([8, 917504] fp32) against another
+    "similarity_llama_batch": ("similarity", dict(n1=8, n2=8, D=917504)),
+    "similarity_pythia_batch": ("similarity", dict(n1=16, n2=16, D=98304)),
+    "similarity_64_rows": ("similarity", dict(n1=64, n2=64, D=917504)),
 }
 
 
@@ -861,6 +867,17 @@ def run_kernels(args):
             P_o = ops.prepare_projection(torch.randn(c["k"], c["n_o"], generator=g, device=dev) / c["k"] ** 0.5, False)
             out = torch.empty(c["B"], c["k"] * c["k"], device=dev)
             fn = lambda: ops.gradproj_dense(G, A, P_o, P_i, c["k"], c["k"], float(c["B"]), out)
+        elif kind == "gradproj_embedding":
+            ids = torch.randint(0, c["vocab"], (c["B"], c["T"]), generator=g, device=dev)
+            G = rnd(c["B"], c["T"], c["d"], scale=c["d"] ** -0.5)
+            P_o = ops.prepare_projection(torch.randn(c["k_o"], c["d"], generator=g, device=dev) / c["k_o"] ** 0.5, False)
+            P_i_t = ops.prepare_embedding_projection(torch.randn(c["k_i"], c["vocab"], generator=g, device=dev) / c["k_i"] ** 0.5)
+            out = torch.empty(c["B"], c["k_o"] * c["k_i"], device=dev)
+            fn = lambda: ops.gradproj_embedding(ids, G, P_o, P_i_t, c["k_o"], c["k_i"], 1.0, out)
+        elif kind == "similarity":
+            P1 = torch.randn(c["n1"], c["D"], generator=g, device=dev)
+            P2 = torch.randn(c["n2"], c["D"], generator=g, device=dev)
+            fn = lambda: ops.projection_similarity(P1, P2)
         for _ in range(max(1, args.warmup)):
             fn()
         torch.cuda.synchronize()
