@@ -54,6 +54,7 @@ PROTOTYPES = {
     "ghost_rows_sum": (_i, [_vp, _i, _i, _f, _vp, _i, _i, _vp]),
     "ghost_small_reduce_batch": (_i, [C.POINTER(SmallJob), _i, _vp]),
     "ghost_embedding_dot_workspace_bytes": (_ll, [_i, _ll, _i]),
+    "ghost_embedding_dot_workspace_bytes_for": (_ll, [_i, _ll, _i, _i]),
     "ghost_embedding_dot": (_i, [_vp, _vp, _i, _i, _i, _ll, _i, _i, _f, _vp, _vp, _ll, _vp]),
     "ghost_embedding_dot_noalloc": (_i, [_vp, _vp, _i, _i, _i, _ll, _i, _i, _f, _vp, _vp]),
     "ghost_embedding_wgrad_workspace_bytes": (_ll, [_i, _ll, _i]),

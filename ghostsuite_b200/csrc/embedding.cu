@@ -63,16 +63,52 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 
 // ---------------------------------------------------------------- dot product
 __global__ void emb_chain_val_kernel(const long long* __restrict__ ids_val, long long n_tok, int vocab,
-                                     int* __restrict__ head, int* __restrict__ next, int* __restrict__ err) {
+                                     int* __restrict__ head, int* __restrict__ next, int* __restrict__ cnt,
+                                     int* __restrict__ err) {
   for (long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n_tok;
        j += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long id = ids_val[j];
     if (id >= 0 && id < vocab) {
       next[j] = atomicExch(&head[id], static_cast<int>(j));
+      if (cnt != nullptr) atomicAdd(&cnt[id], 1);
     } else {            // the reference's index_add_ raises here; skipped and reported through the error word
       next[j] = -1;
       atomicExch(err, kErrBadIndex);
     }
+  }
+}
+
+// Ids that many validation tokens share (padding, separators, position ids with a large validation
+// batch) would make every train token with that id walk a long chain.  For the `cap` most ... first
+// ids whose chain is longer than `threshold`, the validation rows are summed once per (id,
+// validation sample) into R[slot][v][d] (float32); a train token then takes n_val dot products
+// against R instead of walking the chain.  cnt[id] is overwritten with -(slot + 1) for such ids.
+__global__ void emb_hot_assign_kernel(int* __restrict__ cnt, int vocab, int threshold, int cap,
+                                      int* __restrict__ n_hot) {
+  for (int id = blockIdx.x * blockDim.x + threadIdx.x; id < vocab; id += gridDim.x * blockDim.x) {
+    if (cnt[id] > threshold) {
+      const int h = atomicAdd(n_hot, 1);
+      if (h < cap) cnt[id] = -(h + 1);
+    }
+  }
+}
+
+// one warp per validation token: rows of hot ids are added into R[slot][v]
+template <typename T>
+__global__ void __launch_bounds__(256)
+emb_hot_reduce_kernel(const long long* __restrict__ ids_val, const T* __restrict__ Gval, long long n_tok,
+                      long long Tn, int d, int n_val, int vocab, const int* __restrict__ cnt,
+                      float* __restrict__ R) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = static_cast<long long>(gridDim.x) * 8;
+  for (long long j = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); j < n_tok; j += warps) {
+    const long long id = ids_val[j];
+    if (id < 0 || id >= vocab) continue;
+    const int c = cnt[id];
+    if (c >= 0) continue;
+    float* dst = R + (static_cast<long long>(-c - 1) * n_val + j / Tn) * d;
+    const T* row = Gval + j * d;
+    for (int f = lane; f < d; f += 32) atomicAdd(dst + f, ld_f32<T>(row + f));
   }
 }
 
@@ -81,8 +117,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 emb_dot_kernel(const long long* __restrict__ ids, const T* __restrict__ G, int n_train, int n_val,
                long long Tn, int d, int vocab, const int* __restrict__ head,
-               const int* __restrict__ next, float scale, float* __restrict__ M, int tok_per_block,
-               int* __restrict__ err) {
+               const int* __restrict__ next, const int* __restrict__ cnt, const float* __restrict__ R,
+               float scale, float* __restrict__ M, int tok_per_block, int* __restrict__ err) {
   extern __shared__ float s_acc[];   // [n_val]
   const int b = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -101,6 +137,20 @@ emb_dot_kernel(const long long* __restrict__ ids, const T* __restrict__ G, int n
     }
     int j = head[id];
     const T* row = G + (static_cast<long long>(b) * Tn + t) * d;
+    const int c = (cnt != nullptr) ? cnt[id] : 0;
+    if (c < 0) {
+      // an id shared by many validation tokens: one dot product per validation sample against the
+      // pre-summed rows
+      const float* Rh = R + static_cast<long long>(-c - 1) * n_val * d;
+      for (int v = 0; v < n_val; ++v) {
+        const float* rv = Rh + static_cast<long long>(v) * d;
+        float s = 0.f;
+        for (int f = lane; f < d; f += 32) s = fmaf(ld_f32<T>(row + f), rv[f], s);
+        s = ewarp_sum(s);
+        if (lane == 0 && s != 0.f) atomicAdd(&s_acc[v], s);
+      }
+      continue;
+    }
     while (j >= 0) {
       const T* vrow = Gval + static_cast<long long>(j) * d;
       float s = 0.f;
@@ -193,7 +243,51 @@ __global__ void emb_fill_kernel(const long long* __restrict__ ids, long long n_t
   }
 }
 
-// one warp per table row: ascending-order float32 segment sum, dtype rounding as the reference
+// Shared pieces of the two segment-sum kernels.  A thread owns 8 consecutive features.
+template <typename T>
+__device__ __forceinline__ void emb_load_row(const T* __restrict__ G, int j, int d, int f, bool vec, float (&x)[8]) {
+  const T* row = G + static_cast<long long>(j) * d + f;
+  if (vec) {
+    if (f < d) {
+      load8(row, x);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = 0.f;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = (f + e < d) ? ld_f32<T>(row + e) : 0.f;
+  }
+}
+// no fma contraction: product and sum are rounded separately, as the reference does
+template <typename T>
+__device__ __forceinline__ void emb_accumulate(const float (&x)[8], float pre_scale, float (&acc)[8]) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = __fadd_rn(acc[e], round_to<T>(__fmul_rn(x[e], pre_scale)));
+}
+template <typename T>
+__device__ __forceinline__ void emb_store_row(T* __restrict__ out, int k, int d, int f, bool vec, const float (&acc)[8],
+                                              float divisor, int accumulate) {
+  T* dst = out + static_cast<long long>(k) * d + f;
+  float o[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    o[e] = round_to<T>(__fdiv_rn(round_to<T>(acc[e]), divisor));
+    if (accumulate && f + e < d) o[e] = round_to<T>(__fadd_rn(ld_f32<T>(dst + e), o[e]));
+  }
+  if (vec) {
+    if (f < d) store8(dst, o);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (f + e < d) dst[e] = from_f32<T>(o[e]);
+  }
+}
+
+constexpr int kEmbSmallBucket = 32;      // buckets up to this size are sorted and summed by one warp
+
+// one warp per table row: ascending-order float32 segment sum, dtype rounding as the reference.
+// Rows with more than kEmbSmallBucket tokens are left to emb_big_bucket_kernel.
 template <typename T>
 __global__ void __launch_bounds__(256)
 emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restrict__ offsets,
@@ -204,8 +298,9 @@ emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restri
   if (k >= vocab) return;
   const int off = offsets[k];
   const int cnt = offsets[k + 1] - off;
+  if (cnt > kEmbSmallBucket) return;
   int mine = INT_MAX;
-  if (cnt > 0 && cnt <= 32) {
+  if (cnt > 0) {
     if (lane < cnt) mine = perm[off + lane];
     // bitonic sort of 32 keys across the warp, ascending
 #pragma unroll
@@ -223,57 +318,95 @@ emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restri
   // each lane owns 8 consecutive features per step (16-byte loads and stores when d % 8 == 0)
   const bool vec = (d % 8 == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0) &&
                    ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
-  auto add_row = [&](int j, int f, float (&acc)[8]) {
-    const T* row = G + static_cast<long long>(j) * d + f;
-    float x[8];
-    if (vec) {
-      if (f < d) {
-        load8(row, x);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) x[e] = 0.f;
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) x[e] = (f + e < d) ? ld_f32<T>(row + e) : 0.f;
-    }
-    // no fma contraction: product and sum are rounded separately, as the reference does
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = __fadd_rn(acc[e], round_to<T>(__fmul_rn(x[e], pre_scale)));
-  };
   for (int fbase = 0; fbase < d; fbase += 256) {      // warp-uniform trip count (shuffles inside)
     const int f = fbase + lane * 8;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (cnt > 0 && cnt <= 32) {
-      for (int i = 0; i < cnt; ++i) add_row(__shfl_sync(0xffffffffu, mine, i), f, acc);
-    } else if (cnt > 32) {
-      // selection in ascending token order: next = min{perm[i] : perm[i] > last}
-      int last = -1;
-      for (int i = 0; i < cnt; ++i) {
-        int best = INT_MAX;
-        for (int q = lane; q < cnt; q += 32) {
-          const int j = perm[off + q];
-          if (j > last && j < best) best = j;
+    for (int i = 0; i < cnt; ++i) {
+      float x[8];
+      emb_load_row<T>(G, __shfl_sync(0xffffffffu, mine, i), d, f, vec, x);
+      emb_accumulate<T>(x, pre_scale, acc);
+    }
+    emb_store_row<T>(out, k, d, f, vec, acc, divisor, accumulate);
+  }
+}
+
+// Rows that many tokens share (padding, separators, position ids of a large batch).  The list of
+// such rows is compacted by emb_list_big_kernel; one CTA per listed row first sorts the row's token
+// list into ascending order -- a bitonic network whose comparators all point the same way, so
+// entries past the end of the list act as +infinity without being stored; in shared memory up to
+// `smem_cap` entries, in place in global memory beyond -- and then sums the rows in that order.
+// The sum itself is sequential per feature (float addition in the CPU's order), so the loads of
+// the next eight rows are issued before the current eight are added.
+__global__ void emb_list_big_kernel(const int* __restrict__ offsets, int vocab, int* __restrict__ big,
+                                    int* __restrict__ n_big) {
+  for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < vocab; k += gridDim.x * blockDim.x)
+    if (offsets[k + 1] - offsets[k] > kEmbSmallBucket) big[atomicAdd(n_big, 1)] = k;
+}
+
+__device__ __forceinline__ void emb_bitonic_ascending(int* keys, int cnt, int n2, int tid, int nthreads) {
+  for (int k = 2; k <= n2; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      // the first stage of every merge pairs i with its mirror image inside the block of k
+      for (int i = tid; i < n2; i += nthreads) {
+        const int l = (j == (k >> 1)) ? (i ^ (k - 1)) : (i ^ j);
+        if (l > i && l < cnt) {
+          const int a = keys[i], b = keys[l];
+          if (a > b) { keys[i] = b; keys[l] = a; }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
-        last = best;
-        add_row(best, f, acc);
       }
+      __syncthreads();
     }
-    T* dst = out + static_cast<long long>(k) * d + f;
-    float o[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      o[e] = round_to<T>(__fdiv_rn(round_to<T>(acc[e]), divisor));
-      if (accumulate && f + e < d) o[e] = round_to<T>(__fadd_rn(ld_f32<T>(dst + e), o[e]));
-    }
-    if (vec) {
-      if (f < d) store8(dst, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+emb_big_bucket_kernel(const T* __restrict__ G, int d, const int* __restrict__ offsets, int* __restrict__ perm,
+                      const int* __restrict__ big, const int* __restrict__ n_big, int smem_cap,
+                      float pre_scale, float divisor, int accumulate, T* __restrict__ out) {
+  extern __shared__ int s_keys[];
+  const int tid = threadIdx.x;
+  const int total = *n_big;
+  const bool vec = (d % 8 == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
+  for (int bi = blockIdx.x; bi < total; bi += gridDim.x) {
+    const int k = big[bi];
+    const int off = offsets[k];
+    const int cnt = offsets[k + 1] - off;
+    int n2 = 64;
+    while (n2 < cnt) n2 <<= 1;
+    const int* keys;
+    __syncthreads();                      // the previous row's readers are done with s_keys
+    if (cnt <= smem_cap) {
+      for (int i = tid; i < cnt; i += blockDim.x) s_keys[i] = perm[off + i];
+      __syncthreads();
+      emb_bitonic_ascending(s_keys, cnt, n2, tid, blockDim.x);
+      keys = s_keys;
     } else {
+      __threadfence_block();
+      emb_bitonic_ascending(perm + off, cnt, n2, tid, blockDim.x);   // in place; the CTA owns this range
+      keys = perm + off;
+    }
+    for (int f = tid * 8; f < d; f += blockDim.x * 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float cur[8][8], nxt[8][8];
+      auto fetch = [&](int i0, float (&buf)[8][8]) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
-        if (f + e < d) dst[e] = from_f32<T>(o[e]);
+        for (int r = 0; r < 8; ++r)
+          if (i0 + r < cnt) emb_load_row<T>(G, keys[i0 + r], d, f, vec, buf[r]);
+      };
+      fetch(0, cur);
+      for (int i0 = 0; i0 < cnt; i0 += 8) {
+        fetch(i0 + 8, nxt);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (i0 + r < cnt) emb_accumulate<T>(cur[r], pre_scale, acc);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) cur[r][e] = nxt[r][e];
+      }
+      emb_store_row<T>(out, k, d, f, vec, acc, divisor, accumulate);
     }
   }
 }
@@ -284,8 +417,18 @@ static inline long long up256(long long x) { return (x + 255) / 256 * 256; }
 
 using namespace gb;
 
-extern "C" long long ghost_embedding_dot_workspace_bytes(int n_val, long long T, int vocab) {
+// head [vocab] + next [n_val * T]: the least a caller must provide.  With the full size below the
+// repeated-id path is enabled as well: cnt [vocab], a counter, and R [kEmbHotCap, n_val, d] float32.
+constexpr int kEmbHotCap = 256;
+static long long emb_dot_min_bytes(int n_val, long long T, int vocab) {
   return up256(4ll * vocab) + up256(4ll * n_val * T);
+}
+extern "C" long long ghost_embedding_dot_workspace_bytes_for(int n_val, long long T, int vocab, int d) {
+  return emb_dot_min_bytes(n_val, T, vocab) + up256(4ll * vocab) + 256 +
+         up256(4ll * kEmbHotCap * static_cast<long long>(n_val) * d);
+}
+extern "C" long long ghost_embedding_dot_workspace_bytes(int n_val, long long T, int vocab) {
+  return emb_dot_min_bytes(n_val, T, vocab);
 }
 
 extern "C" int ghost_embedding_dot(const long long* ids, const void* G, int is_f32, int n_train, int n_val,
@@ -303,27 +446,56 @@ extern "C" int ghost_embedding_dot(const long long* ids, const void* G, int is_f
   int* head = static_cast<int*>(ws);
   int* next = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + up256(4ll * vocab));
   const long long n_vtok = static_cast<long long>(n_val) * T;
+  // the repeated-id path needs the larger workspace (ghost_embedding_dot_workspace_bytes_for)
+  const bool hot = ws_bytes >= ghost_embedding_dot_workspace_bytes_for(n_val, T, vocab, d);
+  uint8_t* extra = static_cast<uint8_t*>(ws) + emb_dot_min_bytes(n_val, T, vocab);
+  int* cnt = hot ? reinterpret_cast<int*>(extra) : nullptr;
+  int* n_hot = hot ? reinterpret_cast<int*>(extra + up256(4ll * vocab)) : nullptr;
+  float* R = hot ? reinterpret_cast<float*>(extra + up256(4ll * vocab) + 256) : nullptr;
+  if (hot) GB_CUDA_OK(cudaMemsetAsync(cnt, 0, up256(4ll * vocab) + 256, st));
   GB_CUDA_OK(cudaMemsetAsync(head, 0xFF, 4ull * vocab, st));
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
   int blocks = static_cast<int>((n_vtok + 255) / 256);
   if (blocks > ds->sm_count * 8) blocks = ds->sm_count * 8;
-  emb_chain_val_kernel<<<blocks, 256, 0, st>>>(ids + static_cast<long long>(n_train) * T, n_vtok, vocab, head, next, ds->err_word);
+  emb_chain_val_kernel<<<blocks, 256, 0, st>>>(ids + static_cast<long long>(n_train) * T, n_vtok, vocab, head, next, cnt, ds->err_word);
   count_launch();
   int rc = post_launch("emb_chain_val_kernel");
   if (rc != GHOST_OK) return rc;
+  if (hot) {
+    // chains longer than four dot products per validation sample are worth summing up front
+    const int threshold = 4 * n_val > 16 ? 4 * n_val : 16;
+    if (n_vtok > threshold) {
+      GB_CUDA_OK(cudaMemsetAsync(R, 0, 4ull * kEmbHotCap * static_cast<size_t>(n_val) * d, st));
+      int vb = ceil_div(vocab, 256);
+      if (vb > ds->sm_count * 4) vb = ds->sm_count * 4;
+      emb_hot_assign_kernel<<<vb, 256, 0, st>>>(cnt, vocab, threshold, kEmbHotCap, n_hot);
+      int rb = static_cast<int>((n_vtok + 7) / 8);
+      if (rb > ds->sm_count * 8) rb = ds->sm_count * 8;
+      const long long* ids_val = ids + static_cast<long long>(n_train) * T;
+      if (is_f32)
+        emb_hot_reduce_kernel<float><<<rb, 256, 0, st>>>(ids_val, static_cast<const float*>(G) + static_cast<long long>(n_train) * T * d, n_vtok, T, d, n_val, vocab, cnt, R);
+      else
+        emb_hot_reduce_kernel<__nv_bfloat16><<<rb, 256, 0, st>>>(ids_val, static_cast<const __nv_bfloat16*>(G) + static_cast<long long>(n_train) * T * d, n_vtok, T, d, n_val, vocab, cnt, R);
+      count_launch(2);
+      if ((rc = post_launch("emb_hot_reduce_kernel")) != GHOST_OK) return rc;
+    }
+  }
   const int tok_per_block = 64;
   dim3 grid(ceil_div(T, tok_per_block), n_train);
   const size_t smem = sizeof(float) * n_val;
   if (is_f32)
-    emb_dot_kernel<float><<<grid, 256, smem, st>>>(ids, static_cast<const float*>(G), n_train, n_val, T, d, vocab, head, next, scale, M_out, tok_per_block, ds->err_word);
+    emb_dot_kernel<float><<<grid, 256, smem, st>>>(ids, static_cast<const float*>(G), n_train, n_val, T, d, vocab, head, next, cnt, R, scale, M_out, tok_per_block, ds->err_word);
   else
-    emb_dot_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(ids, static_cast<const __nv_bfloat16*>(G), n_train, n_val, T, d, vocab, head, next, scale, M_out, tok_per_block, ds->err_word);
+    emb_dot_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(ids, static_cast<const __nv_bfloat16*>(G), n_train, n_val, T, d, vocab, head, next, cnt, R, scale, M_out, tok_per_block, ds->err_word);
   count_launch();
   return post_launch("emb_dot_kernel");
 }
 
+// counts, offsets, cursor ([vocab + 1] each), the token permutation, and the list of rows with more
+// than kEmbSmallBucket tokens (its counter in front)
+static long long emb_big_list_bytes(long long n_tok) { return up256(4ll * (n_tok / (kEmbSmallBucket + 1) + 2)); }
 extern "C" long long ghost_embedding_wgrad_workspace_bytes(int n_train, long long T, int vocab) {
-  return 3 * up256(4ll * (vocab + 1)) + up256(4ll * n_train * T);
+  return 3 * up256(4ll * (vocab + 1)) + up256(4ll * n_train * T) + emb_big_list_bytes(static_cast<long long>(n_train) * T);
 }
 
 extern "C" int ghost_embedding_wgrad(const long long* ids, const void* G, int is_f32, int n_train, long long T,
@@ -344,18 +516,37 @@ extern "C" int ghost_embedding_wgrad(const long long* ids, const void* G, int is
   int* cursor = reinterpret_cast<int*>(w + 2 * seg);
   int* perm = reinterpret_cast<int*>(w + 3 * seg);
   const long long n_tok = static_cast<long long>(n_train) * T;
+  int* n_big = reinterpret_cast<int*>(w + 3 * seg + up256(4ll * n_tok));
+  int* big = n_big + 1;
   GB_CUDA_OK(cudaMemsetAsync(counts, 0, seg, st));
   GB_CUDA_OK(cudaMemsetAsync(cursor, 0, seg, st));
+  GB_CUDA_OK(cudaMemsetAsync(n_big, 0, 4, st));
   int blocks = static_cast<int>((n_tok + 255) / 256);
   if (blocks > ds->sm_count * 8) blocks = ds->sm_count * 8;
   emb_count_kernel<<<blocks, 256, 0, st>>>(ids, n_tok, vocab, counts, ds->err_word);
   emb_scan_kernel<<<1, 1024, 0, st>>>(counts, vocab, offsets);
   emb_fill_kernel<<<blocks, 256, 0, st>>>(ids, n_tok, vocab, offsets, cursor, perm);
-  if (is_f32)
+  int vblocks = ceil_div(vocab, 256);
+  if (vblocks > ds->sm_count * 4) vblocks = ds->sm_count * 4;
+  emb_list_big_kernel<<<vblocks, 256, 0, st>>>(offsets, vocab, big, n_big);
+  // rows shared by many tokens: sorted in up to 128 KB of shared memory (32768 tokens), else in place
+  constexpr int kSmemCap = 32768;
+  static bool attr_set[64] = {};
+  if (!attr_set[ds->device]) {
+    GB_CUDA_OK(cudaFuncSetAttribute(emb_big_bucket_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemCap * 4));
+    GB_CUDA_OK(cudaFuncSetAttribute(emb_big_bucket_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemCap * 4));
+    attr_set[ds->device] = true;
+  }
+  long long big_max = n_tok / (kEmbSmallBucket + 1) + 1;
+  const int big_blocks = static_cast<int>(big_max < ds->sm_count ? big_max : ds->sm_count);
+  if (is_f32) {
     emb_segsum_kernel<float><<<ceil_div(vocab, 8), 256, 0, st>>>(static_cast<const float*>(G), d, vocab, offsets, perm, pre_scale, divisor, accumulate, static_cast<float*>(out));
-  else
+    emb_big_bucket_kernel<float><<<big_blocks, 256, kSmemCap * 4, st>>>(static_cast<const float*>(G), d, offsets, perm, big, n_big, kSmemCap, pre_scale, divisor, accumulate, static_cast<float*>(out));
+  } else {
     emb_segsum_kernel<__nv_bfloat16><<<ceil_div(vocab, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(G), d, vocab, offsets, perm, pre_scale, divisor, accumulate, static_cast<__nv_bfloat16*>(out));
-  count_launch(4);
+    emb_big_bucket_kernel<__nv_bfloat16><<<big_blocks, 256, kSmemCap * 4, st>>>(static_cast<const __nv_bfloat16*>(G), d, offsets, perm, big, n_big, kSmemCap, pre_scale, divisor, accumulate, static_cast<__nv_bfloat16*>(out));
+  }
+  count_launch(6);
   return post_launch("ghost_embedding_wgrad");
 }
 

@@ -457,7 +457,7 @@ def embedding_dot(ids: torch.Tensor, G: torch.Tensor, n_val: int, vocab: int,
         raise ValueError("No training samples to compute dot product, check batch sizes.")
     M = torch.empty((n_val, n_train), dtype=_F32, device=G.device)
     arena = _Arena(G.device)
-    ws_bytes = int(lib.ghost_embedding_dot_workspace_bytes(n_val, T, vocab))
+    ws_bytes = int(lib.ghost_embedding_dot_workspace_bytes_for(n_val, T, vocab, d))
     off = arena.plan(ws_bytes)
     base = arena.commit()
     with _Timed("emb_dot_kernel", "hbm", 0.0, float(N) * T * d * G.element_size() + 8.0 * N * T):

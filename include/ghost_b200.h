@@ -177,8 +177,16 @@ int ghost_small_reduce_batch(const ghost_small_job* jobs, int n_jobs, void* stre
 
 /* ---- Embedding -------------------------------------------------------------------------------- */
 /* M[v,b] = scale * sum_{t,s : ids_b[t] == ids_v[s]} <G_b[t], G_v[s]>.  ids: int64 [N, T]; G: [N, T, d].
- * Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:181-211. */
+ * Validation tokens are chained per id; a train token walks the chain of its id.  The workspace
+ * must hold at least ghost_embedding_dot_workspace_bytes (the chain tables).  With
+ * ghost_embedding_dot_workspace_bytes_for or more, ids that more than max(16, 4 * n_val) validation
+ * tokens share (padding, separators; up to 256 such ids) are first summed per (id, validation
+ * sample), so a train token costs at most n_val dot products however often its id repeats; with the
+ * smaller workspace the work is sum over ids of count_train(id) * count_val(id) * d.  An id
+ * outside [0, vocab) contributes nothing and makes the next ghost_poll_kernel_error return
+ * GHOST_ERR_INDEX.  Replaces ghostEngines/supported_layers_grad_samplers_dotprod.py:181-211. */
 long long ghost_embedding_dot_workspace_bytes(int n_val, long long T, int vocab);
+long long ghost_embedding_dot_workspace_bytes_for(int n_val, long long T, int vocab, int d);
 int ghost_embedding_dot(const long long* ids, const void* G, int is_f32, int n_train, int n_val,
                         long long T, int d, int vocab, float scale, float* M_out, void* ws,
                         long long ws_bytes, void* stream);

@@ -328,6 +328,35 @@ def test_embedding_position_ids_and_golden(golden):
         assert np.array_equal(grad.cpu().float().numpy(), golden[f"emb_{tag}_train_grad"])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", [
+    # n_t, n_v, T, d, vocab, share of tokens that carry one and the same id
+    (6, 3, 200, 64, 50, 0.6),        # validation chain of ~360 tokens, train bucket of ~720
+    (64, 2, 48, 24, 48, None),       # position ids: every id 64 times in the train rows (> 32), twice in val
+    (40, 2, 1024, 16, 1000, 0.9),    # a train bucket above 32768 tokens: sorted in place in global memory
+    (5, 40, 64, 40, 30, 0.5)])       # many validation samples, feature size not a multiple of 16
+def test_embedding_with_heavily_repeated_ids(case, dtype):
+    """Padding-like batches: one id carried by most tokens.  The dot products go through the
+    per-(id, validation sample) pre-summed rows, the train gradient through the big-bucket kernel,
+    and the train gradient stays bit-identical to the CPU's sequential index_add_."""
+    n_t, n_v, T, d, vocab, share = case
+    N = n_t + n_v
+    g = torch.Generator().manual_seed(31)
+    if share is None:
+        ids = torch.arange(T).repeat(N, 1)
+    else:
+        ids = torch.randint(0, vocab, (N, T), generator=g)
+        ids[torch.rand(N, T, generator=g) < share] = 7
+    G = (torch.randn(N, T, d, generator=g) / d ** 0.5).to(dtype)
+    o = ops()
+    M = o.embedding_dot(ids.cuda(), G.cuda(), n_v, vocab)
+    grad = o.embedding_wgrad(ids.cuda(), G.cuda(), n_t, vocab, float(N), float(n_t))
+    after()
+    assert O.rel_fro(M, O.embedding_dot_exact(ids, G, n_v)) < (1e-5 if dtype == torch.float32 else 1e-4)
+    ref = O.embedding_train_grad(ids, G * N, n_v, vocab, sequential=True)
+    assert torch.equal(grad.cpu().float(), ref.float())
+
+
 def test_embedding_out_of_range_ids_are_reported():
     """An id outside the table makes the reference's index_add_ raise.  The kernels skip such a token
     and record it; the next poll of the error word raises IndexError."""
