@@ -789,6 +789,8 @@ KERNEL_CASES = {
     "gram_pair_T512": ("gram_pair", dict(n_t=256, n_v=32, T=512, d=4096, p=11008)),
     "gram_pair_small": ("gram_pair", dict(n_t=64, n_v=8, T=256, d=2048, p=4096)),
     "persample_cfc": ("persample", dict(n_t=32, n_v=8, T=1024, d=768, p=3072)),  # GPT-2 mlp.c_fc
+    "persample_cfc_colsum": ("persample", dict(n_t=32, n_v=8, T=1024, d=768, p=3072, colsum="Y")),
+    "persample_cproj_colsum": ("persample", dict(n_t=32, n_v=8, T=1024, d=3072, p=768, colsum="Y")),
     "persample_T512": ("persample", dict(n_t=256, n_v=32, T=512, d=4096, p=11008)),
     "persample_T2048": ("persample", dict(n_t=64, n_v=32, T=2048, d=4096, p=11008)),
     "wgrad_cfc": ("wgrad", dict(n_t=32, n_v=8, T=1024, d=768, p=3072)),
@@ -842,7 +844,11 @@ def run_kernels(args):
             if kind == "gram":
                 fn = lambda: ops.gram_dot(A, G, c["n_v"])
             elif kind == "persample":
-                fn = lambda: ops.persample_dot(G, A, c["n_v"], want_grad=True, grad_scale=1.0, grad_dtype=torch.bfloat16)
+                if c.get("colsum"):      # Conv1D orientation: X = activations, Y = out-grad, its column sums fused
+                    fn = lambda: ops.persample_dot(A, G, c["n_v"], want_grad=True, grad_scale=1.0,
+                                                   grad_dtype=torch.bfloat16, colsum_of=c["colsum"])
+                else:
+                    fn = lambda: ops.persample_dot(G, A, c["n_v"], want_grad=True, grad_scale=1.0, grad_dtype=torch.bfloat16)
             else:
                 fn = lambda: ops.wgrad(G[:c["n_t"]], A[:c["n_t"]], 1.0, torch.bfloat16)
         elif kind == "layernorm":
@@ -1306,12 +1312,17 @@ def main():
                          "Gram vs per-sample path over T on one Linear layer; gradproj_model: GradProj on a "
                          "Pythia-410M-shaped model")
     ap.add_argument("--only", default="", help="kernels mode: comma-separated case names")
+    ap.add_argument("--fuse-bias-colsums", type=int, default=-1,
+                    help="override the engines' FUSE_BIAS_COLSUMS switch (0 / 1) for an A/B run")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     guard_stdout()
+    if args.fuse_bias_colsums >= 0:
+        from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as _L
+        _L.FUSE_BIAS_COLSUMS = bool(args.fuse_bias_colsums)
     if args.mode == "kernels":
         run_kernels(args)
         return

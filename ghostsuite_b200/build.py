@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libghost_b200.so")
 SOURCES = ["common.cu", "ghost_gram.cu", "ghost_gram_pair.cu", "xty_gemm.cu", "xty_gemm_pair.cu", "tile_dot.cu", "rowwise.cu", "embedding.cu", "gradproj.cu", "proj_extras.cu", "workload_loss.cu"]
-HEADERS = ["common.cuh", "sm100_ptx.cuh", "mma_sync.cuh", os.path.join("..", "..", "include", "ghost_b200.h")]
+HEADERS = ["common.cuh", "sm100_ptx.cuh", "mma_sync.cuh", "xty_colsum.cuh", os.path.join("..", "..", "include", "ghost_b200.h")]
 
 
 def _nvcc() -> str:

@@ -22,6 +22,7 @@
 // allocator + MMA issuer.  128 x 256 fp32 accumulator, double-buffered in TMEM (512 columns).
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "xty_colsum.cuh"
 
 namespace gb {
 
@@ -45,10 +46,12 @@ struct XtyParams {
   long long ld_v;
   int v_is_f32;
   int sample_major;          // unit order (sample, tile), dealt round-robin to the CTAs; needs k_splits == 1
-  // per-sample column sums of one operand (bias terms), taken by four extra warps from the stages
-  // the MMAs consume: 0 = none, 1 = X, 2 = Y; out [all samples, cols of that operand] fp32
+  // per-sample column sums of one operand (bias terms), taken by four extra warps that read the
+  // operand rows through L2: 0 = none, 1 = X, 2 = Y; out [all samples, cols of that operand] fp32
   int colsum_of;
   float* colsum_out;
+  const __nv_bfloat16* cs_src;   // that operand, [all samples, T, cols], row pitch cs_ld
+  long long cs_ld;
   int blocked_x, blocked_y;  // operand map is the blocked 4-D form: one TMA per stage instead of one per 64 columns
   int* err;
 };
@@ -57,7 +60,8 @@ struct XtyCfg {
   static constexpr int BM = 128, BN = 256, BK = 64;
   static constexpr int kStageBytes = (BM + BN) * BK * 2;   // 48 KB
   static constexpr int kStages = 4;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kColsumBytes = 8 * 128 * 4;          // reduction scratch of the column-sum warps
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kColsumBytes;
 };
 
 // one 256-bit store (the address must be 32-byte aligned)
@@ -101,10 +105,8 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   uint64_t* empty_bar = bars + kStages;
   uint64_t* acc_full = bars + 2 * kStages;     // [2]
   uint64_t* acc_empty = acc_full + 2;          // [2]
-  uint64_t* cs_done = acc_empty + 2;           // [kStages], column-sum warps only
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cs_done + kStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* issued = abort_flag + 1;       // stages the producer has issued so far (column sums)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -125,14 +127,12 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
-      if (kColsum) mbar_init(&cs_done[s], 4);        // one arrival per column-sum warp
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);
     }
     *abort_flag = 0;
-    *issued = 0;
     fence_barrier_init();
   }
   if (warp == 5) {
@@ -176,26 +176,13 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      // column sums: a stage last filled for a summed unit may only be refilled once the
-      // column-sum warps have read it (bit s of the masks: stage s)
-      uint32_t cs_pending = 0, cs_phase = 0;
-      int n_issued = 0;
       for (long long u = u_begin; u < u_end && ok; u += u_step) {
         int tile, sample, kb0, kb1;
         decode(u, tile, sample, kb0, kb1);
         const int m0 = (tile / p.n_tiles) * BM;
         const int n0 = (tile % p.n_tiles) * BN;
-        const bool summed = kColsum && (p.colsum_of == 2 ? tile / p.n_tiles == 0 : tile % p.n_tiles == 0);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 411)) { ok = false; break; }
-          if (kColsum) {
-            const uint32_t bit = 1u << stage;
-            if (cs_pending & bit) {
-              if (!mbar_wait(&cs_done[stage], (cs_phase >> stage) & 1u, abort_flag, p.err, 412)) { ok = false; break; }
-              cs_phase ^= bit;
-            }
-            cs_pending = summed ? (cs_pending | bit) : (cs_pending & ~bit);
-          }
           uint8_t* st = smem + stage * Cfg::kStageBytes;
           mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           const int row = kb * BK;
@@ -216,9 +203,6 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             for (int j = 0; j < BN / 64; ++j)
               tma_load_3d(st + BM * BK * 2 + j * (BK * 128), &tm_y, &full_bar[stage], n0 + j * 64, row, z);
           }
-          // progress counter for the column-sum warps (they only look at it for summed units; no
-          // fence: they need no more than that every earlier phase of the stage is over)
-          if (kColsum) { ++n_issued; if (summed) *issued = n_issued; }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -257,61 +241,22 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
     }
   } else if (kColsum && warp >= 6) {
     // ---------------------------------------------------------------- column sums (warps 6-9)
-    // Thread j owns columns 2j, 2j+1 of the operand tile: one bf16x2 word per token row of the
-    // stage, conflict-free (a row of a panel is 128 bytes = 32 words, one per lane).  The sums are
-    // taken from the units whose other tile index is 0, which see each column block exactly once.
-    // Only the stages of summed units are waited for, read and acknowledged (cs_done); the producer
-    // waits for that acknowledgement before refilling such a stage.  Stages of other units are
-    // skipped by counting.  Because a barrier wait only knows the parity of the phase it waits
-    // for, the warps first wait until the producer's progress counter says that the stage has been
-    // issued: from then on its full barrier can only be in the wanted phase or just past it.  The
-    // four warps do not synchronise with one another.
-    const int j = threadIdx.x - 192;                       // 0..127
+    // The sums of a (sample, column block) are taken by the unit whose other tile index is 0,
+    // which sees each column block exactly once; see xty_colsum.cuh.
+    float* red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + 1024 + 256);
+    const int ct = static_cast<int>(threadIdx.x) - 192;
     const bool of_y = p.colsum_of == 2;
-    const int cols_tile = of_y ? BN : BM;
-    const int col = 2 * j;                                 // column inside the tile
-    const bool own = col < cols_tile;
-    const uint32_t op_off = of_y ? BM * BK * 2 : 0;
-    // address of token row 0: panel (col / 64), 16-byte chunk (col % 64) / 8, word ((col % 8) / 2)
-    const uint32_t base_off = op_off + (col >> 6) * (BK * 128) + (((col & 63) >> 1) & 3) * 4;
-    const int chunk = (col & 63) >> 3;
     const int total_cols = of_y ? p.n_cols : p.m_cols;
-    int kcount = 0;                                        // stages of this CTA before the current unit
-    bool alive = true;
-    for (long long u = u_begin; u < u_end && alive; u += u_step) {
+    for (long long u = u_begin; u < u_end; u += u_step) {
       int tile, sample, kb0, kb1;
       decode(u, tile, sample, kb0, kb1);
       const int tm = tile / p.n_tiles, tn = tile % p.n_tiles;
-      const bool summed = of_y ? tm == 0 : tn == 0;
-      if (!summed) { kcount += kb1 - kb0; continue; }
-      float s0 = 0.f, s1 = 0.f;
-      for (int kb = kb0; kb < kb1; ++kb, ++kcount) {
-        const int stage = kcount % kStages;
-        const uint32_t phase = (kcount / kStages) & 1;
-        int ok = 1;
-        if (lane == 0)
-          ok = (counter_wait(issued, kcount, abort_flag, p.err, 615) &&
-                mbar_wait(&full_bar[stage], phase, abort_flag, p.err, 616)) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { alive = false; break; }
-        if (own) {
-          const uint8_t* st = smem + stage * Cfg::kStageBytes + base_off;
-#pragma unroll 8
-          for (int t = 0; t < BK; ++t) {
-            const uint32_t w = *reinterpret_cast<const uint32_t*>(st + t * 128 + ((chunk ^ (t & 7)) << 4));
-            s0 += __uint_as_float(w << 16);
-            s1 += __uint_as_float(w & 0xffff0000u);
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&cs_done[stage]);
-      }
-      if (own && alive) {
-        const int c = (of_y ? tn * BN : tm * BM) + col;
-        float* dst = p.colsum_out + static_cast<long long>(p.sample0 + sample) * total_cols + c;
-        if (c < total_cols) dst[0] = s0;
-        if (c + 1 < total_cols) dst[1] = s1;
-      }
+      if (!(of_y ? tm == 0 : tn == 0)) continue;
+      const long long s_idx = p.sample0 + sample;
+      const int width = of_y ? BN : BM;
+      for (int half = 0; half < width; half += 128)
+        xty_colsum_128(p.cs_src + s_idx * p.T * p.cs_ld, p.T, p.cs_ld, (of_y ? tn * BN : tm * BM) + half, total_cols,
+                       red, p.colsum_out + s_idx * total_cols, ct, 1);
     }
   } else {
     // ---------------------------------------------------------------- epilogue
@@ -434,7 +379,7 @@ __global__ void xty_finalize_kernel(const float* __restrict__ ws, long long ld_w
 // CTA-pair variant of the tile-store pass (xty_gemm_pair.cu)
 int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_total, long long T, int m_cols,
                           int n_cols, long long ldx, long long ldy, int samples, int sample0, void* vgrad,
-                          int v_is_f32, const DeviceState* ds, cudaStream_t st);
+                          int v_is_f32, int colsum_of, float* colsum_out, const DeviceState* ds, cudaStream_t st);
 int launch_xty_pair_wgrad(const void* X, const void* Y, long long n_rows, int m_cols, int n_cols, long long ldx,
                           long long ldy, float* acc_ws, long long ld_acc, const DeviceState* ds, cudaStream_t st);
 bool xty_pair_usable(const DeviceState* ds);
@@ -639,6 +584,8 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   p.v_is_f32 = v_is_f32;
   p.colsum_of = colsum_of;
   p.colsum_out = colsum_out;
+  p.cs_src = static_cast<const __nv_bfloat16*>(colsum_of == 1 ? X : Y);
+  p.cs_ld = (colsum_of == 1) ? ldx : ldy;
   p.err = ds->err_word;
   const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
   const int group = persample_group(n_train, n_val, tiles, esize, kPersampleBudget);
@@ -652,11 +599,11 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
   GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
   // tile pass: the CTA-pair kernel when it is selected and applicable, else the single-CTA kernel
   const bool use_pair = pair_kernel_fits(g_persample_pair_mode, m_cols, n_cols) && p.blocked_x && p.blocked_y &&
-                        colsum_of == 0 && xty_pair_usable(ds);
+                        xty_pair_usable(ds);
   auto tile_pass = [&](const XtyParams& q) -> int {
     if (use_pair)
       return launch_xty_pair_tiles(X, Y, N, T, m_cols, n_cols, ldx, ldy, q.samples, q.sample0, q.vgrad,
-                                   v_is_f32, ds, st);
+                                   v_is_f32, colsum_of, colsum_out, ds, st);
     return launch_xty(tx, ty, q, ds, st);
   };
   if (group == n_train) {

@@ -23,6 +23,7 @@
 // fetches what it needs itself.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "xty_colsum.cuh"
 
 namespace gb {
 
@@ -38,6 +39,13 @@ struct XtyPairParams {
   int kb_per_split;          // row blocks (BK tokens) per split (accumulate)
   float* acc_ws;             // [m_cols, ld_acc] fp32, zeroed by the host
   long long ld_acc;
+  // per-sample column sums of one operand (the bias terms' input), taken by four extra warps that
+  // read the operand rows through L2 while the tensor core works: 0 none, 1 X, 2 Y
+  int cs_of;
+  const __nv_bfloat16* cs_src;   // that operand, [n_samples_total, T, cs_cols], row pitch cs_ld
+  long long cs_ld;
+  int cs_cols;
+  float* cs_out;             // [n_samples_total, cs_cols] fp32
   int* err;
 };
 
@@ -48,7 +56,8 @@ struct XtyPairCfg {
   static constexpr int BK = 128;           // tokens per stage: eight MMAs per barrier round trip
   static constexpr int kStageBytes = (BM + BNH) * BK * 2;   // 64 KB
   static constexpr int kStages = 3;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kColsumBytes = 8 * 128 * 4;          // cross-row-lane reduction of the column-sum warps
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kColsumBytes;
 };
 
 __device__ __forceinline__ void st_global_v8_pair(void* addr, const uint32_t* v) {
@@ -71,7 +80,7 @@ __device__ __forceinline__ void red_add_row32_pair(float* dst, const uint32_t (&
   }
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                      const XtyPairParams p) {
   using Cfg = XtyPairCfg;
@@ -199,6 +208,23 @@ xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ column sums (warps 6-9, both CTAs)
+    // Present only in launches that ask for them (320 threads).  For every (sample, 256-column
+    // block) of the chosen operand, the pair that runs the block's first unit sums the sample's
+    // token rows of that block: CTA r the 128 columns it also loads for the tensor core.
+    float* red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + 1024 + 256);
+    const int ct = static_cast<int>(threadIdx.x) - 192;
+    for (long long u = pair; u < units; u += num_pairs) {
+      int sample, tm, tn;
+      decode(u, sample, tm, tn);
+      const bool mine = (p.cs_of == 1) ? (tn == 0) : (tm == 0);
+      if (!mine) continue;
+      const int cbase = ((p.cs_of == 1) ? tm : tn) * BN + static_cast<int>(rank) * 128;
+      const long long s_idx = p.sample0 + sample;
+      xty_colsum_128(p.cs_src + s_idx * p.T * p.cs_ld, p.T, p.cs_ld, cbase, p.cs_cols, red,
+                     p.cs_out + s_idx * p.cs_cols, ct, 1);
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 0-3, both CTAs)
     int acc = 0;
@@ -319,7 +345,7 @@ bool xty_pair_usable(const DeviceState* ds) {
 // of 64.  Writes the tiles of samples [sample0, sample0 + samples) to vgrad ([tile][samples][128][256]).
 int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_total, long long T, int m_cols,
                           int n_cols, long long ldx, long long ldy, int samples, int sample0, void* vgrad,
-                          int v_is_f32, const DeviceState* ds, cudaStream_t st) {
+                          int v_is_f32, int colsum_of, float* colsum_out, const DeviceState* ds, cudaStream_t st) {
   using Cfg = XtyPairCfg;
   XtyPairParams p;
   p.m_cols = m_cols;
@@ -336,6 +362,11 @@ int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_tota
   p.kb_per_split = 0;
   p.acc_ws = nullptr;
   p.ld_acc = 0;
+  p.cs_of = (colsum_out != nullptr) ? colsum_of : 0;
+  p.cs_src = static_cast<const __nv_bfloat16*>(p.cs_of == 1 ? X : Y);
+  p.cs_ld = (p.cs_of == 1) ? ldx : ldy;
+  p.cs_cols = (p.cs_of == 1) ? m_cols : n_cols;
+  p.cs_out = colsum_out;
   p.err = ds->err_word;
   CUtensorMap tx, ty;
   int rc;
@@ -345,7 +376,7 @@ int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_tota
   const long long units = static_cast<long long>(p.m_tiles) * p.n_tiles * samples;
   long long pairs = ds->sm_count / 2;
   if (pairs > units) pairs = units;
-  xty_gemm_pair_kernel<<<static_cast<int>(2 * pairs), 192, Cfg::kSmemBytes, st>>>(tx, ty, p);
+  xty_gemm_pair_kernel<<<static_cast<int>(2 * pairs), p.cs_of ? 320 : 192, Cfg::kSmemBytes, st>>>(tx, ty, p);
   count_launch();
   return post_launch("xty_gemm_pair_kernel");
 }
@@ -369,6 +400,11 @@ int launch_xty_pair_wgrad(const void* X, const void* Y, long long n_rows, int m_
   p.accumulate = 1;
   p.acc_ws = acc_ws;
   p.ld_acc = ld_acc;
+  p.cs_of = 0;
+  p.cs_src = nullptr;
+  p.cs_ld = 0;
+  p.cs_cols = 0;
+  p.cs_out = nullptr;
   p.err = ds->err_word;
   const long long pairs_max = ds->sm_count / 2;
   const int kb = static_cast<int>(ceil_div(n_rows, static_cast<long long>(Cfg::BK)));

@@ -256,9 +256,10 @@ def _backprop_scale(layer: nn.Module) -> float:
     return float(getattr(layer, "_ghost_backprop_scale", 1.0))
 
 
-#: take the bias terms' per-sample column sums of the out-grad inside the per-sample GEMM pass
-#: (extra warps of that kernel) instead of a separate pass over the out-grad
-FUSE_BIAS_COLSUMS = False
+#: take the bias terms' per-sample column sums of the out-grad inside the per-sample GEMM pass (four
+#: extra warps of that kernel read the out-grad rows through L2 while the tensor core works on them)
+#: instead of a separate pass over the out-grad from HBM
+FUSE_BIAS_COLSUMS = True
 
 
 def _bias_terms(layer: nn.Module, B: torch.Tensor, val_batch_size: int, colsums=None) -> None:

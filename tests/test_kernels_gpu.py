@@ -172,7 +172,10 @@ def test_persample_dot(case, dtype):
     assert O.rel_fro(M, M2.cpu()) < TOL[dtype]
 
 
-@pytest.mark.parametrize("case", [(5, 3, 6, 16, 24), (3, 1, 130, 72, 40), (2, 2, 300, 200, 136), (9, 4, 70, 264, 520)])
+@pytest.mark.parametrize("case", [(5, 3, 6, 16, 24), (3, 1, 130, 72, 40), (2, 2, 300, 200, 136), (9, 4, 70, 264, 520),
+                                  # column counts that take the CTA-pair kernel (multiples of 64, an even
+                                  # number of 128-row tiles), T not a multiple of 32
+                                  (5, 3, 130, 256, 512), (3, 2, 77, 768, 256), (4, 2, 1024, 512, 1024)])
 @pytest.mark.parametrize("which", ["X", "Y"])
 def test_persample_dot_column_sums(case, which):
     """Per-sample column sums of one operand taken inside the GEMM pass (the bias terms)."""
