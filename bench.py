@@ -569,21 +569,28 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ms_torch_loss, _, _ = timed(step, False, False)
     model.cfg.fused_loss = True
 
-    # the fixed-batch step replayed from a CUDA graph (validation replicated)
+    # the fixed-batch step replayed from a CUDA graph (validation replicated; with more than one GPU
+    # also with the validation batch sharded)
     graph_note = None
-    try:
-        step, graph_launches, h2d = make_graph_step("val_replicated")
-        for i in range(args.warmup):
-            step(i, False)
-        torch.cuda.synchronize()
-        ms_dev, _, _ = timed(step, False, False)
-        ms_e2e, _, _ = timed(step, True, False)
-        results["val_replicated_cuda_graph"] = {"ms_dev": ms_dev, "ms_e2e": ms_e2e, "launches": graph_launches * args.steps,
-                                                "h2d": h2d}
-        names.insert(1, "val_replicated_cuda_graph")
-        _lib.poll_kernel_error()
-    except Exception as exc:
-        graph_note = f"not measured: {exc}"
+    for base in (["val_replicated"] if world == 1 else ["val_replicated", "val_sharded"]):
+        try:
+            step, graph_launches, h2d = make_graph_step(base)
+            for i in range(args.warmup):
+                step(i, False)
+            torch.cuda.synchronize()
+            ms_dev, _, _ = timed(step, False, False)
+            ms_e2e, _, _ = timed(step, True, False)
+            rec = {"ms_dev": ms_dev, "ms_e2e": ms_e2e, "launches": graph_launches * args.steps, "h2d": h2d}
+            sv = getattr(state["engine"], "_ghost_val_shard", None)
+            if sv is not None:              # counted once, at capture (plus the two eager warm-up steps)
+                rec["val_gather_calls_per_step"] = sv.calls / 3
+                rec["val_gather_bytes_per_step"] = sv.bytes / 3
+            results[base + "_cuda_graph"] = rec
+            names.insert(1, base + "_cuda_graph")
+            _lib.poll_kernel_error()
+        except Exception as exc:
+            graph_note = f"{base}: not measured: {exc}"
+            break
 
     if rank != 0:
         state["engine"].detach()
@@ -606,7 +613,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     roof = dominant_kernel_roofline(prof, peaks)
     how = {"val_replicated": "validation batch replicated, eager launches",
            "val_replicated_cuda_graph": "validation batch replicated, step replayed from a CUDA graph",
-           "val_sharded": "validation batch sharded, per-layer all-gather of its operands"}[best]
+           "val_sharded": "validation batch sharded, per-layer all-gather of its operands",
+           "val_sharded_cuda_graph": "validation batch sharded (per-layer all-gather of its operands), step replayed "
+                                     "from a CUDA graph"}[best]
     if world == 1:
         parallelism = f"1 GPU; {how} (the fastest of the variants measured in this run)"
     else:
@@ -630,8 +639,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "kernel_time_share": prof["share"] if prof else None,
         "library_ms_per_step": (prof["total_ms"] / args.steps) if prof else None,
         "variants": variants,
-        "cuda_graph_note": graph_note or "val_replicated_cuda_graph: the same step captured once (forward, backward with "
-                           "the hooks, collectives, optimizer) and replayed; ids copied in before, result read back after",
+        "cuda_graph_note": graph_note or "*_cuda_graph: the same step captured once (forward, backward with the hooks, "
+                           "collectives, optimizer) and replayed; ids copied in before, result read back after",
         "weak_scaling": weak,
         "ms_per_step_torch_loss": ms_torch_loss / args.steps,
     }
