@@ -707,10 +707,12 @@ def dominant_kernel_roofline(prof, peaks):
         achieved = rec["flops"] / calls / avg_s / 1e12
         traffic = None
         if "persample" in name:
-            # ncu capture of the mlp.c_fc shape: 669 MB of DRAM traffic per call (315 MB inputs read
-            # once, 159 MB of tile write-back, 189 MB of tiles read once, 6 MB of results) for
-            # 315 MB of input bytes; scaled by input bytes
-            traffic = rec["bytes"] / calls * (669.0 / 315.0)
+            # ncu capture of the mlp.c_fc shape with the bias column sums inside the GEMM kernel: 800.5 MB
+            # of DRAM traffic per call -- GEMM pass 445.3 MB read (315 MB of inputs once + 130 MB of
+            # out-grad rows the column-sum warps did not find in L2) and 160.5 MB of tile write-back,
+            # streaming pass 188.8 MB of tiles read once and 5.9 MB of results -- for 315 MB of input
+            # bytes; scaled by input bytes
+            traffic = rec["bytes"] / calls * (800.5 / 315.0)
         return {"kernel": name, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor"],
                 "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": traffic,
                 "launches": calls, "avg_ms": avg_s * 1e3, "peak_source": peaks["source"]}
