@@ -12,13 +12,16 @@
 
 namespace gb {
 
-// Sums rows [0, T) of columns [cbase, cbase + 128) of `src` (row pitch ld, 16-byte aligned, column
-// count a multiple of 8) and stores them to out[cbase ..].  ct = 0..127 is the thread's index among
-// the column-sum warps; red is 8 * 128 floats of shared memory; sixteen 16-byte loads are in flight
-// per thread (32 KB per CTA), so that a unit's sums arrive before the tensor core is done with it.
-__device__ __forceinline__ void xty_colsum_128(const __nv_bfloat16* __restrict__ src, long long T, long long ld,
-                                               int cbase, int total_cols, float* red, float* __restrict__ out,
-                                               int ct, int bar_id) {
+// Sums rows [t_begin, t_end) of columns [cbase, cbase + 128) of `src` (row pitch ld, 16-byte aligned,
+// column count a multiple of 8) and adds them to out[cbase ..] (zeroed by the host: every unit
+// that works on a (sample, column block) takes its share of the sample's rows, so the column-sum
+// warps of a unit never have more to read than its tensor-core work covers and read the rows the
+// TMA producer is fetching at that moment).  ct = 0..127 is the thread's index among the
+// column-sum warps; red is 8 * 128 floats of shared memory; up to sixteen 16-byte loads are in
+// flight per thread.
+__device__ __forceinline__ void xty_colsum_128(const __nv_bfloat16* __restrict__ src, long long t_begin,
+                                               long long T, long long ld, int cbase, int total_cols, float* red,
+                                               float* __restrict__ out, int ct, int bar_id) {
   const int cv = ct & 15, rl = ct >> 4;     // 16 column vectors x 8 row lanes
   const int c0 = cbase + cv * 8;
   float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -32,7 +35,7 @@ __device__ __forceinline__ void xty_colsum_128(const __nv_bfloat16* __restrict__
         a[2 * e + 1] += __uint_as_float(ww[e] & 0xffff0000u);
       }
     };
-    long long t = rl;
+    long long t = t_begin + rl;
     for (; t + 120 < T; t += 128) {
       uint4 w[16];
 #pragma unroll
@@ -55,7 +58,7 @@ __device__ __forceinline__ void xty_colsum_128(const __nv_bfloat16* __restrict__
   float sum = 0.f;
 #pragma unroll
   for (int r = 0; r < 8; ++r) sum += red[r * 128 + ct];
-  if (cbase + ct < total_cols) out[cbase + ct] = sum;
+  if (cbase + ct < total_cols && sum != 0.f) atomicAdd(out + cbase + ct, sum);
   asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
 }
 

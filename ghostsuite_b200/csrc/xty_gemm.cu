@@ -241,8 +241,8 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
     }
   } else if (kColsum && warp >= 6) {
     // ---------------------------------------------------------------- column sums (warps 6-9)
-    // The sums of a (sample, column block) are taken by the unit whose other tile index is 0,
-    // which sees each column block exactly once; see xty_colsum.cuh.
+    // Every unit adds its share of the sample's token rows to the sums of its column block; see
+    // xty_colsum.cuh.
     float* red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + 1024 + 256);
     const int ct = static_cast<int>(threadIdx.x) - 192;
     const bool of_y = p.colsum_of == 2;
@@ -251,11 +251,16 @@ xty_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       int tile, sample, kb0, kb1;
       decode(u, tile, sample, kb0, kb1);
       const int tm = tile / p.n_tiles, tn = tile % p.n_tiles;
-      if (!(of_y ? tm == 0 : tn == 0)) continue;
+      // the units that share this (sample, column block) split the sample's token rows among them
+      const int part = of_y ? tm : tn, parts = of_y ? p.m_tiles : p.n_tiles;
+      const long long per = ((p.T + parts - 1) / parts + 7) / 8 * 8;
+      const long long t0 = part * per;
+      const long long t1 = (t0 + per < p.T) ? t0 + per : p.T;
+      if (t0 >= t1) continue;
       const long long s_idx = p.sample0 + sample;
       const int width = of_y ? BN : BM;
       for (int half = 0; half < width; half += 128)
-        xty_colsum_128(p.cs_src + s_idx * p.T * p.cs_ld, p.T, p.cs_ld, (of_y ? tn * BN : tm * BM) + half, total_cols,
+        xty_colsum_128(p.cs_src + s_idx * p.T * p.cs_ld, t0, t1, p.cs_ld, (of_y ? tn * BN : tm * BM) + half, total_cols,
                        red, p.colsum_out + s_idx * total_cols, ct, 1);
     }
   } else {
@@ -414,8 +419,13 @@ static int launch_xty(const CUtensorMap& tx, const CUtensorMap& ty, XtyParams p,
   int grid = static_cast<int>(units < ds->sm_count ? units : ds->sm_count);
   p.units_per_cta = static_cast<int>((units + grid - 1) / grid);
   if (!p.sample_major) grid = static_cast<int>((units + p.units_per_cta - 1) / p.units_per_cta);
-  if (p.colsum_of != 0 && p.colsum_out != nullptr)
+  if (p.colsum_of != 0 && p.colsum_out != nullptr) {
+    // the column-sum warps add into the output: zero the rows of this launch's samples first
+    const int cs_cols = p.colsum_of == 2 ? p.n_cols : p.m_cols;
+    GB_CUDA_OK(cudaMemsetAsync(p.colsum_out + static_cast<long long>(p.sample0) * cs_cols, 0,
+                               sizeof(float) * static_cast<size_t>(p.samples) * cs_cols, st));
     xty_gemm_kernel<true><<<grid, 320, XtyCfg::kSmemBytes, st>>>(tx, ty, p);
+  }
   else
     xty_gemm_kernel<false><<<grid, 192, XtyCfg::kSmemBytes, st>>>(tx, ty, p);
   count_launch();

@@ -210,19 +210,23 @@ xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ column sums (warps 6-9, both CTAs)
-    // Present only in launches that ask for them (320 threads).  For every (sample, 256-column
-    // block) of the chosen operand, the pair that runs the block's first unit sums the sample's
-    // token rows of that block: CTA r the 128 columns it also loads for the tensor core.
+    // Present only in launches that ask for them (320 threads).  Every unit adds its share of the
+    // sample's token rows of the chosen operand's 256-column block to the sums: CTA r the 128
+    // columns it also loads for the tensor core.
     float* red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + 1024 + 256);
     const int ct = static_cast<int>(threadIdx.x) - 192;
     for (long long u = pair; u < units; u += num_pairs) {
       int sample, tm, tn;
       decode(u, sample, tm, tn);
-      const bool mine = (p.cs_of == 1) ? (tn == 0) : (tm == 0);
-      if (!mine) continue;
+      // the units that share this (sample, column block) split the sample's token rows among them
+      const int part = (p.cs_of == 1) ? tn : tm, parts = (p.cs_of == 1) ? p.n_tiles : p.m_tiles;
+      const long long per = ((p.T + parts - 1) / parts + 7) / 8 * 8;
+      const long long t0 = part * per;
+      const long long t1 = (t0 + per < p.T) ? t0 + per : p.T;
+      if (t0 >= t1) continue;
       const int cbase = ((p.cs_of == 1) ? tm : tn) * BN + static_cast<int>(rank) * 128;
       const long long s_idx = p.sample0 + sample;
-      xty_colsum_128(p.cs_src + s_idx * p.T * p.cs_ld, p.T, p.cs_ld, cbase, p.cs_cols, red,
+      xty_colsum_128(p.cs_src + s_idx * p.T * p.cs_ld, t0, t1, p.cs_ld, cbase, p.cs_cols, red,
                      p.cs_out + s_idx * p.cs_cols, ct, 1);
     }
   } else {
@@ -368,6 +372,9 @@ int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_tota
   p.cs_cols = (p.cs_of == 1) ? m_cols : n_cols;
   p.cs_out = colsum_out;
   p.err = ds->err_word;
+  if (p.cs_of)
+    GB_CUDA_OK(cudaMemsetAsync(colsum_out + static_cast<long long>(sample0) * p.cs_cols, 0,
+                               sizeof(float) * static_cast<size_t>(samples) * p.cs_cols, st));
   CUtensorMap tx, ty;
   int rc;
   if ((rc = make_tmap_bf16_blocks(&tx, X, n_samples_total, T, m_cols, ldx, Cfg::BK, Cfg::BM / 64)) != GHOST_OK) return rc;
