@@ -115,11 +115,10 @@ int ghost_set_wgrad_pair_mode(int mode);
 /* colsum_of = 1 (X) or 2 (Y) also writes the per-sample column sums of that operand,
  * colsum_out[s, c] = sum_t operand[s, t, c] (fp32, [n_train + n_val, cols]): the bias terms of
  * ghostEngines/supported_layers_grad_samplers_dotprod.py:138-146, 454-471 without a second pass over
- * the out-grad (four extra warps read the operand stages the MMAs consume).  Only meaningful when
- * the operand holds the values themselves (not the hi/lo split of fp32 data); 0 = off.  On the
- * shapes measured so far this costs the GEMM more than the separate ghost_colsum pass takes (the
- * extra shared-memory reads compete with the tensor core's operand fetch), so the Python layer
- * leaves it off. */
+ * the out-grad: four extra warps of the GEMM kernel read the operand rows through L2 while the TMA
+ * producer fetches the same rows for the tensor core (about 5 % on the GEMM call, less than the
+ * separate ghost_colsum pass).  Only meaningful when the operand holds the values themselves (not the
+ * hi/lo split of fp32 data); 0 = off. */
 int ghost_persample_dot_bf16(const void* X, const void* Y, int n_train, int n_val, long long T,
                              int m_cols, int n_cols, long long ldx, long long ldy, float dot_scale,
                              float* M_out, int v_is_f32, void* grad_out, int grad_is_f32,
