@@ -943,6 +943,7 @@ KERNEL_CASES = {
     "colsum_3072": ("colsum", dict(N=40, T=1024, p=3072)),
     "embedding_wte": ("embedding", dict(n_t=32, n_v=8, T=1024, d=768, vocab=50257)),
     # half of all tokens share one id (padding-like): every such train token walks a chain of ~4096 validation tokens
+    "embedding_wpe": ("embedding", dict(n_t=32, n_v=8, T=1024, d=768, vocab=1024, positions=True)),   # GPT-2 position table
     "embedding_repeated_ids": ("embedding", dict(n_t=32, n_v=8, T=1024, d=768, vocab=50257, repeat_frac=0.5)),
     "gradproj_llama_q": ("gradproj", dict(B=8, T=4096, n_i=4096, n_o=4096, k=64)),
     "gradproj_llama_gate": ("gradproj", dict(B=8, T=4096, n_i=4096, n_o=14336, k=64)),
@@ -1004,6 +1005,8 @@ def run_kernels(args):
         elif kind == "embedding":
             N = c["n_t"] + c["n_v"]
             ids = torch.randint(0, c["vocab"], (N, c["T"]), generator=g, device=dev)
+            if c.get("positions"):       # every sample holds the ids 0 .. T - 1 in order
+                ids = torch.arange(c["T"], device=dev).repeat(N, 1)
             if c.get("repeat_frac"):
                 hot = torch.rand(N, c["T"], generator=g, device=dev) < c["repeat_frac"]
                 ids = torch.where(hot, torch.zeros_like(ids), ids)

@@ -191,43 +191,57 @@ __global__ void emb_count_kernel(const long long* __restrict__ ids, long long n_
   }
 }
 
-// exclusive scan of counts[0..vocab) into offsets (single block of 1024 threads)
+constexpr int kEmbSmallBucket = 32;      // buckets up to this size are sorted and summed by one warp
+
+// Exclusive scan of counts[0..vocab) into offsets (single block of 1024 threads; tiles of 4096 ids,
+// four consecutive ids per thread, the next tile's loads issued before this tile is scanned), and
+// the list of rows with more than kEmbSmallBucket tokens for emb_big_bucket_kernel.
 __global__ void __launch_bounds__(1024)
-emb_scan_kernel(const int* __restrict__ counts, int vocab, int* __restrict__ offsets) {
-  __shared__ int s_warp[32];
-  __shared__ int s_carry;
-  if (threadIdx.x == 0) s_carry = 0;
-  __syncthreads();
+emb_scan_kernel(const int* __restrict__ counts, int vocab, int* __restrict__ offsets, int* __restrict__ big,
+                int* __restrict__ n_big) {
+  __shared__ int s_warp[2][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int base = 0; base < vocab; base += 1024) {
-    const int i = base + threadIdx.x;
-    const int c = (i < vocab) ? counts[i] : 0;
-    int x = c;
+  auto load4 = [&](int base, int (&c)[4]) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) c[e] = (base + e < vocab) ? counts[base + e] : 0;
+  };
+  int carry = 0, cur[4], nxt[4];
+  load4(threadIdx.x * 4, cur);
+  int buf = 0;
+  for (int tile = 0; tile < vocab; tile += 4096, buf ^= 1) {
+    const int base = tile + threadIdx.x * 4;
+    load4(base + 4096, nxt);
+    const int total = cur[0] + cur[1] + cur[2] + cur[3];
+    int x = total;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int y = __shfl_up_sync(0xffffffffu, x, o);
       if (lane >= o) x += y;
     }
-    if (lane == 31) s_warp[warp] = x;
+    if (lane == 31) s_warp[buf][warp] = x;
     __syncthreads();
-    if (warp == 0) {
-      int w = s_warp[lane];
+    // every warp scans the 32 warp totals itself (one barrier per tile; the two buffers alternate)
+    int w = s_warp[buf][lane];
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int y = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += y;
-      }
-      s_warp[lane] = w;   // inclusive over warps
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += y;
     }
-    __syncthreads();
-    const int warp_off = (warp == 0) ? 0 : s_warp[warp - 1];
-    const int carry = s_carry;
-    if (i < vocab) offsets[i] = carry + warp_off + x - c;
-    __syncthreads();
-    if (threadIdx.x == 1023) s_carry = carry + warp_off + x;
-    __syncthreads();
+    const int tile_total = __shfl_sync(0xffffffffu, w, 31);
+    const int warp_off = __shfl_sync(0xffffffffu, w, (warp + 31) & 31);
+    int run = carry + (warp == 0 ? 0 : warp_off) + x - total;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (base + e < vocab) {
+        offsets[base + e] = run;
+        if (cur[e] > kEmbSmallBucket) big[atomicAdd(n_big, 1)] = base + e;
+      }
+      run += cur[e];
+      cur[e] = nxt[e];
+    }
+    carry += tile_total;
   }
-  if (threadIdx.x == 0) offsets[vocab] = s_carry;
+  if (threadIdx.x == 0) offsets[vocab] = carry;
 }
 
 __global__ void emb_fill_kernel(const long long* __restrict__ ids, long long n_tok, int vocab,
@@ -284,12 +298,48 @@ __device__ __forceinline__ void emb_store_row(T* __restrict__ out, int k, int d,
   }
 }
 
-constexpr int kEmbSmallBucket = 32;      // buckets up to this size are sorted and summed by one warp
+// Eight consecutive features of a row as loaded (16 bytes of bf16, 32 bytes of float32)
+template <typename T> struct EmbRaw;
+template <> struct EmbRaw<__nv_bfloat16> {
+  using type = uint4;
+  static __device__ __forceinline__ uint4 load(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  static __device__ __forceinline__ uint4 zero() { return make_uint4(0u, 0u, 0u, 0u); }
+  static __device__ __forceinline__ void unpack(const uint4& w, float (&x)[8]) {
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      x[2 * e] = __uint_as_float(ww[e] << 16);
+      x[2 * e + 1] = __uint_as_float(ww[e] & 0xffff0000u);
+    }
+  }
+};
+struct EmbFloat8 { float4 a, b; };
+template <> struct EmbRaw<float> {
+  using type = EmbFloat8;
+  static __device__ __forceinline__ EmbFloat8 load(const float* p) {
+    EmbFloat8 r;
+    r.a = *reinterpret_cast<const float4*>(p);
+    r.b = *reinterpret_cast<const float4*>(p + 4);
+    return r;
+  }
+  static __device__ __forceinline__ EmbFloat8 zero() {
+    EmbFloat8 r;
+    r.a = make_float4(0.f, 0.f, 0.f, 0.f);
+    r.b = r.a;
+    return r;
+  }
+  static __device__ __forceinline__ void unpack(const EmbFloat8& w, float (&x)[8]) {
+    x[0] = w.a.x; x[1] = w.a.y; x[2] = w.a.z; x[3] = w.a.w; x[4] = w.b.x; x[5] = w.b.y; x[6] = w.b.z; x[7] = w.b.w;
+  }
+};
 
 // one warp per table row: ascending-order float32 segment sum, dtype rounding as the reference.
-// Rows with more than kEmbSmallBucket tokens are left to emb_big_bucket_kernel.
+// Rows with more than kEmbSmallBucket tokens are left to emb_big_bucket_kernel.  The work of a
+// row is the list of (256-feature step, token) units, step-major; the loads of eight units are
+// issued before their rows are added in order, so a row with one or two tokens has all its loads
+// in flight at once.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restrict__ offsets,
                   const int* __restrict__ perm, float pre_scale, float divisor, int accumulate,
                   T* __restrict__ out) {
@@ -299,9 +349,17 @@ emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restri
   const int off = offsets[k];
   const int cnt = offsets[k + 1] - off;
   if (cnt > kEmbSmallBucket) return;
+  const bool vec = (d % 8 == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
+  const int steps = (d + 255) / 256;
+  if (cnt == 0) {
+    const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int c = 0; c < steps; ++c) emb_store_row<T>(out, k, d, c * 256 + lane * 8, vec, zero, divisor, accumulate);
+    return;
+  }
   int mine = INT_MAX;
-  if (cnt > 0) {
-    if (lane < cnt) mine = perm[off + lane];
+  if (lane < cnt) mine = perm[off + lane];
+  if (cnt > 1) {
     // bitonic sort of 32 keys across the warp, ascending
 #pragma unroll
     for (int size = 2; size <= 32; size <<= 1) {
@@ -315,34 +373,63 @@ emb_segsum_kernel(const T* __restrict__ G, int d, int vocab, const int* __restri
       }
     }
   }
-  // each lane owns 8 consecutive features per step (16-byte loads and stores when d % 8 == 0)
-  const bool vec = (d % 8 == 0) && ((reinterpret_cast<uintptr_t>(G) & 15u) == 0) &&
-                   ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
-  for (int fbase = 0; fbase < d; fbase += 256) {      // warp-uniform trip count (shuffles inside)
-    const int f = fbase + lane * 8;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int i = 0; i < cnt; ++i) {
-      float x[8];
-      emb_load_row<T>(G, __shfl_sync(0xffffffffu, mine, i), d, f, vec, x);
-      emb_accumulate<T>(x, pre_scale, acc);
+  // each lane owns 8 consecutive features of a step (16-byte loads and stores when d % 8 == 0);
+  // loaded rows stay packed until they are added (32 registers per batch for either dtype)
+  constexpr int kBatch = sizeof(T) == 2 ? 8 : 4;
+  const int units = steps * cnt;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  int step = 0, i = 0;                     // unit -> (step, token index), advanced without divisions
+  auto finish_unit = [&]() {
+    if (++i == cnt) {                      // last token of this step: write the row's 256 features
+      emb_store_row<T>(out, k, d, step * 256 + lane * 8, vec, acc, divisor, accumulate);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      i = 0;
+      ++step;
     }
-    emb_store_row<T>(out, k, d, f, vec, acc, divisor, accumulate);
+  };
+  if (!vec) {                              // odd feature counts: one unit at a time
+    for (int u = 0; u < units; ++u) {
+      float x[8];
+      emb_load_row<T>(G, __shfl_sync(0xffffffffu, mine, i), d, step * 256 + lane * 8, false, x);
+      emb_accumulate<T>(x, pre_scale, acc);
+      finish_unit();
+    }
+    return;
+  }
+  using Raw = typename EmbRaw<T>::type;
+  for (int u0 = 0; u0 < units; u0 += kBatch) {
+    Raw x[kBatch];
+    {
+      int c = step, ii = i;
+#pragma unroll
+      for (int r = 0; r < kBatch; ++r) {
+        const int j = __shfl_sync(0xffffffffu, mine, ii & 31);
+        const int f = c * 256 + lane * 8;
+        if (u0 + r < units && f < d) x[r] = EmbRaw<T>::load(G + static_cast<long long>(j) * d + f);
+        else x[r] = EmbRaw<T>::zero();
+        if (++ii == cnt) { ii = 0; ++c; }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kBatch; ++r) {
+      if (u0 + r < units) {
+        float xf[8];
+        EmbRaw<T>::unpack(x[r], xf);
+        emb_accumulate<T>(xf, pre_scale, acc);
+        finish_unit();
+      }
+    }
   }
 }
 
 // Rows that many tokens share (padding, separators, position ids of a large batch).  The list of
-// such rows is compacted by emb_list_big_kernel; one CTA per listed row first sorts the row's token
+// such rows is made by emb_scan_kernel; one CTA per listed row first sorts the row's token
 // list into ascending order -- a bitonic network whose comparators all point the same way, so
 // entries past the end of the list act as +infinity without being stored; in shared memory up to
 // `smem_cap` entries, in place in global memory beyond -- and then sums the rows in that order.
 // The sum itself is sequential per feature (float addition in the CPU's order), so the loads of
 // the next eight rows are issued before the current eight are added.
-__global__ void emb_list_big_kernel(const int* __restrict__ offsets, int vocab, int* __restrict__ big,
-                                    int* __restrict__ n_big) {
-  for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < vocab; k += gridDim.x * blockDim.x)
-    if (offsets[k + 1] - offsets[k] > kEmbSmallBucket) big[atomicAdd(n_big, 1)] = k;
-}
-
 __device__ __forceinline__ void emb_bitonic_ascending(int* keys, int cnt, int n2, int tid, int nthreads) {
   for (int k = 2; k <= n2; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
@@ -511,24 +598,20 @@ extern "C" int ghost_embedding_wgrad(const long long* ids, const void* G, int is
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* w = static_cast<uint8_t*>(ws);
   const long long seg = up256(4ll * (vocab + 1));
-  int* counts = reinterpret_cast<int*>(w);
-  int* offsets = reinterpret_cast<int*>(w + seg);
-  int* cursor = reinterpret_cast<int*>(w + 2 * seg);
-  int* perm = reinterpret_cast<int*>(w + 3 * seg);
   const long long n_tok = static_cast<long long>(n_train) * T;
-  int* n_big = reinterpret_cast<int*>(w + 3 * seg + up256(4ll * n_tok));
+  // counts, cursor and the big-row counter sit next to each other: one memset clears them
+  int* counts = reinterpret_cast<int*>(w);
+  int* cursor = reinterpret_cast<int*>(w + seg);
+  int* n_big = reinterpret_cast<int*>(w + 2 * seg);
   int* big = n_big + 1;
-  GB_CUDA_OK(cudaMemsetAsync(counts, 0, seg, st));
-  GB_CUDA_OK(cudaMemsetAsync(cursor, 0, seg, st));
-  GB_CUDA_OK(cudaMemsetAsync(n_big, 0, 4, st));
+  int* offsets = reinterpret_cast<int*>(w + 2 * seg + emb_big_list_bytes(n_tok));
+  int* perm = reinterpret_cast<int*>(w + 3 * seg + emb_big_list_bytes(n_tok));
+  GB_CUDA_OK(cudaMemsetAsync(counts, 0, 2 * seg + 4, st));
   int blocks = static_cast<int>((n_tok + 255) / 256);
   if (blocks > ds->sm_count * 8) blocks = ds->sm_count * 8;
   emb_count_kernel<<<blocks, 256, 0, st>>>(ids, n_tok, vocab, counts, ds->err_word);
-  emb_scan_kernel<<<1, 1024, 0, st>>>(counts, vocab, offsets);
+  emb_scan_kernel<<<1, 1024, 0, st>>>(counts, vocab, offsets, big, n_big);
   emb_fill_kernel<<<blocks, 256, 0, st>>>(ids, n_tok, vocab, offsets, cursor, perm);
-  int vblocks = ceil_div(vocab, 256);
-  if (vblocks > ds->sm_count * 4) vblocks = ds->sm_count * 4;
-  emb_list_big_kernel<<<vblocks, 256, 0, st>>>(offsets, vocab, big, n_big);
   // rows shared by many tokens: sorted in up to 128 KB of shared memory (32768 tokens), else in place
   constexpr int kSmemCap = 32768;
   static bool attr_set[64] = {};
@@ -546,7 +629,7 @@ extern "C" int ghost_embedding_wgrad(const long long* ids, const void* G, int is
     emb_segsum_kernel<__nv_bfloat16><<<ceil_div(vocab, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(G), d, vocab, offsets, perm, pre_scale, divisor, accumulate, static_cast<__nv_bfloat16*>(out));
     emb_big_bucket_kernel<__nv_bfloat16><<<big_blocks, 256, kSmemCap * 4, st>>>(static_cast<const __nv_bfloat16*>(G), d, offsets, perm, big, n_big, kSmemCap, pre_scale, divisor, accumulate, static_cast<__nv_bfloat16*>(out));
   }
-  count_launch(6);
+  count_launch(5);
   return post_launch("ghost_embedding_wgrad");
 }
 
