@@ -293,12 +293,19 @@ def test_layernorm_golden(golden):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("case", [(5, 3, 6, 8, 11), (4, 2, 64, 40, 50), (3, 2, 100, 768, 7), (6, 1, 33, 16, 1000)])
+@pytest.mark.parametrize("case", [(5, 3, 6, 8, 11), (4, 2, 64, 40, 50), (3, 2, 100, 768, 7), (6, 1, 33, 16, 1000),
+                                  # tables that span several 4096-id tiles of the bucket scan, feature counts
+                                  # off the 16-byte path, a crowded row in the last, partial tile
+                                  (6, 2, 700, 20, 9001), (40, 2, 64, 72, 4099), (12, 3, 50, 264, 12289)])
 def test_embedding(case, dtype):
     n_t, n_v, T, d, vocab = case
     N = n_t + n_v
     g = torch.Generator().manual_seed(8)
     ids = torch.randint(0, vocab, (N, T), generator=g)
+    if vocab > 4096:
+        ids[:, :3] = vocab - 1
+        ids[:, 3] = 4095
+        ids[:, 4] = 4096
     G = (torch.randn(N, T, d, generator=g) / d ** 0.5).to(dtype)
     o = ops()
     M = o.embedding_dot(ids.cuda(), G.cuda(), n_v, vocab)
