@@ -187,6 +187,9 @@ def _check_dotprod_model(model, run, ids, n_t, n_v, dtype, path_rule, n_hooked):
                 rw, rb = O.layernorm_dot_exact(A, B, n_v, m.eps)
                 assert O.rel_fro(results[(name, "weight")], rw) < tol, name
                 assert O.rel_fro(results[(name, "bias")], rb) < tol, name
+            elif type(m).__name__.endswith("RMSNorm"):
+                eps = getattr(m, "variance_epsilon", None) or m.eps
+                assert O.rel_fro(results[(name, "weight")], O.rmsnorm_dot_exact(A, B, n_v, eps)) < tol, name
             else:
                 ref = O.linear_dot_exact(A, B, n_v)
                 assert O.rel_fro(results[(name, "weight")], ref) < tol, name
@@ -244,6 +247,31 @@ def test_hf_gpt2_lm_head_model_per_module_parity(dtype, path_rule):
     ids = torch.randint(0, cfg.vocab_size, (n_t + n_v, T)).cuda()
     _check_dotprod_model(model, lambda m, x: m(input_ids=x, labels=x).loss, ids, n_t, n_v, dtype, path_rule,
                          2 + 2 * 6 + 1 + 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("path_rule", ["cost", "persample"])
+def test_hf_llama_model_per_module_parity(dtype, path_rule):
+    """``transformers.LlamaForCausalLM`` (small configuration: grouped-query attention, gated MLP, RMS
+    norms, untied head, no biases) through ``GradDotProdEngine`` in dummy-bias mode -- a family the
+    reference leaves partly unhooked (it skips RMS-norm layers): the embedding gets the dummy bias
+    that keeps the graph alive, every Linear / RMSNorm / Embedding is hooked, and the recovered train
+    gradients equal autograd's on the train-only batch."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    torch.manual_seed(4)
+    cfg = LlamaConfig(vocab_size=251, hidden_size=64, intermediate_size=192, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                      tie_word_embeddings=False, attention_dropout=0.0, use_cache=False)
+    model = LlamaForCausalLM(cfg).to(dtype).cuda()
+    with torch.no_grad():
+        for m in model.modules():
+            if type(m).__name__.endswith("RMSNorm"):
+                m.weight.uniform_(0.5, 1.5)
+    n_t, n_v, T = 3, 2, 40
+    ids = torch.randint(0, cfg.vocab_size, (n_t + n_v, T)).cuda()
+    # embedding, 2 blocks x (4 attention + 3 MLP Linear + 2 RMSNorm), final norm, head
+    _check_dotprod_model(model, lambda m, x: m(input_ids=x, labels=x).loss, ids, n_t, n_v, dtype, path_rule,
+                         1 + 2 * 9 + 1 + 1)
 
 
 @pytest.mark.parametrize("path_rule", ["gram", "persample"])
