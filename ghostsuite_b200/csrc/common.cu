@@ -137,6 +137,26 @@ int make_tmap_plain_2d(CUtensorMap* out, const void* base, int elem_bytes, uint6
   return GHOST_OK;
 }
 
+int make_tmap_bf16_store_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || cols % 32 != 0)
+    return fail(GHOST_ERR_INVALID, "TMA store target %p / %llu columns: needs 16-byte alignment and a multiple of 32 columns",
+                base, (unsigned long long)cols);
+  if (rows == 0 || rows >= (1ull << 32) || box_rows == 0 || box_rows > 256)
+    return fail(GHOST_ERR_INVALID, "bad TMA store map (rows=%llu box_rows=%u)", (unsigned long long)rows, box_rows);
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {32, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled(store) failed with CUresult %d", (int)r);
+  return GHOST_OK;
+}
+
 int make_tmap_plain_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t planes, uint64_t rows,
                        uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn fn = encode_fn();

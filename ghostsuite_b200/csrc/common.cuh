@@ -68,6 +68,10 @@ int make_tmap_bf16_blocks(CUtensorMap* out, const void* base, uint64_t samples, 
 // Plain (unswizzled) 2-D map of a row-major matrix of 2- or 4-byte elements; box = [box_rows, box_cols].
 int make_tmap_plain_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
                        uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+// 2-D map of a dense row-major bf16 matrix for tiled STORES of [box_rows, 32 columns] boxes (64-byte
+// rows) from shared memory written with the 64-byte swizzle: 16-byte chunk c of row r sits at
+// r * 64 + ((c ^ ((r >> 1) & 3)) * 16).
+int make_tmap_bf16_store_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 // Plain 3-D map of a dense [planes, rows, cols] array; box = [1, box_rows, box_cols].
 int make_tmap_plain_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t planes, uint64_t rows,
                        uint64_t cols, uint32_t box_rows, uint32_t box_cols);

@@ -8,7 +8,9 @@
 // columns (64 KB per stage of 128 tokens, three stages), the leader issues 256 x 256 x 16 MMAs that
 // read both CTAs' shared memory (eight per stage: with 64-token stages the issuing thread spent as
 // long on the two barrier operations of a stage as the tensor core on its four MMAs), and each CTA writes the 128 x 256 tile that
-// sits in its own tensor memory.  Per output element the Y operand crosses L2 -> shared memory and
+// sits in its own tensor memory: bf16 tiles through two swizzled [128][32] staging boxes in shared
+// memory that the copy engine stores (cp.async.bulk.tensor, shared -> global), fp32 tiles with
+// 256-bit stores.  Per output element the Y operand crosses L2 -> shared memory and
 // shared memory -> tensor core half as often as in the single-CTA kernel.
 //
 // Train-gradient pass (one "sample" holding all token rows): a unit is a 256 x 256 block and one of
@@ -35,6 +37,7 @@ struct XtyPairParams {
   long long T;
   void* vgrad;
   int v_is_f32;
+  int tma_store;             // bf16 tiles: staged in shared memory and stored by the copy engine
   int accumulate;            // 0: store tiles; 1: add into acc_ws ("samples" = k_splits, one real sample)
   int kb_per_split;          // row blocks (BK tokens) per split (accumulate)
   float* acc_ws;             // [m_cols, ld_acc] fp32, zeroed by the host
@@ -57,7 +60,11 @@ struct XtyPairCfg {
   static constexpr int kStageBytes = (BM + BNH) * BK * 2;   // 64 KB
   static constexpr int kStages = 3;
   static constexpr int kColsumBytes = 8 * 128 * 4;          // cross-row-lane reduction of the column-sum warps
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kColsumBytes;
+  // bf16 tiles leave through shared memory: two [128 rows][32 columns] boxes (64-byte rows, 64-byte
+  // swizzle) that the epilogue warps fill alternately and one thread hands to the copy engine
+  static constexpr int kStoreBoxBytes = 128 * 32 * 2;
+  static constexpr int kStoreBytes = 2 * kStoreBoxBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256 + kColsumBytes;
 };
 
 __device__ __forceinline__ void st_global_v8_pair(void* addr, const uint32_t* v) {
@@ -82,13 +89,14 @@ __device__ __forceinline__ void red_add_row32_pair(float* dst, const uint32_t (&
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
-                     const XtyPairParams p) {
+                     const __grid_constant__ CUtensorMap tm_out, const XtyPairParams p) {
   using Cfg = XtyPairCfg;
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, kStages = Cfg::kStages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  uint8_t* store_box = smem + kStages * Cfg::kStageBytes;      // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_box + Cfg::kStoreBytes);
   uint64_t* full_bar = bars;                 // used in the leader only
   uint64_t* empty_bar = bars + kStages;      // both CTAs
   uint64_t* acc_full = bars + 2 * kStages;   // [2], both CTAs
@@ -143,6 +151,7 @@ xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_y);
+    if (p.tma_store) tma_prefetch_desc(&tm_out);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -213,7 +222,7 @@ xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     // Present only in launches that ask for them (320 threads).  Every unit adds its share of the
     // sample's token rows of the chosen operand's 256-column block to the sums: CTA r the 128
     // columns it also loads for the tensor core.
-    float* red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + 1024 + 256);
+    float* red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes + Cfg::kStoreBytes + 1024 + 256);
     const int ct = static_cast<int>(threadIdx.x) - 192;
     for (long long u = pair; u < units; u += num_pairs) {
       int sample, tm, tn;
@@ -233,11 +242,15 @@ xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     // ------------------------------------------------------------------ epilogue (warps 0-3, both CTAs)
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t boxes = 0;          // boxes handed to the copy engine so far (selects the staging buffer)
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     for (long long u = pair; u < units; u += num_pairs) {
       int sample, tm, tn;
       decode(u, sample, tm, tn);
-      if (!mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag, p.err, 154)) break;
+      bool ok = mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag, p.err, 154);
+      // the staged store synchronises the four warps on a named barrier: they leave together
+      if (p.tma_store) ok = named_bar_and(2, 128, ok);
+      if (!ok) break;
       tc_fence_after_sync();
       const int tile128 = tm * 2 + static_cast<int>(rank);      // this CTA's 128-row tile
       if (p.accumulate) {
@@ -255,6 +268,43 @@ xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
           tmem_ld_wait();
           if (live)
             red_add_row32_pair(p.acc_ws + static_cast<long long>(m) * p.ld_acc + n0 + c0, r, p.n_cols - (n0 + c0));
+        }
+      } else if (tile128 < p.m_tiles128 && p.tma_store) {
+        // Tile rows of 512 bytes lie 512 bytes apart: a warp-wide st.global touches 32 lines, and
+        // its passes through the L1 data path compete with the column-sum warps' loads and the
+        // operand traffic of the tensor core.  Instead every thread writes its row's 64 bytes into
+        // a swizzled [128][32] box (conflict-free 16-byte stores) and the copy engine writes the
+        // box out: 2.5 % off the call inside the GPT-2 step.  (Leaving the stores out altogether
+        // makes the kernel 13 % faster: the 189 MB of tile writes themselves are what costs.)
+        const uint32_t t_acc = tmem_base + lane_base + acc * BN;
+        const int row = static_cast<int>(threadIdx.x);
+        const int y0 = ((tile128 * p.n_tiles + tn) * p.samples + sample) * BM;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32, ++boxes) {
+          uint32_t r[32];
+          tmem_ld32(t_acc + c0, r);
+          tmem_ld_wait();
+          uint8_t* box = store_box + (boxes & 1) * Cfg::kStoreBoxBytes;
+          // the store that read this buffer two boxes ago has finished reading it
+          if (threadIdx.x == 0) bulk_wait_group_read<1>();
+          named_bar_sync(2, 128);
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __nv_bfloat162 hv =
+                  __floats2bfloat162_rn(__uint_as_float(r[8 * ch + 2 * e]), __uint_as_float(r[8 * ch + 2 * e + 1]));
+              w[e] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            st_shared_v4(box + row * 64 + ((ch ^ ((row >> 1) & 3)) << 4), w[0], w[1], w[2], w[3]);
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(2, 128);
+          if (threadIdx.x == 0) {
+            tma_store_2d(&tm_out, box, c0, y0);
+            bulk_commit_group();
+          }
         }
       } else if (tile128 < p.m_tiles128) {
         const uint32_t t_acc = tmem_base + lane_base + acc * BN;
@@ -293,6 +343,8 @@ xty_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    // the boxes still in flight are written out before the CTA gives up its shared memory
+    if (threadIdx.x == 0) bulk_wait_group<0>();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -362,6 +414,9 @@ int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_tota
   p.T = T;
   p.vgrad = vgrad;
   p.v_is_f32 = v_is_f32;
+  // bf16 tiles go out through the copy engine (row counts up to 2^31 keep the box coordinate an int)
+  const unsigned long long out_rows = static_cast<unsigned long long>(p.m_tiles128) * p.n_tiles * samples * Cfg::BM;
+  p.tma_store = (!v_is_f32 && out_rows < (1ull << 31)) ? 1 : 0;
   p.accumulate = 0;
   p.kb_per_split = 0;
   p.acc_ws = nullptr;
@@ -379,11 +434,13 @@ int launch_xty_pair_tiles(const void* X, const void* Y, long long n_samples_tota
   int rc;
   if ((rc = make_tmap_bf16_blocks(&tx, X, n_samples_total, T, m_cols, ldx, Cfg::BK, Cfg::BM / 64)) != GHOST_OK) return rc;
   if ((rc = make_tmap_bf16_blocks(&ty, Y, n_samples_total, T, n_cols, ldy, Cfg::BK, Cfg::BNH / 64)) != GHOST_OK) return rc;
+  CUtensorMap tout = tx;
+  if (p.tma_store && (rc = make_tmap_bf16_store_2d(&tout, vgrad, out_rows, Cfg::BN, Cfg::BM)) != GHOST_OK) return rc;
   if ((rc = pair_kernel_smem_attr(ds)) != GHOST_OK) return rc;
   const long long units = static_cast<long long>(p.m_tiles) * p.n_tiles * samples;
   long long pairs = ds->sm_count / 2;
   if (pairs > units) pairs = units;
-  xty_gemm_pair_kernel<<<static_cast<int>(2 * pairs), p.cs_of ? 320 : 192, Cfg::kSmemBytes, st>>>(tx, ty, p);
+  xty_gemm_pair_kernel<<<static_cast<int>(2 * pairs), p.cs_of ? 320 : 192, Cfg::kSmemBytes, st>>>(tx, ty, tout, p);
   count_launch();
   return post_launch("xty_gemm_pair_kernel");
 }
@@ -404,6 +461,7 @@ int launch_xty_pair_wgrad(const void* X, const void* Y, long long n_rows, int m_
   p.T = n_rows;
   p.vgrad = nullptr;
   p.v_is_f32 = 0;
+  p.tma_store = 0;
   p.accumulate = 1;
   p.acc_ws = acc_ws;
   p.ld_acc = ld_acc;
@@ -434,7 +492,7 @@ int launch_xty_pair_wgrad(const void* X, const void* Y, long long n_rows, int m_
   if ((rc = pair_kernel_smem_attr(ds)) != GHOST_OK) return rc;
   const long long units = blocks * p.samples;
   const long long pairs = pairs_max < units ? pairs_max : units;
-  xty_gemm_pair_kernel<<<static_cast<int>(2 * pairs), 192, Cfg::kSmemBytes, st>>>(tx, ty, p);
+  xty_gemm_pair_kernel<<<static_cast<int>(2 * pairs), 192, Cfg::kSmemBytes, st>>>(tx, ty, tx, p);
   count_launch();
   return post_launch("xty_gemm_pair_kernel");
 }
