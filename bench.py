@@ -12,9 +12,10 @@ prepare_gradients, the optimizer step, and aggregate_and_log.  Metric: train tok
 
 The batch is the configuration's: 32 train + 8 validation sequences in total (strong scaling).  With
 N > 1 (launched by torch.distributed.run, one rank per GPU) every rank takes 32 / N train sequences
-and either the whole validation batch (`val_replicated`) or 8 / N of it with a per-layer all-gather
-of the validation operands (`val_sharded`); both variants are timed and the faster one is the
-line's `value`.  After backward the per-parameter dot-product blocks are all-gathered and the train
+and either the whole validation batch (`val_replicated`) or 8 / N of it, with a per-layer all-gather
+of the validation operands (`val_sharded`) or of the validation samples' per-sample gradients
+(`val_exchanged`: tiles on the per-sample path, vectors of bias and norm layers); all variants are
+timed and the fastest one is the line's `value`.  After backward the per-parameter dot-product blocks are all-gathered and the train
 gradients all-reduced over NCCL.  `weak_scaling` is the same step with 32 train sequences on every
 GPU.  On the first, untimed step of each variant the gathered results are checked (`dist_check`).
 
@@ -327,7 +328,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         state["engine"] = eng
         state["sync"] = gdist.overlap_train_grad_sync(eng, group) if world > 1 else None
         if shard_val and world > 1:
-            gdist.shard_validation(eng, group)
+            if shard_val == "gradients":
+                gdist.exchange_validation(eng, group)
+            else:
+                gdist.shard_validation(eng, group)
         return eng
 
     def variant(name):
@@ -335,9 +339,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         if name == "weak":
             return None, dev_val, N_VAL, False
         lo, hi = gdist.shard_bounds(N_TRAIN, rank, world)
-        if name == "val_sharded":
+        if name in ("val_sharded", "val_exchanged"):
             vlo, vhi = gdist.shard_bounds(N_VAL, rank, world)
-            return (lo, hi), dev_val[vlo:vhi], vhi - vlo, True
+            return (lo, hi), dev_val[vlo:vhi], vhi - vlo, ("gradients" if name == "val_exchanged" else "operands")
         return (lo, hi), dev_val, N_VAL, False
 
     def make_step(name, optimise=True):
@@ -529,6 +533,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         state["deterministic"] = True
         dist_check["val_replicated"], ref_res = check_variant("val_replicated")
         dist_check["val_sharded"], _ = check_variant("val_sharded", reference=ref_res)
+        dist_check["val_exchanged"], _ = check_variant("val_exchanged", reference=ref_res)
         dist_check["weak"], _ = check_variant("weak")
         del ref_res
         state["deterministic"] = False
@@ -537,7 +542,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     sampler = ClockSampler(local_rank)
     results = {}
     prof = None
-    names = ["val_replicated"] if world == 1 else ["val_replicated", "val_sharded", "weak"]
+    names = ["val_replicated"] if world == 1 else ["val_replicated", "val_sharded", "val_exchanged", "weak"]
+    keep = [v for v in args.only_variants.split(",") if v]
+    if keep:
+        names = [n for n in names if n == "val_replicated" or n == "weak" or n in keep]
     for name in names:
         step, engine, h2d = make_step(name)
         for i in range(args.warmup):
@@ -554,10 +562,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         rec["ms_e2e"], _, _ = timed(step, True, False)
         if rank == 0 and name == "val_replicated":
             rec["clocks"] = sampler.stop()
+        n_steps_run = max(1, (args.warmup + 2 * args.steps))
         sv = getattr(engine, "_ghost_val_shard", None)
+        ex = getattr(engine, "_ghost_val_exchange", None)
         if sv is not None:
-            rec["val_gather_calls_per_step"] = sv.calls / max(1, (args.warmup + 2 * args.steps))
-            rec["val_gather_bytes_per_step"] = sv.bytes / max(1, (args.warmup + 2 * args.steps))
+            rec["val_gather_calls_per_step"] = (sv.calls + (ex.calls if ex else 0)) / n_steps_run
+            rec["val_gather_bytes_per_step"] = (sv.bytes + (ex.bytes if ex else 0)) / n_steps_run
         results[name] = rec
     _lib.poll_kernel_error()
 
@@ -572,7 +582,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # the fixed-batch step replayed from a CUDA graph (validation replicated; with more than one GPU
     # also with the validation batch sharded)
     graph_note = None
-    for base in (["val_replicated"] if world == 1 else ["val_replicated", "val_sharded"]):
+    for base in (["val_replicated"] if world == 1 else
+                 [n for n in ("val_replicated", "val_sharded", "val_exchanged") if n in names]):
         try:
             step, graph_launches, h2d = make_graph_step(base)
             for i in range(args.warmup):
@@ -582,9 +593,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             ms_e2e, _, _ = timed(step, True, False)
             rec = {"ms_dev": ms_dev, "ms_e2e": ms_e2e, "launches": graph_launches * args.steps, "h2d": h2d}
             sv = getattr(state["engine"], "_ghost_val_shard", None)
+            ex = getattr(state["engine"], "_ghost_val_exchange", None)
             if sv is not None:              # counted once, at capture (plus the two eager warm-up steps)
-                rec["val_gather_calls_per_step"] = sv.calls / 3
-                rec["val_gather_bytes_per_step"] = sv.bytes / 3
+                rec["val_gather_calls_per_step"] = (sv.calls + (ex.calls if ex else 0)) / 3
+                rec["val_gather_bytes_per_step"] = (sv.bytes + (ex.bytes if ex else 0)) / 3
             results[base + "_cuda_graph"] = rec
             names.insert(1, base + "_cuda_graph")
             _lib.poll_kernel_error()
@@ -615,7 +627,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
            "val_replicated_cuda_graph": "validation batch replicated, step replayed from a CUDA graph",
            "val_sharded": "validation batch sharded, per-layer all-gather of its operands",
            "val_sharded_cuda_graph": "validation batch sharded (per-layer all-gather of its operands), step replayed "
-                                     "from a CUDA graph"}[best]
+                                     "from a CUDA graph",
+           "val_exchanged": "validation batch sharded, per-layer all-gather of its per-sample gradients (tiles / "
+                            "vectors; operands for the embeddings)",
+           "val_exchanged_cuda_graph": "validation batch sharded (per-layer all-gather of its per-sample gradients), "
+                                       "step replayed from a CUDA graph"}[best]
     if world == 1:
         parallelism = f"1 GPU; {how} (the fastest of the variants measured in this run)"
     else:
@@ -1459,6 +1475,10 @@ def main():
                          "Gram vs per-sample path over T on one Linear layer; gradproj_model: GradProj on a "
                          "Pythia-410M-shaped model")
     ap.add_argument("--only", default="", help="kernels mode: comma-separated case names")
+    ap.add_argument("--only-variants", default="",
+                    help="multi-GPU step: comma-separated variants to time (val_replicated is always timed)")
+    ap.add_argument("--exchange-overlap", type=int, default=-1,
+                    help="override the engines' EXCHANGE_OVERLAP switch (0 / 1) for an A/B run")
     ap.add_argument("--fuse-bias-colsums", type=int, default=-1,
                     help="override the engines' FUSE_BIAS_COLSUMS switch (0 / 1) for an A/B run")
     args = ap.parse_args()
@@ -1467,6 +1487,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     guard_stdout()
+    if args.exchange_overlap >= 0:
+        from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as _L3
+        _L3.EXCHANGE_OVERLAP = bool(args.exchange_overlap)
     if args.fuse_bias_colsums >= 0:
         from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as _L
         _L.FUSE_BIAS_COLSUMS = bool(args.fuse_bias_colsums)

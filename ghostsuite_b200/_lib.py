@@ -46,6 +46,9 @@ PROTOTYPES = {
     "ghost_persample_workspace_bytes": (_ll, [_i, _i, _i, _i, _i]),
     "ghost_set_persample_budget_bytes": (_i, [_ll]),
     "ghost_persample_dot_bf16": (_i, [_vp, _vp, _i, _i, _ll, _i, _i, _ll, _ll, _f, _vp, _i, _vp, _i, _f, _i, _i, _vp, _vp, _ll, _vp]),
+    "ghost_persample_tiles_bytes": (_ll, [_i, _i, _i]),
+    "ghost_persample_tiles_bf16": (_i, [_vp, _vp, _i, _ll, _i, _i, _ll, _ll, _i, _i, _i, _vp, _vp, _ll, _vp]),
+    "ghost_tile_dot_bf16": (_i, [_vp, _i, _i, _vp, _i, _i, _i, _f, _vp, _vp, _i, _f, _i, _vp]),
     "ghost_colsum": (_i, [_vp, _i, _i, _ll, _i, _ll, _vp, _vp]),
     "ghost_layernorm_workspace_bytes": (_ll, [_i, _ll, _i]),
     "ghost_layernorm_persample": (_i, [_vp, _vp, _i, _i, _ll, _i, _f, _vp, _vp, _vp, _ll, _vp]),

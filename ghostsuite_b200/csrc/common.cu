@@ -228,6 +228,30 @@ int make_tmap_bf16_blocks(CUtensorMap* out, const void* base, uint64_t samples, 
   return GHOST_OK;
 }
 
+int make_tmap_bf16_gathered_tiles(CUtensorMap* out, const void* base, uint64_t ranks, uint64_t tiles,
+                                  uint64_t per_rank, uint32_t box_rows, uint32_t box_blocks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+    return fail(GHOST_ERR_INVALID, "TMA operand base %p is not 16-byte aligned", base);
+  if (ranks == 0 || tiles == 0 || per_rank == 0 || box_rows == 0 ||
+      !(box_rows % per_rank == 0 || per_rank % box_rows == 0))
+    return fail(GHOST_ERR_INVALID, "gathered tiles: %llu samples per rank do not fit boxes of %u rows",
+                (unsigned long long)per_rank, box_rows);
+  const uint64_t tile_bytes = 32768ull * 2;
+  const uint32_t bs = box_rows < per_rank ? box_rows : static_cast<uint32_t>(per_rank);
+  cuuint64_t dims[5] = {64, per_rank, ranks, 512, tiles};
+  cuuint64_t strides[4] = {tile_bytes, tiles * per_rank * tile_bytes, 128, per_rank * tile_bytes};
+  cuuint32_t box[5] = {64, bs, box_rows / bs, box_blocks, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(GHOST_ERR_CUDA, "cuTensorMapEncodeTiled(gathered tiles) failed with CUresult %d", (int)r);
+  return GHOST_OK;
+}
+
 }  // namespace gb
 
 extern "C" {

@@ -65,6 +65,14 @@ int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t samples, uint
 int make_tmap_bf16_blocks(CUtensorMap* out, const void* base, uint64_t samples, uint64_t rows,
                           uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_blocks);
 
+// Validation tiles as an all-gather leaves them: [ranks][tiles][per_rank samples][32768] bf16, seen as
+// [64, per_rank, ranks, 512 panels, tiles]; a box holds `box_rows` consecutive validation samples
+// (global index = rank * per_rank + sample) of `box_blocks` panels, each panel a swizzled
+// [box_rows][64] block -- the layout make_tmap_bf16_blocks gives for a tile-major buffer.  box_rows
+// must divide per_rank or be a multiple of it.  Coordinates: (0, sample, rank, panel, tile).
+int make_tmap_bf16_gathered_tiles(CUtensorMap* out, const void* base, uint64_t ranks, uint64_t tiles,
+                                  uint64_t per_rank, uint32_t box_rows, uint32_t box_blocks);
+
 // Plain (unswizzled) 2-D map of a row-major matrix of 2- or 4-byte elements; box = [box_rows, box_cols].
 int make_tmap_plain_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
                        uint64_t ld, uint32_t box_rows, uint32_t box_cols);

@@ -163,6 +163,15 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* m, uint64_t* bar,
+                                            int x, int y, int z, int w, int v) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(v)
+      : "memory");
+}
+
 // Tiled store shared -> global (x * elemsize a multiple of 16 bytes, never a negative coordinate).
 // The store belongs to the issuing thread's bulk group: that thread commits the group, waits for
 // the group's reads of shared memory before the buffer is rewritten, and for its completion before

@@ -39,6 +39,7 @@ struct TileDotParams {
   long long stages_per_cta;
   int n_val, n_grp;           // validation samples, train samples in this group
   int v_off;                  // index of the first validation sample inside V's sample dimension
+  int v_per_rank;             // > 0: V is [ranks][tiles][v_per_rank][32768] (bf16 kernel only), v_off = 0
   int b0, n_train;            // first train sample of the group, total train samples (M row pitch)
   float scale;
   float* M;                   // [n_val, n_train]
@@ -291,7 +292,10 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
             const int tile = static_cast<int>(s / kStagesPerTile);
             const int panel = static_cast<int>(s % kStagesPerTile) * Cfg::kPanels;   // 64-element panels
             mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-            tma_load_4d(st, &tm_v, &full_bar[stage], 0, p.v_off + v0, panel, tile);
+            if (p.v_per_rank > 0)
+              tma_load_5d(st, &tm_v, &full_bar[stage], 0, v0 % p.v_per_rank, v0 / p.v_per_rank, panel, tile);
+            else
+              tma_load_4d(st, &tm_v, &full_bar[stage], 0, p.v_off + v0, panel, tile);
             tma_load_4d(st + Cfg::kValBytes, &tm_w, &full_bar[stage], 0, j0, panel, tile);
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
@@ -507,8 +511,11 @@ static int launch_tile_dot_mma(const void* V, int v_samples, const void* W, int 
   CUtensorMap tv, tw;
   int rc;
   // [tiles][samples][32768] seen as [tiles][512 panels][samples][64]: one box = 4 panels of the stage
-  if ((rc = make_tmap_bf16_blocks(&tv, V, tiles, v_samples, kTileElems, kTileElems, Cfg::kValRows, Cfg::kPanels)) != GHOST_OK)
-    return rc;
+  if (p.v_per_rank > 0)
+    rc = make_tmap_bf16_gathered_tiles(&tv, V, v_samples / p.v_per_rank, tiles, p.v_per_rank, Cfg::kValRows, Cfg::kPanels);
+  else
+    rc = make_tmap_bf16_blocks(&tv, V, tiles, v_samples, kTileElems, kTileElems, Cfg::kValRows, Cfg::kPanels);
+  if (rc != GHOST_OK) return rc;
   if ((rc = make_tmap_bf16_blocks(&tw, W, tiles, w_samples, kTileElems, kTileElems, kTdTrainRows, Cfg::kPanels)) != GHOST_OK)
     return rc;
   static bool attr_set[64] = {};
@@ -527,12 +534,16 @@ static int launch_tile_dot_mma(const void* V, int v_samples, const void* W, int 
 
 // V: [tiles][v_samples][32768] with the validation samples at index v_off..v_off+n_val-1;
 // W: [tiles][w_samples][32768] with the group's train samples at index 0..n_grp-1.
+// v_per_rank > 0: V holds validation samples only, as an all-gather over ranks leaves them,
+// [v_samples / v_per_rank ranks][tiles][v_per_rank][32768] (bf16).
 int launch_tile_dot(const void* V, int v_samples, int v_off, const void* W, int w_samples, int is_f32,
                     long long tiles, int n_val, int n_grp, int b0, int n_train, float scale, float* M,
                     float* sum, int sum_init, void* out, int out_is_f32, int out_accumulate, int m_cols,
-                    int n_cols, int n_tiles_n, float out_scale, const DeviceState* ds, cudaStream_t st) {
+                    int n_cols, int n_tiles_n, float out_scale, const DeviceState* ds, cudaStream_t st,
+                    int v_per_rank) {
   TileDotParams p;
   p.v_off = v_off;
+  p.v_per_rank = v_per_rank;
   p.out = out; p.out_is_f32 = out_is_f32; p.out_accumulate = out_accumulate;
   p.m_cols = m_cols; p.n_cols = n_cols; p.n_tiles_n = n_tiles_n; p.out_scale = out_scale;
   p.stages = tiles * (kTileElems / (is_f32 ? kTdCols : kMmaCols));

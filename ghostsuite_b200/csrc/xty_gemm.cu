@@ -522,7 +522,8 @@ namespace gb {
 int launch_tile_dot(const void* V, int v_samples, int v_off, const void* W, int w_samples, int is_f32,
                     long long tiles, int n_val, int n_grp, int b0, int n_train, float scale, float* M,
                     float* sum, int sum_init, void* out, int out_is_f32, int out_accumulate, int m_cols,
-                    int n_cols, int n_tiles_n, float out_scale, const DeviceState* ds, cudaStream_t st);
+                    int n_cols, int n_tiles_n, float out_scale, const DeviceState* ds, cudaStream_t st,
+                    int v_per_rank = 0);
 int launch_tile_sum_finalize(const float* sum, int n_tiles_n, void* out, int out_is_f32, int rows, int cols,
                              float scale, int accumulate, const DeviceState* ds, cudaStream_t st);
 }
@@ -656,4 +657,84 @@ extern "C" int ghost_persample_dot_bf16(const void* X, const void* Y, int n_trai
     return launch_tile_sum_finalize(sum, p.n_tiles, grad_out, grad_is_f32, m_cols, n_cols, grad_scale,
                                     grad_accumulate, ds, st);
   return GHOST_OK;
+}
+
+// ---- the two passes as separate calls ---------------------------------------------------------------
+// For callers that put something between the passes: a data-parallel run whose ranks each hold a
+// part of the validation batch computes its own validation tiles, all-gathers them, and only then
+// contracts them with its train tiles.
+
+extern "C" long long ghost_persample_tiles_bytes(int samples, int m_cols, int n_cols) {
+  if (samples <= 0 || m_cols <= 0 || n_cols <= 0) return 0;
+  const long long tiles = static_cast<long long>(ceil_div(m_cols, XtyCfg::BM)) * ceil_div(n_cols, XtyCfg::BN);
+  return tiles * samples * kTileElems * 2;
+}
+
+extern "C" int ghost_persample_tiles_bf16(const void* X, const void* Y, int n_samples_total, long long T, int m_cols,
+                                          int n_cols, long long ldx, long long ldy, int sample0, int samples,
+                                          int colsum_of, float* colsum_out, void* tiles_out, long long tiles_bytes,
+                                          void* stream) {
+  const DeviceState* ds = device_state();
+  if (!ds) return GHOST_ERR_DEVICE;
+  GB_REQUIRE(X && Y && tiles_out, "ghost_persample_tiles_bf16: null pointer");
+  GB_REQUIRE(colsum_of >= 0 && colsum_of <= 2 && (colsum_of == 0 || colsum_out != nullptr),
+             "ghost_persample_tiles_bf16: colsum_of must be 0, 1 (X) or 2 (Y) with an output buffer");
+  GB_REQUIRE(T > 0 && T < (1ll << 31) - 64 && m_cols > 0 && n_cols > 0, "ghost_persample_tiles_bf16: bad dimensions");
+  GB_REQUIRE(samples > 0 && sample0 >= 0 && sample0 + samples <= n_samples_total,
+             "ghost_persample_tiles_bf16: sample range outside the batch");
+  GB_REQUIRE(tiles_bytes >= ghost_persample_tiles_bytes(samples, m_cols, n_cols),
+             "ghost_persample_tiles_bf16: tile buffer too small");
+  GB_REQUIRE((reinterpret_cast<uintptr_t>(tiles_out) & 255u) == 0, "ghost_persample_tiles_bf16: tiles must be 256-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  XtyParams p = {};
+  p.mode = kEpiStoreTiles;
+  p.m_cols = m_cols;
+  p.n_cols = n_cols;
+  p.m_tiles = ceil_div(m_cols, XtyCfg::BM);
+  p.n_tiles = ceil_div(n_cols, XtyCfg::BN);
+  p.T = T;
+  p.k_splits = 1;
+  p.sample_major = 1;
+  p.kb_per_split = ceil_div(T, XtyCfg::BK);
+  p.v_is_f32 = 0;
+  p.colsum_of = colsum_of;
+  p.colsum_out = colsum_out;
+  p.cs_src = static_cast<const __nv_bfloat16*>(colsum_of == 1 ? X : Y);
+  p.cs_ld = (colsum_of == 1) ? ldx : ldy;
+  p.err = ds->err_word;
+  p.samples = samples;
+  p.sample0 = sample0;
+  p.vgrad = tiles_out;
+  CUtensorMap tx, ty;
+  int rc;
+  if ((rc = make_xty_maps(&tx, &ty, p, X, Y, n_samples_total, T, ldx, ldy)) != GHOST_OK) return rc;
+  if (pair_kernel_fits(g_persample_pair_mode, m_cols, n_cols) && p.blocked_x && p.blocked_y && xty_pair_usable(ds))
+    return launch_xty_pair_tiles(X, Y, n_samples_total, T, m_cols, n_cols, ldx, ldy, samples, sample0, tiles_out, 0,
+                                 colsum_of, colsum_out, ds, st);
+  return launch_xty(tx, ty, p, ds, st);
+}
+
+extern "C" int ghost_tile_dot_bf16(const void* V, int v_ranks, int v_per_rank, const void* W, int n_train, int m_cols,
+                                   int n_cols, float dot_scale, float* M_out, void* grad_out, int grad_is_f32,
+                                   float grad_scale, int grad_accumulate, void* stream) {
+  const DeviceState* ds = device_state();
+  if (!ds) return GHOST_ERR_DEVICE;
+  GB_REQUIRE(V && W && M_out, "ghost_tile_dot_bf16: null pointer");
+  GB_REQUIRE(n_train > 0, "No training samples to compute dot product, check batch sizes.");
+  GB_REQUIRE(v_ranks > 0 && v_per_rank > 0 && m_cols > 0 && n_cols > 0, "ghost_tile_dot_bf16: bad dimensions");
+  GB_REQUIRE(!grad_out || grad_is_f32 || n_train <= 32,
+             "ghost_tile_dot_bf16: a bf16 train gradient is written directly only for up to 32 train samples");
+  const int n_val = v_ranks * v_per_rank;
+  const int vr = n_val <= 8 ? 8 : (n_val <= 16 ? 16 : 32);
+  GB_REQUIRE(vr % v_per_rank == 0 || v_per_rank % vr == 0,
+             "ghost_tile_dot_bf16: %d validation samples per rank do not fit the kernel's blocks of %d", v_per_rank, vr);
+  GB_REQUIRE((reinterpret_cast<uintptr_t>(V) & 255u) == 0 && (reinterpret_cast<uintptr_t>(W) & 255u) == 0,
+             "ghost_tile_dot_bf16: tile buffers must be 256-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n_tiles_n = ceil_div(n_cols, XtyCfg::BN);
+  const long long tiles = static_cast<long long>(ceil_div(m_cols, XtyCfg::BM)) * n_tiles_n;
+  GB_CUDA_OK(cudaMemsetAsync(M_out, 0, sizeof(float) * static_cast<size_t>(n_val) * n_train, st));
+  return launch_tile_dot(V, n_val, 0, W, n_train, 0, tiles, n_val, n_train, 0, n_train, dot_scale, M_out, nullptr, 1,
+                         grad_out, grad_is_f32, grad_accumulate, m_cols, n_cols, n_tiles_n, grad_scale, ds, st,
+                         v_per_rank);
 }

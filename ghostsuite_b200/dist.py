@@ -294,6 +294,52 @@ class ShardedValidation:
         return out[0], out[1], n_val_local * self.world
 
 
+class ValidationExchange:
+    """What the layer functions need to exchange validation gradients (``gather_rows``): an
+    all-gather along dimension 0 into a new local tensor, rank-major."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.calls = 0
+        self.bytes = 0
+
+    def gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        x = x.contiguous()
+        out = x.new_empty((x.shape[0] * self.world,) + tuple(x.shape[1:]))
+        dist.all_gather_into_tensor(out, x, group=self.group)
+        self.calls += 1
+        self.bytes += out.numel() * out.element_size()
+        return out
+
+    def gather_rows_async(self, x: torch.Tensor, out: Optional[torch.Tensor] = None):
+        """``(out, work)``: the all-gather is enqueued behind what the current stream holds so far and
+        nothing waits for it until ``work.wait()``.  ``out`` may be the contiguous tail of a larger
+        tensor."""
+        x = x.contiguous()
+        if out is None:
+            out = x.new_empty((x.shape[0] * self.world,) + tuple(x.shape[1:]))
+        work = dist.all_gather_into_tensor(out, x, group=self.group, async_op=True)
+        self.calls += 1
+        self.bytes += out.numel() * out.element_size()
+        return out, work
+
+
+def exchange_validation(engine, group=None) -> ValidationExchange:
+    """:func:`shard_validation` with the cheaper exchange where a layer allows it: on the per-sample
+    path of Linear / Conv1D layers every rank computes the gradient tiles of its own validation
+    samples and the ranks all-gather those (``2 * n_val * d * p`` bytes per layer) instead of the
+    validation rows of both operands, and no rank repeats another rank's validation GEMMs; bias and
+    norm layers exchange their per-sample vectors.  Other layers (Gram path, embeddings) gather
+    operands as :class:`ShardedValidation` does.  Undo with :func:`unshard_validation`."""
+    from .ghostEngines import supported_layers_grad_samplers_dotprod as layers
+    shard_validation(engine, group)
+    ex = ValidationExchange(group)
+    layers.VALIDATION_EXCHANGE = ex
+    engine._ghost_val_exchange = ex
+    return ex
+
+
 def shard_validation(engine, group=None) -> ShardedValidation:
     """Install :class:`ShardedValidation` for the hooks of ``engine`` (built with the per-rank
     validation count).  Pass ``n_val_local`` to :func:`sync_engine` afterwards; undo with
@@ -307,9 +353,13 @@ def shard_validation(engine, group=None) -> ShardedValidation:
 
 def unshard_validation(engine=None) -> None:
     from .ghostEngines import autograd_grad_sample_dotprod as plumbing
+    from .ghostEngines import supported_layers_grad_samplers_dotprod as layers
     plumbing.VALIDATION_GATHER = None
-    if engine is not None and hasattr(engine, "_ghost_val_shard"):
-        del engine._ghost_val_shard
+    layers.VALIDATION_EXCHANGE = None
+    if engine is not None:
+        for attr in ("_ghost_val_shard", "_ghost_val_exchange"):
+            if hasattr(engine, attr):
+                delattr(engine, attr)
 
 
 def overlap_train_grad_sync(engine, group=None, bucket_bytes: int = 32 << 20) -> OverlappedGradSync:

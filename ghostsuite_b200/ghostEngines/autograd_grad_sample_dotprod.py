@@ -105,16 +105,30 @@ def _prepare_sample_grad_or_dotprod(layer: nn.Module, grad_output: Tuple[torch.T
     # 'mean' losses carry a 1/batch factor (the batch this process ran); the train-gradient kernels
     # undo it in their epilogue
     layer._ghost_backprop_scale = float(backprops.shape[0]) if loss_reduction == "mean" else 1.0
-    if VALIDATION_GATHER is not None and A is not None:
-        A, backprops, val_batch_size = VALIDATION_GATHER(layer, A, backprops, val_batch_size)
-        layer.activations = A
-    layer._ghost_val_batch = val_batch_size
     # the per-parameter [n_train] vectors are reduced in one batched op when the backward pass ends
     if _layers.begin_deferred_dots():
         try:
             torch.autograd.Variable._execution_engine.queue_callback(_layers.finalize_pending_dots)
         except Exception:
             _layers.finalize_pending_dots()      # not inside a backward pass: reduce immediately
+    exchange = _layers.VALIDATION_EXCHANGE
+    if exchange is not None and VALIDATION_GATHER is not None and A is not None and A.is_floating_point():
+        # validation batch split over ranks: the ranks exchange validation gradients where the layer
+        # type allows it ...
+        layer._ghost_val_batch = val_batch_size
+        try:
+            handled = _layers.dot_product_with_exchange(layer, A, backprops, val_batch_size, exchange)
+        except BaseException:
+            _layers.finalize_pending_dots()
+            raise
+        if handled:
+            layer.backprops = backprops
+            return
+    if VALIDATION_GATHER is not None and A is not None:
+        # ... and validation operands everywhere else
+        A, backprops, val_batch_size = VALIDATION_GATHER(layer, A, backprops, val_batch_size)
+        layer.activations = A
+    layer._ghost_val_batch = val_batch_size
     try:
         dot_fn(layer, A, backprops, val_batch_size=val_batch_size)
     except BaseException:
@@ -142,7 +156,8 @@ def _apply_train_grad(layer: nn.Module, val_batch_size: int, loss_reduction: str
                     raise ValueError(
                         f"Layer {layer.__class__.__name__} returned None for weight gradient. "
                         "Ensure the compute_layer_train_grad function is implemented correctly.")
-                _create_or_accumulate_train_grad(weight, grad_weight)
+                if grad_weight is not _layers.DEFERRED:      # else: handed over by the launch that makes it
+                    _create_or_accumulate_train_grad(weight, grad_weight)
             bias = getattr(layer, "bias", None)
             if bias is not None and getattr(bias, "initially_requires_grad", bias.requires_grad):
                 _train_grad_bias_from_layer(layer, val_batch_size, loss_reduction)

@@ -64,7 +64,7 @@ def _token_count(A: torch.Tensor) -> int:
 
 
 def _should_use_ghost_computation(layer: nn.Module, A: torch.Tensor, B: torch.Tensor,
-                                  conv: bool = False, val_batch_size: int = None):
+                                  conv: bool = False, val_batch_size: int = None, n_train: int = None):
     """Decide once per layer whether the Gram kernel is used (cached in
     ``layer.use_ghost_computation``, as in the reference at :7-41).
 
@@ -86,7 +86,7 @@ def _should_use_ghost_computation(layer: nn.Module, A: torch.Tensor, B: torch.Te
         layer.use_ghost_computation = bool(2 * T ** 2 <= layer.weight.numel())
         return
     n_v = int(val_batch_size)
-    n_t = int(A.shape[0]) - n_v
+    n_t = int(A.shape[0]) - n_v if n_train is None else int(n_train)
     gram = 2.0 * n_t * n_v * T * T * (d + p) / _GRAM_FLOPS
     if A.dtype == torch.float32:
         gram *= 3.0       # hi/lo split operands: three bf16 products per fp32 product, both paths
@@ -190,9 +190,14 @@ def finalize_pending_dots() -> None:
     matrix, as it does when every hook overwrites the attribute.  Safe to call when nothing is
     pending."""
     global _PENDING_DOTS, _PENDING_SMALL
+    ops.finish_exchange_jobs()       # streaming passes that still wait for their all-gather
     with _PENDING_LOCK:
         pending, _PENDING_DOTS = _PENDING_DOTS, None
         small, _PENDING_SMALL = _PENDING_SMALL, None
+        waits = list(_PENDING_WAITS)
+        del _PENDING_WAITS[:]
+    for work in waits:
+        work.wait()
     if small:
         ops.small_reduce_batch(small)
         for job in small:
@@ -269,6 +274,112 @@ def _bias_terms(layer: nn.Module, B: torch.Tensor, val_batch_size: int, colsums=
         colsums = ops.colsum(B)                   # [N, p] float32
     _set_dot(layer.bias, _gram_of_vectors(colsums, val_batch_size))
     layer._ghost_colsums = colsums               # reused by the bias train gradient
+
+
+# --------------------------------------------------------------------------------------------
+# Validation batch split over data-parallel ranks
+# --------------------------------------------------------------------------------------------
+#: set by ``ghostsuite_b200.dist.exchange_validation``: an object with ``world`` and
+#: ``gather_rows(t)`` (all-gather along dimension 0).  Every rank then runs ``1 / world`` of the
+#: validation batch through the model and the ranks exchange per-sample GRADIENTS of their validation
+#: samples instead of running each other's validation sequences: tiles on the per-sample path of
+#: Linear / Conv1D layers, the per-sample vectors of bias and norm layers.  Layers this function does
+#: not take (Gram path, embeddings, convolutions, fp32 operands) return False and get the other
+#: ranks' validation OPERANDS from the caller.
+VALIDATION_EXCHANGE = None
+
+#: let the all-gather of a layer's validation tiles run under the next layer's kernels: the layer's
+#: streaming pass, its matrix and its train gradient then come one layer late (the last one when the
+#: backward pass ends)
+EXCHANGE_OVERLAP = True
+
+
+#: wait handles of small all-gathers whose results only the end-of-backward batch reads
+_PENDING_WAITS = []
+
+#: returned by a train-gradient function whose result is handed to
+#: ``_create_or_accumulate_train_grad`` later, by the launch that computes it
+DEFERRED = object()
+
+
+def _with_gathered_val_rows(x: torch.Tensor, n_train: int, ex) -> torch.Tensor:
+    """``cat(x[:n_train], all ranks' x[n_train:])`` for per-sample vectors ``x[N_local, F]``.  Inside a
+    backward pass the all-gather is only waited for when the pass ends (its result feeds the batched
+    small reductions), so it never holds up the kernels of the following layers."""
+    n_val_local = x.shape[0] - n_train
+    with _PENDING_LOCK:
+        deferred = _PENDING_SMALL is not None and hasattr(ex, "gather_rows_async")
+    if not deferred:
+        return torch.cat([x[:n_train], ex.gather_rows(x[n_train:].contiguous())], dim=0)
+    full = x.new_empty((n_train + n_val_local * int(ex.world),) + tuple(x.shape[1:]))
+    full[:n_train].copy_(x[:n_train])
+    _, work = ex.gather_rows_async(x[n_train:], out=full[n_train:])
+    with _PENDING_LOCK:
+        _PENDING_WAITS.append(work)
+    return full
+
+
+def dot_product_with_exchange(layer: nn.Module, A: torch.Tensor, B: torch.Tensor, n_val_local: int, ex) -> bool:
+    """Dot products of ``layer`` from local operands plus exchanged validation gradients; True when
+    the layer was handled (the train-gradient functions then run on the local operands as usual)."""
+    world = int(ex.world)
+    n_train = A.size(0) - n_val_local
+    if world <= 1 or n_train <= 0 or n_val_local <= 0:
+        return False
+    n_val = n_val_local * world
+    if isinstance(layer, nn.LayerNorm):
+        gw, gb = _layernorm_vectors(layer, A, B)
+        if layer.bias is None:
+            _set_dot(layer.weight, _gram_of_vectors(_with_gathered_val_rows(gw, n_train, ex), n_val))
+            return True
+        # (two collectives: their results may still be in flight, so nothing here may copy them)
+        _set_dot(layer.weight, _gram_of_vectors(_with_gathered_val_rows(gw, n_train, ex), n_val))
+        _set_dot(layer.bias, _gram_of_vectors(_with_gathered_val_rows(gb, n_train, ex), n_val))
+        return True
+    if type(layer) in _SELF_APPLYING and type(layer).__name__.endswith("RMSNorm"):
+        gw = _rmsnorm_vectors(layer, A, B)
+        _set_dot(layer.weight, _gram_of_vectors(_with_gathered_val_rows(gw, n_train, ex), n_val))
+        return True
+    if _HFConv1D is not None and isinstance(layer, _HFConv1D):
+        weight_is_in_by_out = True
+    elif isinstance(layer, nn.Linear):
+        weight_is_in_by_out = False
+    else:
+        return False
+    A = A.detach()
+    B = B.detach()
+    _should_use_ghost_computation(layer, A, B, val_batch_size=n_val, n_train=n_train)
+    if layer.use_ghost_computation:
+        return False
+    X, Y = (A, B) if weight_is_in_by_out else (B, A)
+    want = bool(getattr(layer.weight, "initially_requires_grad", True))
+    has_bias = getattr(layer, "bias", None) is not None
+    with _PENDING_LOCK:
+        in_backward = _PENDING_DOTS is not None
+    holder = {}
+
+    def hand_over(weight=layer.weight):
+        if holder.get("grad") is not None:
+            _create_or_accumulate_train_grad(weight, holder["grad"])
+
+    res = ops.persample_dot_exchanged(
+        X, Y, n_val_local, ex, want_grad=want, grad_scale=_backprop_scale(layer) / n_train,
+        grad_dtype=_grad_dtype(layer.weight, A),
+        colsum_of=("Y" if weight_is_in_by_out else "X") if (has_bias and FUSE_BIAS_COLSUMS) else None,
+        on_ready=hand_over if (in_backward and EXCHANGE_OVERLAP) else None)
+    if res is None:
+        return False
+    M, grad, colsums = res
+    if want:
+        late = in_backward and EXCHANGE_OVERLAP and hasattr(ex, "gather_rows_async")
+        holder["grad"] = grad if late else None
+        layer._ghost_cached_train_grad = (A.data_ptr(), B.data_ptr(), A.size(0), DEFERRED if late else grad)
+    _set_dot(layer.weight, M)
+    if has_bias:
+        if colsums is None:
+            colsums = ops.colsum(B)
+        _bias_terms(layer, B, n_val, _with_gathered_val_rows(colsums, n_train, ex))
+    return True
 
 
 # --------------------------------------------------------------------------------------------

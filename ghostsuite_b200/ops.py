@@ -273,6 +273,9 @@ def wgrad(X: torch.Tensor, Y: torch.Tensor, scale: float, out_dtype: torch.dtype
     return out
 
 
+_PERSAMPLE_NAME = "xty_gemm_pair_kernel+tile_dot_mma_kernel[persample]"
+
+
 def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float = 1.0,
                   want_grad: bool = False, grad_scale: float = 1.0,
                   grad_dtype: Optional[torch.dtype] = None, colsum_of: Optional[str] = None):
@@ -313,7 +316,7 @@ def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float
     if colsum_of is not None and not split:
         colsums = torch.empty((N, m if colsum_of == "X" else n), dtype=_F32, device=X.device)
         cs_flag = 1 if colsum_of == "X" else 2
-    with _Timed("xty_gemm_pair_kernel+tile_dot_mma_kernel[persample]", "tensor",
+    with _Timed(_PERSAMPLE_NAME, "tensor",
                 2.0 * N * T * m * n + 2.0 * n_val * n_train * m * n, 2.0 * N * T * (m + n)):
         xp, yp, ldx, ldy, T_eff = mat(base)
         _lib.check(lib.ghost_persample_dot_bf16(
@@ -323,6 +326,134 @@ def persample_dot(X: torch.Tensor, Y: torch.Tensor, n_val: int, dot_scale: float
             base + off_ws, ws_bytes, _stream_ptr()))
     if colsum_of is None:
         return M, grad
+    return M, grad, colsums
+
+
+def persample_tiles(X: torch.Tensor, Y: torch.Tensor, sample0: int, samples: int,
+                    colsum_of: Optional[str] = None, colsums: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """First pass of the per-sample path alone: the bf16 tiles ``X_s^T Y_s`` of samples
+    ``[sample0, sample0 + samples)``, laid out ``[tiles, samples, 32768]`` (128 x 256 tiles).  ``X`` /
+    ``Y``: contiguous bf16 ``[N, T, cols]`` with column counts that are multiples of 8.  With
+    ``colsum_of`` the rows ``sample0 ..`` of ``colsums`` (``[N, cols]`` float32) are filled too."""
+    lib = _lib.load()
+    N, T, m = X.shape
+    n = Y.shape[-1]
+    nbytes = int(lib.ghost_persample_tiles_bytes(samples, m, n))
+    tiles = torch.empty((nbytes // (samples * 65536), samples, 32768), dtype=_BF16, device=X.device)
+    cs_flag = 0 if colsum_of is None else (1 if colsum_of == "X" else 2)
+    with _Timed(_PERSAMPLE_NAME, "tensor", 2.0 * samples * T * m * n, 2.0 * samples * T * (m + n)):
+        _lib.check(lib.ghost_persample_tiles_bf16(
+            X.data_ptr(), Y.data_ptr(), N, T, m, n, m, n, int(sample0), int(samples), cs_flag,
+            colsums.data_ptr() if cs_flag else None, tiles.data_ptr(), nbytes, _stream_ptr()))
+    return tiles
+
+
+def tile_dot(V: torch.Tensor, W: torch.Tensor, m: int, n: int, dot_scale: float = 1.0,
+             want_grad: bool = False, grad_scale: float = 1.0, grad_dtype: torch.dtype = _BF16,
+             M: Optional[torch.Tensor] = None, grad: Optional[torch.Tensor] = None):
+    """Second pass alone.  ``W``: train tiles ``[tiles, n_train, 32768]``; ``V``: validation tiles, either
+    ``[tiles, n_val, 32768]`` or, as an all-gather over ranks leaves them, ``[ranks, tiles, per_rank,
+    32768]`` (validation sample ``r * per_rank + i`` of the result is sample ``i`` of rank ``r``).
+    Returns ``(M[n_val, n_train], train_grad[m, n] or None)``, written into ``M`` / ``grad`` when given."""
+    lib = _lib.load()
+    if V.dim() == 3:
+        V = V.unsqueeze(0)
+    ranks, tiles, per_rank, _ = V.shape
+    n_train = W.shape[1]
+    n_val = ranks * per_rank
+    if M is None:
+        M = torch.empty((n_val, n_train), dtype=_F32, device=W.device)
+    if want_grad and grad is None:
+        grad = torch.empty((m, n), dtype=grad_dtype, device=W.device)
+    with _Timed(_PERSAMPLE_NAME, "tensor", 2.0 * n_val * n_train * m * n, 0.0):
+        _lib.check(lib.ghost_tile_dot_bf16(
+            V.data_ptr(), ranks, per_rank, W.data_ptr(), n_train, m, n, float(dot_scale), M.data_ptr(),
+            grad.data_ptr() if want_grad else None, _dt_flag(grad) if want_grad else 0, float(grad_scale), 0,
+            _stream_ptr()))
+    return M, (grad if want_grad else None)
+
+
+# Streaming passes that wait for an all-gather in flight, per (device, stream): the pass of one layer
+# is launched when the next layer has launched its own tile passes and all-gather (or by
+# ``finish_exchange_jobs``), so the transfer runs under that layer's GEMMs.
+_exchange_jobs: Dict[Tuple[int, int], dict] = {}
+
+
+def _finish_exchange_job(job: dict) -> None:
+    job["work"].wait()               # the current stream waits for the all-gather
+    tile_dot(job["V"], job["W"], job["m"], job["n"], job["dot_scale"], job["grad"] is not None,
+             job["grad_scale"], _BF16, M=job["M"], grad=job["grad"])
+    cb = job["on_ready"]
+    job.clear()
+    if cb is not None:
+        cb()
+
+
+def finish_exchange_jobs() -> None:
+    """Launch the streaming pass of every layer that still waits for its all-gather."""
+    for key in list(_exchange_jobs):
+        _finish_exchange_job(_exchange_jobs.pop(key))
+
+
+def persample_dot_exchanged(X: torch.Tensor, Y: torch.Tensor, n_val_local: int, exchange, dot_scale: float = 1.0,
+                            want_grad: bool = False, grad_scale: float = 1.0,
+                            grad_dtype: Optional[torch.dtype] = None, colsum_of: Optional[str] = None,
+                            on_ready=None):
+    """The per-sample path of a rank that holds ``n_val_local`` of the validation samples (the last
+    rows of ``X`` / ``Y``): tiles of the local validation samples, an all-gather of them along
+    dimension 0 over ``exchange.world`` ranks (``exchange.gather_rows``), tiles of the local train
+    samples, then the contraction of ALL validation tiles with the local train tiles.  Returns
+    ``(M[world * n_val_local, n_train], train_grad or None, colsums of the LOCAL samples or None)``, or
+    None when the shapes are outside what the two-pass entry points take (fp32 operands, a bf16
+    train gradient of more than 32 samples, a validation split that does not fit the kernel's row
+    blocks).
+
+    With ``on_ready`` and an exchange that has ``gather_rows_async`` the all-gather is not waited
+    for: ``M`` and the gradient are filled by a later launch -- when the next call on this stream has
+    enqueued its own tile passes, or in :func:`finish_exchange_jobs` -- and ``on_ready()`` is called
+    right after that launch has been enqueued."""
+    _require_cuda(X, Y)
+    if X.dtype != _BF16 or Y.dtype != _BF16:
+        return None
+    X, Y = _as3d(X), _as3d(Y)
+    N, T, m = X.shape
+    n = Y.shape[-1]
+    n_train = N - n_val_local
+    ranks = int(exchange.world)
+    if n_train <= 0:
+        raise ValueError("No training samples to compute dot product, check batch sizes.")
+    if n_val_local <= 0 or Y.shape[0] != N or Y.shape[1] != T or not (_tma_ready(X) and _tma_ready(Y)):
+        return None
+    gdt = grad_dtype or X.dtype
+    if want_grad and gdt != _F32 and n_train > 32:
+        return None
+    n_val = n_val_local * ranks
+    block = 8 if n_val <= 8 else (16 if n_val <= 16 else 32)
+    if block % n_val_local != 0 and n_val_local % block != 0:
+        return None
+    if colsum_of not in (None, "X", "Y"):
+        raise ValueError("colsum_of must be None, 'X' or 'Y'")
+    colsums = None
+    if colsum_of is not None:
+        colsums = torch.empty((N, m if colsum_of == "X" else n), dtype=_F32, device=X.device)
+    V_loc = persample_tiles(X, Y, n_train, n_val_local, colsum_of, colsums)
+    deferred = on_ready is not None and hasattr(exchange, "gather_rows_async")
+    if deferred:
+        V_all, work = exchange.gather_rows_async(V_loc.unsqueeze(0))
+    else:
+        V_all = exchange.gather_rows(V_loc.unsqueeze(0))     # [ranks, tiles, n_val_local, 32768]
+    W = persample_tiles(X, Y, 0, n_train, colsum_of, colsums)
+    if not deferred:
+        M, grad = tile_dot(V_all, W, m, n, dot_scale, want_grad, grad_scale, gdt)
+        return M, grad, colsums
+    M = torch.empty((n_val, n_train), dtype=_F32, device=X.device)
+    grad = torch.empty((m, n), dtype=gdt, device=X.device) if want_grad else None
+    key = (X.device.index if X.device.index is not None else torch.cuda.current_device(), _stream_ptr())
+    prev = _exchange_jobs.pop(key, None)
+    _exchange_jobs[key] = {"V": V_all, "W": W, "work": work, "m": m, "n": n, "dot_scale": dot_scale,
+                           "grad_scale": grad_scale, "M": M, "grad": grad, "on_ready": on_ready}
+    if prev is not None:
+        _finish_exchange_job(prev)
     return M, grad, colsums
 
 

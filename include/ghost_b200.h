@@ -125,6 +125,30 @@ int ghost_persample_dot_bf16(const void* X, const void* Y, int n_train, int n_va
                              float grad_scale, int grad_accumulate, int colsum_of, float* colsum_out,
                              void* ws, long long ws_bytes, void* stream);
 
+/* The same path as two calls, for callers that put something between the passes: in a data-parallel
+ * run whose ranks each hold a part of the validation batch, a rank computes the tiles of its own
+ * validation samples, all-gathers them (NCCL, into local memory), and then contracts all validation
+ * tiles with its train tiles -- half the bytes of gathering the validation operands, and no rank
+ * repeats another rank's validation GEMMs.
+ *   ghost_persample_tiles_bf16: the tile pass for samples [sample0, sample0 + samples) of X, Y
+ *     ([n_samples_total, T, cols] bf16) into tiles_out, laid out [tile][samples][128 x 256] bf16
+ *     (ghost_persample_tiles_bytes, 256-byte aligned); colsum_of / colsum_out as above (rows sample0..).
+ *   ghost_tile_dot_bf16: M_out[v, b] = dot_scale * <V_v, W_b> and, if grad_out != NULL, the train
+ *     gradient grad_scale * sum_b W_b (bf16 only for n_train <= 32).  W: [tile][n_train][128 x 256];
+ *     V: [v_ranks][tile][v_per_rank][128 x 256], what all_gather leaves (validation sample v of the
+ *     result is sample v % v_per_rank of rank v / v_per_rank; v_ranks = 1 is a plain tile-major
+ *     buffer).  v_per_rank must divide, or be a multiple of, the kernel's block of 8 / 16 / 32
+ *     validation rows (8 up to 8 validation samples, 16 up to 16, else 32).
+ * Same reference lines as ghost_persample_dot_bf16. */
+long long ghost_persample_tiles_bytes(int samples, int m_cols, int n_cols);
+int ghost_persample_tiles_bf16(const void* X, const void* Y, int n_samples_total, long long T, int m_cols,
+                               int n_cols, long long ldx, long long ldy, int sample0, int samples,
+                               int colsum_of, float* colsum_out, void* tiles_out, long long tiles_bytes,
+                               void* stream);
+int ghost_tile_dot_bf16(const void* V, int v_ranks, int v_per_rank, const void* W, int n_train, int m_cols,
+                        int n_cols, float dot_scale, float* M_out, void* grad_out, int grad_is_f32,
+                        float grad_scale, int grad_accumulate, void* stream);
+
 /* ---- bias / LayerNorm / small reductions ------------------------------------------------------- */
 /* out[n, c] = sum_t G[n, t, c]  (fp32).  Replaces the token sums of
  * ghostEngines/supported_layers_grad_samplers_dotprod.py:138-146, 454-471 and

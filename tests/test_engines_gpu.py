@@ -860,3 +860,124 @@ def test_step_under_cuda_graph_replay():
         assert O.rel_fro(gr, p.train_grad) < 1e-5
     e_eng.detach()
     eng.detach()
+
+
+class _RecordedExchange:
+    """Stands in for the process group of a validation batch split over ``world`` ranks, on one GPU.
+    What a rank SENDS never depends on what it receives, so every rank is first run with
+    ``replay=None`` (its sends are recorded in call order, it receives zeros), then again with the
+    recordings of all ranks."""
+
+    def __init__(self, rank, world, replay=None):
+        self.rank, self.world, self.replay = rank, world, replay
+        self.sent = []
+        self.calls = 0
+
+    def _exchange(self, x):
+        x = x.contiguous()
+        i = len(self.sent)
+        self.sent.append(x.clone())
+        if self.replay is None:
+            parts = [x if r == self.rank else torch.zeros_like(x) for r in range(self.world)]
+        else:
+            parts = [self.replay[r][i] for r in range(self.world)]
+        self.calls += 1
+        return torch.cat(parts, dim=0)
+
+    def gather_rows(self, x):
+        return self._exchange(x)
+
+    def __call__(self, layer, A, B, n_val_local):          # the operand gather of ShardedValidation
+        n_train = A.shape[0] - n_val_local
+        out = [torch.cat([x[:n_train], self._exchange(x[n_train:])], dim=0) for x in (A, B)]
+        return out[0], out[1], n_val_local * self.world
+
+
+class _RecordedExchangeAsync(_RecordedExchange):
+    """The same with the non-blocking form the engine uses to run a layer's all-gather under the next
+    layer's kernels.  The output holds NaN until ``wait()`` is called, so anything that reads or
+    copies it early shows up in the results."""
+
+    class _Work:
+        def __init__(self, out, res):
+            self.out, self.res = out, res
+
+        def wait(self):
+            if self.res is not None:
+                self.out.copy_(self.res)
+                self.res = None
+            return True
+
+    def gather_rows_async(self, x, out=None):
+        res = self._exchange(x)
+        if out is None:
+            out = torch.empty_like(res)
+        out.fill_(float("nan"))
+        return out, self._Work(out, res)
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+@pytest.mark.parametrize("world", [2, 4])
+def test_validation_gradient_exchange_matches_replicated_validation(world, overlap):
+    """Validation batch split over ranks with the ranks exchanging validation GRADIENTS (tiles on the
+    per-sample path, per-sample vectors of bias and norm layers, operands elsewhere): every rank's
+    matrices equal those of the same rank run with the whole validation batch replicated, up to the
+    (local batch size)^2 factor of the loss mean, and the train gradients are the same."""
+    from ghostsuite_b200.ghostEngines import GradDotProdEngine
+    from ghostsuite_b200.ghostEngines import autograd_grad_sample_dotprod as plumbing
+    from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as L
+    from ghostsuite_b200.workloads import GPT2Like, GPT2Config
+    torch.manual_seed(6)
+    cfg = GPT2Config(vocab_size=211, n_positions=48, n_embd=64, n_layer=2, n_head=4)
+    model = GPT2Like(cfg).to(torch.bfloat16).cuda()
+    n_t, per, T = 3, 4 // world if world == 4 else 2, 40
+    n_val = per * world
+    g = torch.Generator().manual_seed(3)
+    train = [torch.randint(0, cfg.vocab_size, (n_t, T), generator=g).cuda() for _ in range(world)]
+    val = torch.randint(0, cfg.vocab_size, (n_val, T), generator=g).cuda()
+
+    def run(ids, n_v, exchange):
+        opt = torch.optim.SGD(model.parameters(), lr=0.0)
+        eng = GradDotProdEngine(module=model, val_batch_size=n_v, use_dummy_bias=True)
+        eng.attach(opt)
+        plumbing.VALIDATION_GATHER = exchange
+        L.VALIDATION_EXCHANGE = exchange
+        try:
+            model(ids, labels=ids)[0].backward()
+            torch.cuda.synchronize()
+            out = {n: (p.grad_dot_prod_matrix.float().cpu(), p.train_grad.float().cpu())
+                   for n, p in model.named_parameters() if hasattr(p, "grad_dot_prod_matrix")}
+        finally:
+            plumbing.VALIDATION_GATHER = None
+            L.VALIDATION_EXCHANGE = None
+            eng.clear_gradients()
+            eng.detach()
+            for p in model.parameters():
+                p.requires_grad = True
+        return out
+
+    old_rule = L.PATH_RULE
+    L.PATH_RULE = "persample"
+    try:
+        recorders = []
+        cls = _RecordedExchangeAsync if overlap else _RecordedExchange
+        for r in range(world):
+            rec = cls(r, world)
+            run(torch.cat([train[r], val[r * per:(r + 1) * per]]), per, rec)
+            recorders.append(rec)
+        assert len({rec.calls for rec in recorders}) == 1 and recorders[0].calls > 0
+        replay = [rec.sent for rec in recorders]
+        for r in range(world):
+            ex = cls(r, world, replay)
+            got = run(torch.cat([train[r], val[r * per:(r + 1) * per]]), per, ex)
+            want = run(torch.cat([train[r], val]), n_val, None)
+            factor = ((n_t + n_val) / (n_t + per)) ** 2
+            assert set(got) == set(want)
+            for name in want:
+                assert got[name][0].shape == (n_val, n_t), name
+                # two bf16 forward / backward passes over different batches: a few percent on the
+                # smallest matrices
+                assert O.rel_fro(got[name][0], want[name][0] * factor) < 4e-2, (r, name)
+                assert O.rel_fro(got[name][1], want[name][1]) < 2e-2, (r, name)
+    finally:
+        L.PATH_RULE = old_rule

@@ -244,6 +244,42 @@ def test_persample_dot_cta_pair_kernel(case, dtype):
     assert lib.ghost_set_persample_pair_mode(3) < 0
 
 
+@pytest.mark.parametrize("case", [(5, 8, 70, 64, 128), (12, 8, 64, 256, 512), (7, 16, 33, 192, 320),
+                                  (33, 4, 40, 72, 264), (3, 32, 20, 128, 256)])
+def test_tile_pass_and_gathered_tile_dot(case):
+    """The per-sample path as two calls with the validation tiles laid out as an all-gather over
+    ranks leaves them ([ranks][tiles][per rank][128 x 256]): every split of the validation batch
+    gives the matrix and the train gradient of the one-call path (same tiles, same kernel)."""
+    n_t, n_v, T, d, p = case
+    A, G = make(n_t + n_v, T, d, p, torch.bfloat16, seed=50 + n_v)
+    Ac, Gc = A.cuda(), G.cuda()
+    o = ops()
+    gdt = torch.float32 if n_t > 32 else torch.bfloat16
+    M_ref, grad_ref, cs_ref = o.persample_dot(Gc, Ac, n_v, dot_scale=1.5, want_grad=True, grad_scale=0.25,
+                                              grad_dtype=gdt, colsum_of="X")
+    after()
+    block = 8 if n_v <= 8 else (16 if n_v <= 16 else 32)
+    for ranks in (1, 2, 4, 8):
+        per = n_v // ranks
+        if per * ranks != n_v or per == 0:
+            continue
+        assert block % per == 0 or per % block == 0
+        cs = torch.full((n_t + n_v, p), float("nan"), device="cuda")
+        V = torch.stack([o.persample_tiles(Gc, Ac, n_t + r * per, per, "X", cs) for r in range(ranks)])
+        W = o.persample_tiles(Gc, Ac, 0, n_t, "X", cs)
+        M, grad = o.tile_dot(V, W, p, d, dot_scale=1.5, want_grad=True, grad_scale=0.25, grad_dtype=gdt)
+        after()
+        assert O.rel_fro(M, M_ref.cpu()) < 1e-5, ranks
+        assert torch.equal(grad, grad_ref), ranks
+        assert O.rel_fro(cs, cs_ref.double().cpu()) < 1e-6, ranks
+    # a split that does not fit the kernel's blocks of validation rows is refused, not mangled
+    if n_v == 16:
+        V = torch.zeros(4, W.shape[0], 3, 32768, dtype=torch.bfloat16, device="cuda")      # 12 = 4 x 3
+        with pytest.raises(ValueError):
+            o.tile_dot(V, W, p, d)
+        assert o.persample_dot_exchanged(Gc[:n_t + 3], Ac[:n_t + 3], 3, lambda t: t.repeat(4, 1, 1, 1), 4) is None
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("shape", [(8, 6, 24), (12, 1, 10), (5, 300, 520), (3, 1024, 768)])
 def test_colsum_and_bias(shape, dtype):
