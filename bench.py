@@ -1479,6 +1479,8 @@ def main():
                     help="multi-GPU step: comma-separated variants to time (val_replicated is always timed)")
     ap.add_argument("--exchange-overlap", type=int, default=-1,
                     help="override the engines' EXCHANGE_OVERLAP switch (0 / 1) for an A/B run")
+    ap.add_argument("--exchange-depth", type=int, default=-1,
+                    help="override ops.EXCHANGE_DEPTH (layers whose streaming pass may wait for its all-gather)")
     ap.add_argument("--fuse-bias-colsums", type=int, default=-1,
                     help="override the engines' FUSE_BIAS_COLSUMS switch (0 / 1) for an A/B run")
     args = ap.parse_args()
@@ -1487,6 +1489,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     guard_stdout()
+    if args.exchange_depth >= 0:
+        from ghostsuite_b200 import ops as _ops
+        _ops.EXCHANGE_DEPTH = args.exchange_depth
     if args.exchange_overlap >= 0:
         from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as _L3
         _L3.EXCHANGE_OVERLAP = bool(args.exchange_overlap)

@@ -376,7 +376,11 @@ def tile_dot(V: torch.Tensor, W: torch.Tensor, m: int, n: int, dot_scale: float 
 # Streaming passes that wait for an all-gather in flight, per (device, stream): the pass of one layer
 # is launched when the next layer has launched its own tile passes and all-gather (or by
 # ``finish_exchange_jobs``), so the transfer runs under that layer's GEMMs.
-_exchange_jobs: Dict[Tuple[int, int], dict] = {}
+_exchange_jobs: Dict[Tuple[int, int], list] = {}
+
+#: how many layers' streaming passes may wait for their all-gather at a time (each holds its tile
+#: buffers); a pass is launched when this many later layers have issued theirs
+EXCHANGE_DEPTH = 1
 
 
 def _finish_exchange_job(job: dict) -> None:
@@ -392,7 +396,8 @@ def _finish_exchange_job(job: dict) -> None:
 def finish_exchange_jobs() -> None:
     """Launch the streaming pass of every layer that still waits for its all-gather."""
     for key in list(_exchange_jobs):
-        _finish_exchange_job(_exchange_jobs.pop(key))
+        for job in _exchange_jobs.pop(key):
+            _finish_exchange_job(job)
 
 
 def persample_dot_exchanged(X: torch.Tensor, Y: torch.Tensor, n_val_local: int, exchange, dot_scale: float = 1.0,
@@ -449,11 +454,11 @@ def persample_dot_exchanged(X: torch.Tensor, Y: torch.Tensor, n_val_local: int, 
     M = torch.empty((n_val, n_train), dtype=_F32, device=X.device)
     grad = torch.empty((m, n), dtype=gdt, device=X.device) if want_grad else None
     key = (X.device.index if X.device.index is not None else torch.cuda.current_device(), _stream_ptr())
-    prev = _exchange_jobs.pop(key, None)
-    _exchange_jobs[key] = {"V": V_all, "W": W, "work": work, "m": m, "n": n, "dot_scale": dot_scale,
-                           "grad_scale": grad_scale, "M": M, "grad": grad, "on_ready": on_ready}
-    if prev is not None:
-        _finish_exchange_job(prev)
+    queue = _exchange_jobs.setdefault(key, [])
+    queue.append({"V": V_all, "W": W, "work": work, "m": m, "n": n, "dot_scale": dot_scale,
+                  "grad_scale": grad_scale, "M": M, "grad": grad, "on_ready": on_ready})
+    while len(queue) > max(1, int(EXCHANGE_DEPTH)):
+        _finish_exchange_job(queue.pop(0))
     return M, grad, colsums
 
 

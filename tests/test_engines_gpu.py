@@ -956,8 +956,10 @@ def test_validation_gradient_exchange_matches_replicated_validation(world, overl
                 p.requires_grad = True
         return out
 
-    old_rule = L.PATH_RULE
+    from ghostsuite_b200 import ops as gops
+    old_rule, old_depth = L.PATH_RULE, gops.EXCHANGE_DEPTH
     L.PATH_RULE = "persample"
+    gops.EXCHANGE_DEPTH = 3 if world == 4 else 1       # streaming passes up to three layers late
     try:
         recorders = []
         cls = _RecordedExchangeAsync if overlap else _RecordedExchange
@@ -981,3 +983,4 @@ def test_validation_gradient_exchange_matches_replicated_validation(world, overl
                 assert O.rel_fro(got[name][1], want[name][1]) < 2e-2, (r, name)
     finally:
         L.PATH_RULE = old_rule
+        gops.EXCHANGE_DEPTH = old_depth
