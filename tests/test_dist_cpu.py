@@ -232,6 +232,44 @@ def test_sharded_validation_gather():
     assert _run_ranks(_worker_val_shard) == [(0, True), (1, True)]
 
 
+def _worker_val_exchange(rank, world, port, q):
+    """Validation batch split over ranks with per-sample GRADIENTS exchanged: the all-gather of the
+    validation rows of per-sample vectors, blocking and non-blocking (into the tail of a larger
+    tensor, waited for when the backward pass ends), gives cat(own train rows, all validation rows)
+    in rank order."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as L
+        g = torch.Generator().manual_seed(5)
+        n_t, n_v, F = 4, 4, 6
+        X = torch.randn(n_t + n_v, F, generator=g)               # per-sample vectors of the global batch
+        t_lo, t_hi = gdist.shard_bounds(n_t, rank, world)
+        v_lo, v_hi = gdist.shard_bounds(n_v, rank, world)
+        x_loc = torch.cat((X[t_lo:t_hi], X[n_t + v_lo:n_t + v_hi]))
+        want = torch.cat((X[t_lo:t_hi], X[n_t:]))
+        ex = gdist.ValidationExchange(None)
+        ok = ex.world == world
+        ok = ok and torch.equal(L._with_gathered_val_rows(x_loc, t_hi - t_lo, ex), want)      # nothing deferred
+        tiles = torch.arange(2 * 3 * (v_hi - v_lo) * 4, dtype=torch.float32).reshape(1, 2 * 3, v_hi - v_lo, 4) + 1000 * rank
+        both = ex.gather_rows(tiles)                              # [ranks, tiles, per rank, elems], rank-major
+        ok = ok and both.shape[0] == world and torch.equal(both[rank], tiles[0]) and float(both[1 - rank][0, 0, 0]) == 1000.0 * (1 - rank)
+        assert L.begin_deferred_dots()
+        full = L._with_gathered_val_rows(x_loc, t_hi - t_lo, ex)  # in flight until the pass "ends"
+        ok = ok and len(L._PENDING_WAITS) == 1
+        L.finalize_pending_dots()
+        ok = ok and not L._PENDING_WAITS and torch.equal(full, want)
+        ok = ok and ex.calls == 3
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_validation_gradient_exchange_of_vectors():
+    assert _run_ranks(_worker_val_exchange) == [(0, True), (1, True)]
+
+
 def test_shard_bounds_cover_everything():
     for n in (1, 7, 8, 65536):
         for world in (1, 2, 3, 8):
