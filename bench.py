@@ -301,6 +301,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # ---------------------------------------------------------------- engine per variant
     state = {"engine": None, "sync": None, "deterministic": False}
+    graph_checks = {}
 
     def attention_backend():
         """The fused attention kernels of PyTorch sum their backward with atomics, so two runs of the
@@ -413,6 +414,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     engine.clear_gradients()
                     gopt.zero_grad(set_to_none=True)
                     drop_results()
+                # the eager result on these parameters and this batch, for the check of the first replay
+                loss, _ = model(x_static, labels=x_static)
+                loss.backward()
+                if world > 1:
+                    gdist.sync_engine(engine, group, check_equal_shards=False)
+                named = [p for p in model.parameters() if hasattr(p, "grad_dot_prod_matrix")]
+                eager_mats = torch.stack([p.grad_dot_prod_matrix for p in named]).clone()
+                engine.clear_gradients()
+                gopt.zero_grad(set_to_none=True)
+                drop_results()
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             l0 = _lib.launch_count()
@@ -428,6 +439,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         if float(ok.item()) == 0.0:
             raise RuntimeError("CUDA-graph capture failed" + (f" here: {err}" if err else " on another rank"))
         mats = [prm.grad_dot_prod_matrix for prm in model.parameters() if hasattr(prm, "grad_dot_prod_matrix")]
+        # first replay: same parameters, same batch as the eager step above (the fused attention
+        # backward is not bit-reproducible, hence a bf16-sized tolerance)
+        graph.replay()
+        torch.cuda.synchronize()
+        graph_checks[name + "_cuda_graph"] = {
+            "matrices_rel_err": _rel(torch.stack(mats), eager_mats), "against": "the eager step on the same parameters and batch"}
+        graph_checks[name + "_cuda_graph"]["ok"] = graph_checks[name + "_cuda_graph"]["matrices_rel_err"] < 2e-2
+        del eager_mats
 
         def step(i: int, from_host: bool):
             src = host[i % n_batches] if from_host else devb[i % n_batches]
@@ -660,7 +679,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "weak_scaling": weak,
         "ms_per_step_torch_loss": ms_torch_loss / args.steps,
     }
+    out["cuda_graph_check"] = graph_checks
     if dist_check is not None:
+        dist_check.update(graph_checks)
         out["dist_check"] = "ok" if all(v.get("ok", True) for v in dist_check.values()) else "FAILED"
         out["dist_check_detail"] = dist_check
     state["engine"].detach()
