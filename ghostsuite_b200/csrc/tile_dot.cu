@@ -239,25 +239,29 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 // is made as wide as the shared memory allows: 512 elements = 64 per warp = four k-steps.
 constexpr int kMmaCols = 512;
 
-template <int NVT>   // 8-row validation blocks per stage (1, 2 or 4)
+// NVT: 8-row validation blocks per stage (1, 2 or 4); MT: 16-row train blocks per stage (2, or 1
+// when the group has at most 16 train samples: a data-parallel rank's share of the batch -- the
+// stage then holds and the warps then work on half as many rows)
+template <int NVT, int MT = 2>
 struct TdMmaCfg {
+  static constexpr int kTrainRows = 16 * MT;
   static constexpr int kValRows = 8 * NVT;
   static constexpr int kPanels = kMmaCols / 64;                              // 64-element panels per stage row
   static constexpr int kWarpChunks = kMmaCols / 8 / 8;                       // 16-byte chunks per warp and stage
   static constexpr int kWarpKSteps = kWarpChunks / 2;
   static constexpr int kValBytes = kPanels * kValRows * 128;
-  static constexpr int kStageBytes = kValBytes + kPanels * kTdTrainRows * 128;   // 40 / 48 / 64 KB
+  static constexpr int kStageBytes = kValBytes + kPanels * kTrainRows * 128;     // 40 / 48 / 64 KB at MT = 2
   static constexpr int kStages = NVT == 1 ? 4 : 3;
-  static constexpr int kRedBytes = 8 * kTdTrainRows * kValRows * 4;          // per-warp partial dot blocks
+  static constexpr int kRedBytes = 8 * kTrainRows * kValRows * 4;            // per-warp partial dot blocks
   static constexpr int kSmemBytes = kStages * kStageBytes + kRedBytes + 1024 + 256;
 };
 
-template <int NVT>
+template <int NVT, int MT>
 __global__ void __launch_bounds__(288, 1)
 tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_w,
                     const TileDotParams p) {
-  using Cfg = TdMmaCfg<NVT>;
-  constexpr int kStages = Cfg::kStages, VR = Cfg::kValRows;
+  using Cfg = TdMmaCfg<NVT, MT>;
+  constexpr int kStages = Cfg::kStages, VR = Cfg::kValRows, TR = Cfg::kTrainRows;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* s_red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);            // [8 warps][32][VR]
@@ -284,7 +288,7 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      for (int j0 = 0; j0 < p.n_grp && ok; j0 += kTdTrainRows)
+      for (int j0 = 0; j0 < p.n_grp && ok; j0 += TR)
         for (int v0 = 0; v0 < p.n_val && ok; v0 += VR)
           for (long long s = s_begin; s < s_end; ++s) {
             if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, 431)) { ok = false; break; }
@@ -308,13 +312,13 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
   const int pn = (warp * CW) / 8, c0 = (warp * CW) % 8;
   const int g = lane >> 2, q = lane & 3;
   // ldmatrix lane addresses inside a stage (panel rows are 128 bytes, chunk index XOR (row & 7))
-  uint32_t a_off[2][KS];     // W as the A operand: [m-tile][k-step]
+  uint32_t a_off[MT][KS];    // W as the A operand: [m-tile][k-step]
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
       const int row = mt * 16 + (lane & 15), chunk = c0 + 2 * ks + (lane >> 4);
-      a_off[mt][ks] = Cfg::kValBytes + pn * (kTdTrainRows * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
+      a_off[mt][ks] = Cfg::kValBytes + pn * (TR * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
     }
   uint32_t b_off[NVT][KS / 2];   // V as the B operand: [n-tile][pair of k-steps], one x4 each
 #pragma unroll
@@ -325,13 +329,14 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
       b_off[nt][h] = pn * (VR * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
     }
   uint32_t t_off[CW];        // W transposed, for the column sums: [8-element group], rows = lane
+  const int trow = lane & (TR - 1);      // with 16 train rows lanes 16-31 repeat rows 0-15 (their matrices are not used)
 #pragma unroll
   for (int j = 0; j < CW; ++j)
-    t_off[j] = Cfg::kValBytes + pn * (kTdTrainRows * 128) + lane * 128 + (((c0 + j) ^ (lane & 7)) << 4);
+    t_off[j] = Cfg::kValBytes + pn * (TR * 128) + trow * 128 + (((c0 + j) ^ (trow & 7)) << 4);
 
   int stage = 0; uint32_t phase = 0;
   bool alive = true;
-  for (int j0 = 0; j0 < p.n_grp && alive; j0 += kTdTrainRows) {
+  for (int j0 = 0; j0 < p.n_grp && alive; j0 += TR) {
     // A operand of the column-sum MMA: 1.0 where the train row (the k index) belongs to the group
     uint32_t mask_a[2][4];
 #pragma unroll
@@ -342,9 +347,9 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
       mask_a[kr][0] = lo; mask_a[kr][1] = lo; mask_a[kr][2] = hi; mask_a[kr][3] = hi;
     }
     for (int v0 = 0; v0 < p.n_val && alive; v0 += VR) {
-      float acc[2][NVT][4];
+      float acc[MT][NVT][4];
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int nt = 0; nt < NVT; ++nt)
 #pragma unroll
@@ -358,9 +363,9 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) { alive = false; break; }
         const uint32_t st = smem_u32(smem + stage * Cfg::kStageBytes);
-        uint32_t a[2][KS][4];
+        uint32_t a[MT][KS][4];
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
           for (int ks = 0; ks < KS; ++ks) ldsm_x4(st + a_off[mt][ks], a[mt][ks]);
 #pragma unroll
@@ -370,7 +375,7 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
             uint32_t b[4];
             ldsm_x4(st + b_off[nt][h], b);
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
               mma_bf16_16816(acc[mt][nt], a[mt][2 * h], b[0], b[1]);
               mma_bf16_16816(acc[mt][nt], a[mt][2 * h + 1], b[2], b[3]);
             }
@@ -385,7 +390,7 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
             float cs[4] = {0.f, 0.f, 0.f, 0.f};
             ldsm_x4_trans(st + t_off[j], t);
             mma_bf16_16816(cs, mask_a[0], t[0], t[1]);
-            mma_bf16_16816(cs, mask_a[1], t[2], t[3]);
+            if (MT == 2) mma_bf16_16816(cs, mask_a[1], t[2], t[3]);
             if (g == (j & 7)) { t0 = cs[0]; t1 = cs[1]; }
           }
         }
@@ -440,9 +445,9 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
       // the only CTA-wide agreement: every compute warp gets here once per block, aborted or not
       if (!named_bar_and(1, 256, alive)) { alive = false; break; }
       // reduce the per-warp [32 train x VR val] partial blocks, one atomic per (v, b) and CTA
-      float* mine = s_red + warp * (kTdTrainRows * VR);
+      float* mine = s_red + warp * (TR * VR);
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int nt = 0; nt < NVT; ++nt) {
           const int b_lo = mt * 16 + g, v = nt * 8 + q * 2;
@@ -452,10 +457,10 @@ tile_dot_mma_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
           mine[(b_lo + 8) * VR + v + 1] = acc[mt][nt][3];
         }
       asm volatile("bar.sync 2, 256;" ::: "memory");
-      for (int idx = threadIdx.x; idx < kTdTrainRows * VR; idx += 256) {
+      for (int idx = threadIdx.x; idx < TR * VR; idx += 256) {
         float t = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) t += s_red[w * (kTdTrainRows * VR) + idx];
+        for (int w = 0; w < 8; ++w) t += s_red[w * (TR * VR) + idx];
         const int b = j0 + idx / VR, v = v0 + idx % VR;
         if (v < p.n_val && b < p.n_grp && t != 0.f)
           atomicAdd(&p.M[static_cast<long long>(v) * p.n_train + p.b0 + b], t * p.scale);
@@ -504,10 +509,10 @@ static int launch_tile_dot_t(const void* V, int v_samples, const void* W, int w_
   return post_launch("tile_dot_kernel");
 }
 
-template <int NVT>
-static int launch_tile_dot_mma(const void* V, int v_samples, const void* W, int w_samples, long long tiles,
-                               TileDotParams& p, const DeviceState* ds, cudaStream_t st) {
-  using Cfg = TdMmaCfg<NVT>;
+template <int NVT, int MT>
+static int launch_tile_dot_mma_t(const void* V, int v_samples, const void* W, int w_samples, long long tiles,
+                                 TileDotParams& p, const DeviceState* ds, cudaStream_t st) {
+  using Cfg = TdMmaCfg<NVT, MT>;
   CUtensorMap tv, tw;
   int rc;
   // [tiles][samples][32768] seen as [tiles][512 panels][samples][64]: one box = 4 panels of the stage
@@ -516,20 +521,27 @@ static int launch_tile_dot_mma(const void* V, int v_samples, const void* W, int 
   else
     rc = make_tmap_bf16_blocks(&tv, V, tiles, v_samples, kTileElems, kTileElems, Cfg::kValRows, Cfg::kPanels);
   if (rc != GHOST_OK) return rc;
-  if ((rc = make_tmap_bf16_blocks(&tw, W, tiles, w_samples, kTileElems, kTileElems, kTdTrainRows, Cfg::kPanels)) != GHOST_OK)
+  if ((rc = make_tmap_bf16_blocks(&tw, W, tiles, w_samples, kTileElems, kTileElems, Cfg::kTrainRows, Cfg::kPanels)) != GHOST_OK)
     return rc;
   static bool attr_set[64] = {};
   if (!attr_set[ds->device]) {
-    GB_CUDA_OK(cudaFuncSetAttribute(tile_dot_mma_kernel<NVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    GB_CUDA_OK(cudaFuncSetAttribute(tile_dot_mma_kernel<NVT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set[ds->device] = true;
   }
   long long ctas = ds->sm_count;
   if (ctas > p.stages) ctas = p.stages;
   p.stages_per_cta = (p.stages + ctas - 1) / ctas;
   ctas = (p.stages + p.stages_per_cta - 1) / p.stages_per_cta;
-  tile_dot_mma_kernel<NVT><<<static_cast<int>(ctas), 288, Cfg::kSmemBytes, st>>>(tv, tw, p);
+  tile_dot_mma_kernel<NVT, MT><<<static_cast<int>(ctas), 288, Cfg::kSmemBytes, st>>>(tv, tw, p);
   count_launch();
   return post_launch("tile_dot_mma_kernel");
+}
+
+template <int NVT>
+static int launch_tile_dot_mma(const void* V, int v_samples, const void* W, int w_samples, long long tiles,
+                               TileDotParams& p, const DeviceState* ds, cudaStream_t st) {
+  if (p.n_grp <= 16) return launch_tile_dot_mma_t<NVT, 1>(V, v_samples, W, w_samples, tiles, p, ds, st);
+  return launch_tile_dot_mma_t<NVT, 2>(V, v_samples, W, w_samples, tiles, p, ds, st);
 }
 
 // V: [tiles][v_samples][32768] with the validation samples at index v_off..v_off+n_val-1;

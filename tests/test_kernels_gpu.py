@@ -277,7 +277,21 @@ def test_tile_pass_and_gathered_tile_dot(case):
         V = torch.zeros(4, W.shape[0], 3, 32768, dtype=torch.bfloat16, device="cuda")      # 12 = 4 x 3
         with pytest.raises(ValueError):
             o.tile_dot(V, W, p, d)
-        assert o.persample_dot_exchanged(Gc[:n_t + 3], Ac[:n_t + 3], 3, lambda t: t.repeat(4, 1, 1, 1), 4) is None
+        class FourRanks:
+            world = 4
+
+            @staticmethod
+            def gather_rows(t):
+                return t.repeat(4, 1, 1, 1)
+
+        assert o.persample_dot_exchanged(Gc[:n_t + 3], Ac[:n_t + 3], 3, FourRanks) is None
+        res = o.persample_dot_exchanged(Gc[:n_t + 4], Ac[:n_t + 4], 4, FourRanks, want_grad=True,
+                                        grad_dtype=torch.float32, colsum_of="X")
+        after()
+        one = o.persample_dot(Gc[:n_t + 4], Ac[:n_t + 4], 4, want_grad=True, grad_dtype=torch.float32, colsum_of="X")
+        # four "ranks" that all hold the same four validation samples: the local block four times
+        assert res[0].shape == (16, n_t) and O.rel_fro(res[0], one[0].repeat(4, 1).cpu()) < 1e-5
+        assert torch.equal(res[1], one[1]) and O.rel_fro(res[2], one[2].double().cpu()) < 1e-6
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
