@@ -294,6 +294,21 @@ class ShardedValidation:
         return out[0], out[1], n_val_local * self.world
 
 
+def _require_equal_validation_shards(engine, group=None) -> None:
+    """Every all-gather of validation rows hands NCCL one buffer per rank of the same size: ranks that
+    hold different numbers of validation samples would stall it.  One two-integer collective when
+    the split is installed makes that a ``ValueError`` on every rank instead."""
+    n = int(engine.val_batch_size)
+    params = [p for p in engine.module.parameters()]
+    device = params[0].device if params else torch.device("cpu")
+    probe = torch.tensor([n, -n], dtype=torch.int64, device=device)
+    dist.all_reduce(probe, op=dist.ReduceOp.MIN, group=group)
+    lo, hi = int(probe[0]), -int(probe[1])
+    if lo != hi or n <= 0:
+        raise ValueError(f"ranks hold {lo}..{hi} validation samples; a split validation batch needs the same "
+                         "positive number on every rank")
+
+
 class ValidationExchange:
     """What the layer functions need to exchange validation gradients (``gather_rows``): an
     all-gather along dimension 0 into a new local tensor, rank-major."""
@@ -345,6 +360,7 @@ def shard_validation(engine, group=None) -> ShardedValidation:
     validation count).  Pass ``n_val_local`` to :func:`sync_engine` afterwards; undo with
     :func:`unshard_validation`."""
     from .ghostEngines import autograd_grad_sample_dotprod as plumbing
+    _require_equal_validation_shards(engine, group)
     sv = ShardedValidation(group)
     plumbing.VALIDATION_GATHER = sv
     engine._ghost_val_shard = sv

@@ -266,6 +266,34 @@ def _worker_val_exchange(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def _worker_val_unequal(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        class Eng:
+            module = nn.Linear(3, 2)
+            val_batch_size = 2 + rank
+        raised = 0
+        for install in (gdist.shard_validation, gdist.exchange_validation):
+            try:
+                install(Eng(), None)
+            except ValueError:
+                raised += 1
+            finally:
+                gdist.unshard_validation()
+        Eng.val_batch_size = 2
+        ok = raised == 2 and isinstance(gdist.exchange_validation(Eng(), None), gdist.ValidationExchange)
+        gdist.unshard_validation()
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_unequal_validation_shards_raise():
+    assert _run_ranks(_worker_val_unequal) == [(0, True), (1, True)]
+
+
 def test_validation_gradient_exchange_of_vectors():
     assert _run_ranks(_worker_val_exchange) == [(0, True), (1, True)]
 
