@@ -620,6 +620,25 @@ def test_error_codes_are_python_exceptions():
         o.small_gram(A.reshape(4, 24), 4)
     with pytest.raises(RuntimeError):
         o.colsum(A.cpu())
+    # the two-pass entry points through the raw C ABI: every refusal is GHOST_ERR_INVALID with a message
+    from ghostsuite_b200 import _lib
+    lib = _lib.load()
+    X = torch.zeros(6, 16, 64, dtype=torch.bfloat16, device="cuda")
+    tiles = torch.zeros(6 * 32768, dtype=torch.bfloat16, device="cuda")
+    M = torch.zeros(64, device="cuda")
+    nbytes = lib.ghost_persample_tiles_bytes(6, 64, 64)
+    assert nbytes == 6 * 65536 and lib.ghost_persample_tiles_bytes(0, 64, 64) == 0
+    args = lambda s0, ns, nb: (X.data_ptr(), X.data_ptr(), 6, 16, 64, 64, 64, 64, s0, ns, 0, None, tiles.data_ptr(), nb, None)
+    assert lib.ghost_persample_tiles_bf16(*args(0, 6, nbytes)) == 0
+    assert lib.ghost_persample_tiles_bf16(*args(4, 3, nbytes)) == -1 and b"sample range" in lib.ghost_last_error()
+    assert lib.ghost_persample_tiles_bf16(*args(0, 6, nbytes - 1)) == -1 and b"too small" in lib.ghost_last_error()
+    dot = lambda ranks, per, n_t, grad: lib.ghost_tile_dot_bf16(tiles.data_ptr(), ranks, per, tiles.data_ptr(), n_t, 64, 64, 1.0,
+                                                                M.data_ptr(), grad, 0, 1.0, 0, None)
+    assert dot(1, 2, 4, None) == 0
+    assert dot(4, 3, 4, None) == -1 and b"per rank" in lib.ghost_last_error()
+    assert dot(1, 2, 33, tiles.data_ptr()) == -1 and b"32 train samples" in lib.ghost_last_error()
+    assert dot(1, 2, 0, None) == -1
+    after()
 
 
 # ------------------------------------------------------------------------------------------------
