@@ -613,9 +613,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             rec = {"ms_dev": ms_dev, "ms_e2e": ms_e2e, "launches": graph_launches * args.steps, "h2d": h2d}
             sv = getattr(state["engine"], "_ghost_val_shard", None)
             ex = getattr(state["engine"], "_ghost_val_exchange", None)
-            if sv is not None:              # counted once, at capture (plus the two eager warm-up steps)
-                rec["val_gather_calls_per_step"] = (sv.calls + (ex.calls if ex else 0)) / 3
-                rec["val_gather_bytes_per_step"] = (sv.bytes + (ex.bytes if ex else 0)) / 3
+            if sv is not None:              # counted at capture, in the two warm-up steps and in the eager check step
+                rec["val_gather_calls_per_step"] = (sv.calls + (ex.calls if ex else 0)) / 4
+                rec["val_gather_bytes_per_step"] = (sv.bytes + (ex.bytes if ex else 0)) / 4
             results[base + "_cuda_graph"] = rec
             names.insert(1, base + "_cuda_graph")
             _lib.poll_kernel_error()

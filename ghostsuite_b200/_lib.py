@@ -25,7 +25,8 @@ _vp, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 class SmallJob(C.Structure):
     """``ghost_small_job`` of include/ghost_b200.h."""
     _fields_ = [("X", _vp), ("M", _vp), ("sum_out", _vp), ("n_train", _i), ("n_val", _i), ("F", _i),
-                ("sum_is_f32", _i), ("dot_scale", _f), ("sum_scale", _f)]
+                ("sum_is_f32", _i), ("dot_scale", _f), ("sum_scale", _f),
+                ("Xv", _vp), ("v_rank_pitch", _ll), ("v_per_rank", _i)]
 
 
 # name -> (restype, argtypes); mirrors include/ghost_b200.h one to one

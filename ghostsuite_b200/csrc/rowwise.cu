@@ -419,10 +419,13 @@ __global__ void __launch_bounds__(256) small_reduce_batch_kernel(const __grid_co
     const bool vec = (F & 3) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0;
     for (int pair = blockIdx.x * 8 + (threadIdx.x >> 5); pair < pairs; pair += warps) {
       const int v = pair / j.n_train, b = pair % j.n_train;
-      const float* xv = X + static_cast<long long>(j.n_train + v) * F;
+      const float* xv = j.Xv == nullptr
+                            ? X + static_cast<long long>(j.n_train + v) * F
+                            : j.Xv + static_cast<long long>(v / j.v_per_rank) * j.v_rank_pitch +
+                                  static_cast<long long>(v % j.v_per_rank) * F;
       const float* xb = X + static_cast<long long>(b) * F;
       float s = 0.f;
-      if (vec) {
+      if (vec && (reinterpret_cast<uintptr_t>(xv) & 15) == 0) {
         const float4* xv4 = reinterpret_cast<const float4*>(xv);
         const float4* xb4 = reinterpret_cast<const float4*>(xb);
         const int F4 = F >> 2;
@@ -465,6 +468,8 @@ extern "C" int ghost_small_reduce_batch(const ghost_small_job* jobs, int n_jobs,
     GB_REQUIRE(j.X != nullptr && (j.M != nullptr || j.sum_out != nullptr), "ghost_small_reduce_batch: job %d has no input or no output", i);
     GB_REQUIRE(j.n_train > 0 && j.F > 0 && j.n_val >= 0 && (j.M == nullptr || j.n_val > 0),
                "ghost_small_reduce_batch: job %d has an empty dimension", i);
+    GB_REQUIRE(j.Xv == nullptr || (j.v_per_rank > 0 && j.v_rank_pitch >= static_cast<long long>(j.v_per_rank) * j.F),
+               "ghost_small_reduce_batch: job %d has separate validation rows without a valid layout", i);
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   for (int first = 0; first < n_jobs; first += kSmallJobsPerLaunch) {

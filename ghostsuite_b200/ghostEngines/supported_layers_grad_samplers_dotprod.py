@@ -194,11 +194,8 @@ def finalize_pending_dots() -> None:
     with _PENDING_LOCK:
         pending, _PENDING_DOTS = _PENDING_DOTS, None
         small, _PENDING_SMALL = _PENDING_SMALL, None
-        waits = list(_PENDING_WAITS)
-        del _PENDING_WAITS[:]
-    for work in waits:
-        work.wait()
     if small:
+        _exchange_pending_val_rows(small)        # validation rows of a batch split over ranks
         ops.small_reduce_batch(small)
         for job in small:
             if job.get("param") is not None:
@@ -294,29 +291,46 @@ VALIDATION_EXCHANGE = None
 EXCHANGE_OVERLAP = True
 
 
-#: wait handles of small all-gathers whose results only the end-of-backward batch reads
-_PENDING_WAITS = []
-
 #: returned by a train-gradient function whose result is handed to
 #: ``_create_or_accumulate_train_grad`` later, by the launch that computes it
 DEFERRED = object()
 
 
 def _with_gathered_val_rows(x: torch.Tensor, n_train: int, ex) -> torch.Tensor:
-    """``cat(x[:n_train], all ranks' x[n_train:])`` for per-sample vectors ``x[N_local, F]``.  Inside a
-    backward pass the all-gather is only waited for when the pass ends (its result feeds the batched
-    small reductions), so it never holds up the kernels of the following layers."""
-    n_val_local = x.shape[0] - n_train
+    """``cat(x[:n_train], all ranks' x[n_train:])`` for per-sample vectors ``x[N_local, F]``."""
+    return torch.cat([x[:n_train], ex.gather_rows(x[n_train:].contiguous())], dim=0)
+
+
+def _gram_of_vectors_exchanged(x: torch.Tensor, n_train: int, n_val: int, ex) -> torch.Tensor:
+    """``[n_val, n_train]`` Gram of per-sample vectors whose validation rows are spread over the ranks
+    (``x[N_local, F]`` holds this rank's train rows and its own validation rows).  Inside a backward
+    pass nothing is sent here: the job joins the batched launch at the end of the pass, and ALL such
+    jobs' validation rows cross the ranks in ONE all-gather right before it (a hundred collectives of
+    a few kilobytes per step otherwise queue between the layers' tile all-gathers)."""
     with _PENDING_LOCK:
-        deferred = _PENDING_SMALL is not None and hasattr(ex, "gather_rows_async")
+        deferred = _PENDING_SMALL is not None
     if not deferred:
-        return torch.cat([x[:n_train], ex.gather_rows(x[n_train:].contiguous())], dim=0)
-    full = x.new_empty((n_train + n_val_local * int(ex.world),) + tuple(x.shape[1:]))
-    full[:n_train].copy_(x[:n_train])
-    _, work = ex.gather_rows_async(x[n_train:], out=full[n_train:])
-    with _PENDING_LOCK:
-        _PENDING_WAITS.append(work)
-    return full
+        return _gram_of_vectors(_with_gathered_val_rows(x, n_train, ex), n_val)
+    job = _small_job_for(x, n_train, n_val, "M")
+    M = torch.empty((n_val, n_train), dtype=torch.float32, device=x.device)
+    job["M"], job["n_val"], job["dot_scale"], job["val_exchange"] = M, n_val, 1.0, ex
+    return M
+
+
+def _exchange_pending_val_rows(jobs) -> None:
+    """One all-gather for the validation rows of every job that waits for them: each rank sends its
+    jobs' rows packed one after the other; job ``j`` then reads row ``r * per_rank + i`` at
+    ``gathered[r, offset_j + i * F]`` (``ops.small_reduce_batch``)."""
+    waiting = [j for j in jobs if j.get("val_exchange") is not None and j.get("M") is not None]
+    if not waiting:
+        return
+    ex = waiting[0]["val_exchange"]
+    parts = [j["X"][j["n_train"]:].reshape(-1) for j in waiting]
+    gathered = ex.gather_rows(torch.cat(parts).unsqueeze(0))          # [ranks, floats per rank]
+    offset = 0
+    for j, part in zip(waiting, parts):
+        j["Xv"] = (gathered, offset, j["X"].shape[0] - j["n_train"])
+        offset += part.numel()
 
 
 def dot_product_with_exchange(layer: nn.Module, A: torch.Tensor, B: torch.Tensor, n_val_local: int, ex) -> bool:
@@ -329,16 +343,13 @@ def dot_product_with_exchange(layer: nn.Module, A: torch.Tensor, B: torch.Tensor
     n_val = n_val_local * world
     if isinstance(layer, nn.LayerNorm):
         gw, gb = _layernorm_vectors(layer, A, B)
-        if layer.bias is None:
-            _set_dot(layer.weight, _gram_of_vectors(_with_gathered_val_rows(gw, n_train, ex), n_val))
-            return True
-        # (two collectives: their results may still be in flight, so nothing here may copy them)
-        _set_dot(layer.weight, _gram_of_vectors(_with_gathered_val_rows(gw, n_train, ex), n_val))
-        _set_dot(layer.bias, _gram_of_vectors(_with_gathered_val_rows(gb, n_train, ex), n_val))
+        _set_dot(layer.weight, _gram_of_vectors_exchanged(gw, n_train, n_val, ex))
+        if layer.bias is not None:
+            _set_dot(layer.bias, _gram_of_vectors_exchanged(gb, n_train, n_val, ex))
         return True
     if type(layer) in _SELF_APPLYING and type(layer).__name__.endswith("RMSNorm"):
         gw = _rmsnorm_vectors(layer, A, B)
-        _set_dot(layer.weight, _gram_of_vectors(_with_gathered_val_rows(gw, n_train, ex), n_val))
+        _set_dot(layer.weight, _gram_of_vectors_exchanged(gw, n_train, n_val, ex))
         return True
     if _HFConv1D is not None and isinstance(layer, _HFConv1D):
         weight_is_in_by_out = True
@@ -378,7 +389,8 @@ def dot_product_with_exchange(layer: nn.Module, A: torch.Tensor, B: torch.Tensor
     if has_bias:
         if colsums is None:
             colsums = ops.colsum(B)
-        _bias_terms(layer, B, n_val, _with_gathered_val_rows(colsums, n_train, ex))
+        _set_dot(layer.bias, _gram_of_vectors_exchanged(colsums, n_train, n_val, ex))
+        layer._ghost_colsums = colsums               # local rows: reused by the bias train gradient
     return True
 
 

@@ -513,7 +513,11 @@ def small_reduce_batch(jobs) -> None:
     """Run many :func:`small_gram` / :func:`rows_sum` reductions in one launch (48 jobs per launch).
     ``jobs``: dicts with ``X`` (contiguous float32 ``[n_train + n_val, F]``), ``n_train``, ``n_val`` and
     optionally ``M`` (float32 ``[n_val, n_train]`` output, with ``dot_scale``) and ``sum_out``
-    (float32 / bfloat16 ``[F]`` output, with ``sum_scale``); the outputs are written in place."""
+    (float32 / bfloat16 ``[F]`` output, with ``sum_scale``); the outputs are written in place.  A job
+    with ``Xv = (gathered, offset, per_rank)`` takes its validation rows from ``gathered[r, offset + i
+    * F : ...]`` (row ``r * per_rank + i``; ``gathered`` is a contiguous float32 ``[ranks, pitch]`` tensor, the
+    result of one all-gather that carried many jobs' validation rows) and only its train rows from
+    ``X``."""
     if not jobs:
         return
     lib = _lib.load()
@@ -537,6 +541,18 @@ def small_reduce_batch(jobs) -> None:
         rec.sum_is_f32 = _dt_flag(out) if out is not None else 1
         rec.dot_scale = float(job.get("dot_scale", 1.0))
         rec.sum_scale = float(job.get("sum_scale", 1.0))
+        xv = job.get("Xv")
+        if xv is not None:
+            gathered, offset, per_rank = xv
+            if gathered.dtype != _F32 or gathered.dim() != 2 or not gathered.is_contiguous() \
+                    or offset + per_rank * X.shape[1] > gathered.shape[1] \
+                    or gathered.shape[0] * per_rank != job["n_val"] or X.shape[0] < job["n_train"]:
+                raise ValueError("small_reduce_batch: bad layout of the separate validation rows")
+            rec.Xv = gathered.data_ptr() + 4 * int(offset)
+            rec.v_rank_pitch = int(gathered.shape[1])
+            rec.v_per_rank = int(per_rank)
+        else:
+            rec.Xv = None
         nbytes += 4.0 * X.numel()
     with _Timed("small_reduce_batch_kernel", "hbm", 0.0, nbytes):
         _lib.check(lib.ghost_small_reduce_batch(arr, len(jobs), _stream_ptr()))

@@ -195,6 +195,14 @@ typedef struct ghost_small_job {
   int n_train, n_val, F;
   int sum_is_f32;
   float dot_scale, sum_scale;
+  /* Validation rows kept apart from X (X then holds the train rows, and whatever follows them is
+   * not read): validation row v is Xv[(v / v_per_rank) * v_rank_pitch + (v % v_per_rank) * F], the
+   * layout of one all-gather over ranks that carried many jobs' validation rows at once (every
+   * rank sent one packed buffer of v_rank_pitch floats; this job's rows start at Xv inside it).
+   * Xv = NULL: the validation rows follow the train rows in X. */
+  const float* Xv;
+  long long v_rank_pitch;
+  int v_per_rank;
 } ghost_small_job;
 int ghost_small_reduce_batch(const ghost_small_job* jobs, int n_jobs, void* stream);
 

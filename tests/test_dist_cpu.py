@@ -255,12 +255,23 @@ def _worker_val_exchange(rank, world, port, q):
         tiles = torch.arange(2 * 3 * (v_hi - v_lo) * 4, dtype=torch.float32).reshape(1, 2 * 3, v_hi - v_lo, 4) + 1000 * rank
         both = ex.gather_rows(tiles)                              # [ranks, tiles, per rank, elems], rank-major
         ok = ok and both.shape[0] == world and torch.equal(both[rank], tiles[0]) and float(both[1 - rank][0, 0, 0]) == 1000.0 * (1 - rank)
-        assert L.begin_deferred_dots()
-        full = L._with_gathered_val_rows(x_loc, t_hi - t_lo, ex)  # in flight until the pass "ends"
-        ok = ok and len(L._PENDING_WAITS) == 1
-        L.finalize_pending_dots()
-        ok = ok and not L._PENDING_WAITS and torch.equal(full, want)
-        ok = ok and ex.calls == 3
+        # inside a backward pass the vectors of all layers cross the ranks in one packed all-gather
+        Y = torch.randn(n_t + n_v, 10, generator=g)
+        y_loc = torch.cat((Y[t_lo:t_hi], Y[n_t + v_lo:n_t + v_hi]))
+        jobs = []
+        for vec in (x_loc, y_loc):
+            jobs.append({"X": vec, "n_train": t_hi - t_lo, "n_val": n_v, "M": torch.empty(n_v, t_hi - t_lo),
+                         "val_exchange": ex})
+        jobs.append({"X": x_loc, "n_train": t_hi - t_lo, "n_val": n_v, "sum_out": torch.empty(F)})   # no exchange
+        L._exchange_pending_val_rows(jobs)
+        ok = ok and "Xv" not in jobs[2] and ex.calls == 3
+        for job, full in zip(jobs[:2], (X, Y)):
+            gathered, off, per = job["Xv"]
+            width = job["X"].shape[1]
+            ok = ok and gathered.shape == (world, per * (F + 10)) and per == v_hi - v_lo
+            for v in range(n_v):
+                row = gathered[v // per, off + (v % per) * width: off + (v % per + 1) * width]
+                ok = ok and torch.equal(row, full[n_t + v])
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
