@@ -744,12 +744,11 @@ def dominant_kernel_roofline(prof, peaks):
         achieved = rec["flops"] / calls / avg_s / 1e12
         traffic = None
         if "persample" in name:
-            # ncu capture of the mlp.c_fc shape with the bias column sums inside the GEMM kernel: 800.5 MB
-            # of DRAM traffic per call -- GEMM pass 445.3 MB read (315 MB of inputs once + 130 MB of
-            # out-grad rows the column-sum warps did not find in L2) and 160.5 MB of tile write-back,
-            # streaming pass 188.8 MB of tiles read once and 5.9 MB of results -- for 315 MB of input
-            # bytes; scaled by input bytes
-            traffic = rec["bytes"] / calls * (800.5 / 315.0)
+            # ncu capture of the mlp.c_fc shape with the bias column sums inside the GEMM kernel and the
+            # tiles stored by the copy engine: 669.7 MB of DRAM traffic per call -- GEMM pass 315.3 MB
+            # read (the inputs, once) and 160.1 MB of tile write-back, streaming pass 188.8 MB of tiles
+            # read once and 5.6 MB of results -- for 315 MB of input bytes; scaled by input bytes
+            traffic = rec["bytes"] / calls * (669.7 / 315.0)
         return {"kernel": name, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor"],
                 "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": traffic,
                 "launches": calls, "avg_ms": avg_s * 1e3, "peak_source": peaks["source"]}
