@@ -916,20 +916,32 @@ class _RecordedExchangeAsync(_RecordedExchange):
         return out, self._Work(out, res)
 
 
+@pytest.mark.parametrize("family", ["gpt2", "llama"])
 @pytest.mark.parametrize("overlap", [False, True])
 @pytest.mark.parametrize("world", [2, 4])
-def test_validation_gradient_exchange_matches_replicated_validation(world, overlap):
+def test_validation_gradient_exchange_matches_replicated_validation(world, overlap, family):
     """Validation batch split over ranks with the ranks exchanging validation GRADIENTS (tiles on the
     per-sample path, per-sample vectors of bias and norm layers, operands elsewhere): every rank's
     matrices equal those of the same rank run with the whole validation batch replicated, up to the
-    (local batch size)^2 factor of the loss mean, and the train gradients are the same."""
+    (local batch size)^2 factor of the loss mean, and the train gradients are the same.  Two model
+    families: GPT-2 (Conv1D with biases, LayerNorm, two embeddings) and a Hugging Face Llama (Linear
+    without biases, RMS norms)."""
     from ghostsuite_b200.ghostEngines import GradDotProdEngine
     from ghostsuite_b200.ghostEngines import autograd_grad_sample_dotprod as plumbing
     from ghostsuite_b200.ghostEngines import supported_layers_grad_samplers_dotprod as L
     from ghostsuite_b200.workloads import GPT2Like, GPT2Config
     torch.manual_seed(6)
-    cfg = GPT2Config(vocab_size=211, n_positions=48, n_embd=64, n_layer=2, n_head=4)
-    model = GPT2Like(cfg).to(torch.bfloat16).cuda()
+    if family == "gpt2":
+        cfg = GPT2Config(vocab_size=211, n_positions=48, n_embd=64, n_layer=2, n_head=4)
+        model = GPT2Like(cfg).to(torch.bfloat16).cuda()
+        loss_of = lambda ids: model(ids, labels=ids)[0]
+    else:
+        from transformers import LlamaConfig, LlamaForCausalLM
+        cfg = LlamaConfig(vocab_size=211, hidden_size=64, intermediate_size=192, num_hidden_layers=2,
+                          num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                          tie_word_embeddings=False, attention_dropout=0.0, use_cache=False)
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16).cuda()
+        loss_of = lambda ids: model(input_ids=ids, labels=ids).loss
     n_t, per, T = 3, 4 // world if world == 4 else 2, 40
     n_val = per * world
     g = torch.Generator().manual_seed(3)
@@ -943,7 +955,7 @@ def test_validation_gradient_exchange_matches_replicated_validation(world, overl
         plumbing.VALIDATION_GATHER = exchange
         L.VALIDATION_EXCHANGE = exchange
         try:
-            model(ids, labels=ids)[0].backward()
+            loss_of(ids).backward()
             torch.cuda.synchronize()
             out = {n: (p.grad_dot_prod_matrix.float().cpu(), p.train_grad.float().cpu())
                    for n, p in model.named_parameters() if hasattr(p, "grad_dot_prod_matrix")}
