@@ -330,7 +330,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         state["sync"] = gdist.overlap_train_grad_sync(eng, group) if world > 1 else None
         if shard_val and world > 1:
             if shard_val == "gradients":
-                gdist.exchange_validation(eng, group)
+                if args.exchange_own_group and "xgroup" not in state:
+                    state["xgroup"] = dist.new_group(ranks=list(range(world)))
+                gdist.exchange_validation(eng, group, state.get("xgroup"))
             else:
                 gdist.shard_validation(eng, group)
         return eng
@@ -1499,6 +1501,9 @@ def main():
                     help="multi-GPU step: comma-separated variants to time (val_replicated is always timed)")
     ap.add_argument("--exchange-overlap", type=int, default=-1,
                     help="override the engines' EXCHANGE_OVERLAP switch (0 / 1) for an A/B run")
+    ap.add_argument("--exchange-own-group", type=int, default=1,
+                    help="1 (default): the validation-gradient exchange uses an NCCL communicator of its own, so "
+                         "that its all-gathers do not queue behind the gradient all-reduces; 0: one communicator")
     ap.add_argument("--exchange-depth", type=int, default=-1,
                     help="override ops.EXCHANGE_DEPTH (layers whose streaming pass may wait for its all-gather)")
     ap.add_argument("--fuse-bias-colsums", type=int, default=-1,

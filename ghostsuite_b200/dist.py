@@ -340,16 +340,18 @@ class ValidationExchange:
         return out, work
 
 
-def exchange_validation(engine, group=None) -> ValidationExchange:
+def exchange_validation(engine, group=None, exchange_group=None) -> ValidationExchange:
     """:func:`shard_validation` with the cheaper exchange where a layer allows it: on the per-sample
     path of Linear / Conv1D layers every rank computes the gradient tiles of its own validation
     samples and the ranks all-gather those (``2 * n_val * d * p`` bytes per layer) instead of the
     validation rows of both operands, and no rank repeats another rank's validation GEMMs; bias and
     norm layers exchange their per-sample vectors.  Other layers (Gram path, embeddings) gather
-    operands as :class:`ShardedValidation` does.  Undo with :func:`unshard_validation`."""
+    operands as :class:`ShardedValidation` does.  ``exchange_group`` (same ranks as ``group``) gives the
+    tile and vector all-gathers a communicator of their own, so that they do not queue behind the
+    gradient all-reduces of :func:`overlap_train_grad_sync`.  Undo with :func:`unshard_validation`."""
     from .ghostEngines import supported_layers_grad_samplers_dotprod as layers
     shard_validation(engine, group)
-    ex = ValidationExchange(group)
+    ex = ValidationExchange(exchange_group if exchange_group is not None else group)
     layers.VALIDATION_EXCHANGE = ex
     engine._ghost_val_exchange = ex
     return ex
